@@ -1,0 +1,104 @@
+"""Engine configuration: the knobs of liteinfer's `EngineConfig`, with its names and meanings.
+
+Reference: liteinfer/config.py:13-103.  Fields that chose between attention
+back ends are accepted for compatibility but only name this engine's one path.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+_DTYPES = {
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float32": torch.float32, "fp32": torch.float32, "float": torch.float32,
+}
+
+
+def parse_dtype(dtype: str | torch.dtype) -> torch.dtype:
+    """bfloat16 (the serving precision) or float32 (true 32-bit everywhere)."""
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {dtype} is not supported; use bfloat16 or float32")
+        return dtype
+    try:
+        return _DTYPES[str(dtype).lower().replace("torch.", "")]
+    except KeyError:
+        raise ValueError(f"dtype {dtype!r} is not supported; use bfloat16 or float32") from None
+
+
+@dataclass
+class EngineConfig:
+    model: str
+
+    dtype: torch.dtype | str = torch.bfloat16
+    device: str = "auto"
+
+    max_num_seqs: int = 32
+    max_model_len: int = 4096
+
+    # Tokens one step may compute across all its sequences; a prompt larger than
+    # what is left of it is cut into portions.  None: `max_num_seqs * max_model_len`,
+    # which never cuts (liteinfer/config.py:23-28,92-97).
+    max_num_batched_tokens: int | None = None
+
+    # Seeds requests whose SamplingParams carry no seed of their own.
+    seed: int = 42
+
+    # Only this engine's paged kernels exist; None or "paged" name them.
+    attn_implementation: str | None = None
+
+    max_waiting_seqs: int = 1024
+
+    # Replay decode steps from CUDA graphs.  None: wherever the device is CUDA.
+    enable_cuda_graphs: bool | None = None
+
+    # Programs that share one sequence's key loop in decode attention; None lets
+    # the engine choose from the batch width and the context.
+    paged_decode_splits: int | None = None
+
+    collect_stats: bool = True
+
+    block_size: int = 16
+    gpu_memory_utilization: float = 0.85
+    num_gpu_blocks: int | None = None
+
+    def __post_init__(self) -> None:
+        self.dtype = parse_dtype(self.dtype)
+        if self.max_num_seqs < 1:
+            raise ValueError("max_num_seqs must be >= 1")
+        if self.max_model_len < 1:
+            raise ValueError("max_model_len must be >= 1")
+        if self.block_size < 1:
+            raise ValueError("block_size must be >= 1")
+        if self.max_num_batched_tokens is not None and self.max_num_batched_tokens < self.max_num_seqs:
+            raise ValueError(
+                f"max_num_batched_tokens={self.max_num_batched_tokens} must be >= "
+                f"max_num_seqs={self.max_num_seqs}"
+            )
+        if self.max_waiting_seqs < 1:
+            raise ValueError("max_waiting_seqs must be >= 1")
+        if self.paged_decode_splits is not None and self.paged_decode_splits < 1:
+            raise ValueError("paged_decode_splits must be >= 1")
+        if not 0 < self.gpu_memory_utilization <= 1:
+            raise ValueError("gpu_memory_utilization must be in (0, 1]")
+        if self.num_gpu_blocks is not None and self.num_gpu_blocks < 1:
+            raise ValueError("num_gpu_blocks must be >= 1")
+        if self.attn_implementation not in (None, "paged"):
+            raise ValueError(
+                f"attn_implementation {self.attn_implementation!r} does not exist here; "
+                "this engine has one attention path, 'paged'"
+            )
+
+    @property
+    def token_budget(self) -> int:
+        """`max_num_batched_tokens`, with None resolved to the most a step can ever hold."""
+        if self.max_num_batched_tokens is not None:
+            return self.max_num_batched_tokens
+        return self.max_num_seqs * self.max_model_len
+
+    def resolved_device(self) -> torch.device:
+        if self.device == "auto":
+            return torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
+        return torch.device(self.device)

@@ -1,0 +1,97 @@
+// Shared helpers of the liteinfer_b200 kernels (sm_100a).
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and a
+// stream, launches, and returns the launch's cudaError_t as an int (0 = ok); the
+// Python side turns a non-zero value into an exception.  Nothing here allocates.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LI_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Error codes above cudaError_t's range: a size the kernel refuses.
+#define LI_ERR_UNSUPPORTED 100001
+#define LI_ERR_ALIGNMENT 100002
+
+#define LI_LAUNCH_CHECK() return (int)cudaGetLastError()
+
+namespace li {
+
+// dtype codes shared with Python (liteinfer_b200/ops/kernels.py).
+constexpr int kFloat32 = 0;
+constexpr int kBFloat16 = 1;
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(bf16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+// Rounds through T and back: the value a tensor of dtype T would hold.
+template <typename T> __device__ __forceinline__ float round_to(float x) { return to_float(from_float<T>(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The
+// order of the additions depends only on blockDim, never on the data or the grid.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+template <typename T> struct Vec16;  // 16 bytes of T
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  float4 raw;
+  __device__ __forceinline__ float get(int i) const { return (&raw.x)[i]; }
+  __device__ __forceinline__ void set(int i, float v) { (&raw.x)[i] = v; }
+};
+template <> struct Vec16<bf16> {
+  static constexpr int N = 8;
+  uint4 raw;
+  __device__ __forceinline__ float get(int i) const {
+    return __bfloat162float(reinterpret_cast<const bf16*>(&raw)[i]);
+  }
+  __device__ __forceinline__ void set(int i, float v) {
+    reinterpret_cast<bf16*>(&raw)[i] = __float2bfloat16_rn(v);
+  }
+};
+
+template <typename T> __device__ __forceinline__ Vec16<T> load16(const T* p) {
+  Vec16<T> v;
+  v.raw = *reinterpret_cast<const decltype(v.raw)*>(p);
+  return v;
+}
+template <typename T> __device__ __forceinline__ void store16(T* p, const Vec16<T>& v) {
+  *reinterpret_cast<decltype(v.raw)*>(p) = v.raw;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace li

@@ -1,0 +1,213 @@
+// Row-wise kernels: embedding gather, RMSNorm (alone, fused with the residual
+// add, fused with the gather of the rows whose logits are wanted), gated
+// activation, bias add.  Statistics, the residual sum and the activation are
+// computed in 32-bit whatever the storage type.
+//
+// Rounding points follow liteinfer/models/llama.py:43-48 (the normalised value is
+// rounded to the storage type, then multiplied by the weight), :114 (the
+// activation is rounded, then multiplied by `up`) and :187,192 (the residual
+// sum is rounded to the storage type).
+#include "common.cuh"
+
+namespace li {
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
+                                 int width, int vocab, int* __restrict__ error_flag) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {  // a token id outside the table: record it, write zeros, read nothing
+    if (threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = from_float<T>(0.f);
+    return;
+  }
+  const T* src = table + (size_t)id * width;
+  T* dst = out + (size_t)t * width;
+  constexpr int N = Vec16<T>::N;
+  if (width % N == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0) {
+    for (int i = threadIdx.x * N; i < width; i += blockDim.x * N) store16(dst + i, load16(src + i));
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per output row.  `rows` (optional) picks the input row of each output
+// row; `delta` (optional) is added to the input row first, and when
+// `write_residual` the sum is stored back to the input row (in place).
+template <typename T>
+__global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ weight,
+                               T* __restrict__ out, const int* __restrict__ rows, int width, float eps,
+                               int write_residual) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const size_t src_row = rows ? (size_t)rows[r] : (size_t)r;
+  T* xr = x + src_row * width;
+  const T* dr = delta ? delta + src_row * width : nullptr;
+  T* outr = out + (size_t)r * width;
+
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = to_float(xr[i]);
+    if (dr) {
+      v = round_to<T>(v + to_float(dr[i]));
+      if (write_residual) xr[i] = from_float<T>(v);
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = to_float(xr[i]);
+    if (dr && !write_residual) v = round_to<T>(v + to_float(dr[i]));
+    const float normed = round_to<T>(v * inv);
+    outr[i] = from_float<T>(to_float(weight[i]) * normed);
+  }
+}
+
+// residual += delta (no norm): used where a block ends without a following norm.
+template <typename T>
+__global__ void add_kernel(T* __restrict__ x, const T* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) x[i] = from_float<T>(to_float(x[i]) + to_float(delta[i]));
+}
+
+// out[r, c] += bias[c]
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ out, const T* __restrict__ bias, size_t rows, int width) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t n = rows * (size_t)width, stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = from_float<T>(to_float(out[i]) + to_float(bias[i % width]));
+}
+
+// --------------------------------------------------------- gated activation
+constexpr int kSilu = 0, kGelu = 1, kGeluTanh = 2, kRelu = 3;
+
+__device__ __forceinline__ float activate(float x, int act) {
+  switch (act) {
+    case kSilu: return x / (1.0f + expf(-x));
+    case kGelu: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    case kGeluTanh: {
+      const float inner = 0.79788456080286535588f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + tanhf(inner));
+    }
+    default: return fmaxf(x, 0.f);
+  }
+}
+
+// gate_up [rows, 2*width]: gate in the first `width` columns, up in the rest.
+template <typename T>
+__global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, size_t rows, int width, int act) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t n = rows * (size_t)width, stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const size_t r = i / width;
+    const int c = (int)(i - r * width);
+    const float g = to_float(gate_up[r * 2 * width + c]);
+    const float u = to_float(gate_up[r * 2 * width + width + c]);
+    out[i] = from_float<T>(round_to<T>(activate(g, act)) * u);
+  }
+}
+
+template <typename T>
+__global__ void act_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, size_t rows, int width, int act) {
+  constexpr int N = Vec16<T>::N;
+  const int vec_per_row = width / N;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t n = rows * (size_t)vec_per_row, stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const size_t r = i / vec_per_row;
+    const int c = (int)(i - r * vec_per_row) * N;
+    const Vec16<T> g = load16(gate_up + r * 2 * width + c);
+    const Vec16<T> u = load16(gate_up + r * 2 * width + width + c);
+    Vec16<T> o;
+#pragma unroll
+    for (int k = 0; k < N; ++k) o.set(k, round_to<T>(activate(g.get(k), act)) * u.get(k));
+    store16(out + r * width + c, o);
+  }
+}
+
+static int grid_for(size_t n, int block) {
+  size_t g = (n + block - 1) / block;
+  const size_t cap = 148 * 16;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+template <typename T>
+int launch_embedding(const int* ids, const void* table, void* out, int tokens, int width, int vocab,
+                     int* error_flag, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  embedding_kernel<T><<<tokens, 128, 0, s>>>(ids, (const T*)table, (T*)out, width, vocab, error_flag);
+  LI_LAUNCH_CHECK();
+}
+
+template <typename T>
+int launch_rmsnorm(void* x, const void* delta, const void* weight, void* out, const int* rows, int out_rows,
+                   int width, float eps, int write_residual, cudaStream_t s) {
+  if (out_rows == 0) return 0;
+  const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  rmsnorm_kernel<T><<<out_rows, block, 0, s>>>((T*)x, (const T*)delta, (const T*)weight, (T*)out, rows, width, eps,
+                                               write_residual);
+  LI_LAUNCH_CHECK();
+}
+
+template <typename T>
+int launch_act_mul(const void* gate_up, void* out, size_t rows, int width, int act, cudaStream_t s) {
+  if (rows == 0) return 0;
+  constexpr int N = Vec16<T>::N;
+  if (width % N == 0 && aligned16(gate_up) && aligned16(out)) {
+    const size_t n = rows * (size_t)(width / N);
+    act_mul_vec_kernel<T><<<grid_for(n, 256), 256, 0, s>>>((const T*)gate_up, (T*)out, rows, width, act);
+  } else {
+    act_mul_kernel<T><<<grid_for(rows * (size_t)width, 256), 256, 0, s>>>((const T*)gate_up, (T*)out, rows, width, act);
+  }
+  LI_LAUNCH_CHECK();
+}
+
+}  // namespace li
+
+using namespace li;
+
+// out[t, :] = table[ids[t], :].  An id outside [0, vocab) sets *error_flag (if given) and yields zeros.
+LI_EXPORT int li_embedding(int dtype, const int* ids, const void* table, void* out, int tokens, int width, int vocab,
+                           int* error_flag, cudaStream_t stream) {
+  return dtype == kFloat32 ? launch_embedding<float>(ids, table, out, tokens, width, vocab, error_flag, stream)
+                           : launch_embedding<bf16>(ids, table, out, tokens, width, vocab, error_flag, stream);
+}
+
+// out[r] = weight * norm(x[rows ? rows[r] : r] (+ delta[same row])); with write_residual the sum is stored to x.
+LI_EXPORT int li_rmsnorm(int dtype, void* x, const void* delta, const void* weight, void* out, const int* rows,
+                         int out_rows, int width, float eps, int write_residual, cudaStream_t stream) {
+  return dtype == kFloat32
+             ? launch_rmsnorm<float>(x, delta, weight, out, rows, out_rows, width, eps, write_residual, stream)
+             : launch_rmsnorm<bf16>(x, delta, weight, out, rows, out_rows, width, eps, write_residual, stream);
+}
+
+LI_EXPORT int li_add(int dtype, void* x, const void* delta, size_t n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (dtype == kFloat32)
+    add_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((float*)x, (const float*)delta, n);
+  else
+    add_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((bf16*)x, (const bf16*)delta, n);
+  LI_LAUNCH_CHECK();
+}
+
+LI_EXPORT int li_add_bias(int dtype, void* out, const void* bias, size_t rows, int width, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const size_t n = rows * (size_t)width;
+  if (dtype == kFloat32)
+    add_bias_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((float*)out, (const float*)bias, rows, width);
+  else
+    add_bias_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((bf16*)out, (const bf16*)bias, rows, width);
+  LI_LAUNCH_CHECK();
+}
+
+// out[r, c] = act(gate_up[r, c]) * gate_up[r, width + c];  act: 0 silu, 1 gelu (erf), 2 gelu (tanh), 3 relu.
+LI_EXPORT int li_act_mul(int dtype, const void* gate_up, void* out, size_t rows, int width, int act,
+                         cudaStream_t stream) {
+  if (act < 0 || act > 3) return LI_ERR_UNSUPPORTED;
+  return dtype == kFloat32 ? launch_act_mul<float>(gate_up, out, rows, width, act, stream)
+                           : launch_act_mul<bf16>(gate_up, out, rows, width, act, stream);
+}

@@ -1,0 +1,101 @@
+// Rotary position encoding of q and k, fused with the write of k and v into the
+// paged cache.
+//
+// q, k, v of a token lie side by side in one row of the fused projection's
+// output: [q heads | k heads | v heads], each head `head_dim` wide.  q is rotated
+// in place; k is rotated and v copied into this layer's pages.  Angles are
+// position * inv_freq in 32-bit, cos and sin in 32-bit (liteinfer/models/llama.py:
+// 78-86 computes them in float32 too, then rounds the tables to the model type;
+// here the tables are never rounded, only the rotated result is).  Pairing is
+// half-split: dimension j pairs with j + rotary_dim/2 (llama.py:89-102).
+// Dimensions from rotary_dim on pass through unrotated.
+//
+// A page holds `page_size` tokens of every KV head: pool[page][kv_head][slot][dim].
+// The page of a token is block_table[seq][position / page_size]; a negative entry
+// (a page already given back) skips the write.
+#include "common.cuh"
+
+namespace li {
+
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                     int table_stride, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                     const float* __restrict__ inv_freq, int heads, int kv_heads, int head_dim,
+                                     int rotary_dim, int page_size, int num_pages) {
+  extern __shared__ float cs[];  // cos[half], sin[half]
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rotary_dim / 2;
+  float* cosv = cs;
+  float* sinv = cs + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float angle = (float)pos * inv_freq[i];
+    cosv[i] = cosf(angle);
+    sinv[i] = sinf(angle);
+  }
+  __syncthreads();
+
+  const int row_width = (heads + 2 * kv_heads) * head_dim;
+  T* row = qkv + (size_t)t * row_width;
+
+  // q: rotate in place.  Work item = (head, pair index or pass-through dim).
+  const int pass = head_dim - rotary_dim;
+  const int per_head = half;  // rotated pairs per head; pass-through dims stay as they are
+  for (int w = threadIdx.x; w < heads * per_head; w += blockDim.x) {
+    const int h = w / per_head, i = w - h * per_head;
+    T* p = row + h * head_dim;
+    const float a = to_float(p[i]), b = to_float(p[i + half]);
+    p[i] = from_float<T>(a * cosv[i] - b * sinv[i]);
+    p[i + half] = from_float<T>(b * cosv[i] + a * sinv[i]);
+  }
+  (void)pass;
+
+  const int seq = seq_of_token[t];
+  const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+  if (page < 0 || page >= num_pages) return;
+  const int slot = pos % page_size;
+
+  const T* krow = row + heads * head_dim;
+  const T* vrow = krow + kv_heads * head_dim;
+  for (int w = threadIdx.x; w < kv_heads * head_dim; w += blockDim.x) {
+    const int h = w / head_dim, j = w - h * head_dim;
+    const size_t dst = (((size_t)page * kv_heads + h) * page_size + slot) * head_dim + j;
+    float kv;
+    if (j < half) {
+      kv = to_float(krow[w]) * cosv[j] - to_float(krow[w + half]) * sinv[j];
+    } else if (j < rotary_dim) {
+      kv = to_float(krow[w]) * cosv[j - half] + to_float(krow[w - half]) * sinv[j - half];
+    } else {
+      kv = to_float(krow[w]);
+    }
+    k_pool[dst] = from_float<T>(kv);
+    v_pool[dst] = vrow[w];
+  }
+}
+
+}  // namespace li
+
+using namespace li;
+
+// inv_freq may be null with rotary_dim 0: nothing is rotated, k and v are only stored.
+LI_EXPORT int li_rope_kv_write(int dtype, void* qkv, const int* positions, const int* seq_of_token,
+                               const int* block_table, int table_stride, void* k_pool, void* v_pool,
+                               const float* inv_freq, int tokens, int heads, int kv_heads, int head_dim,
+                               int rotary_dim, int page_size, int num_pages, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return LI_ERR_UNSUPPORTED;
+  if (rotary_dim > 0 && inv_freq == nullptr) return LI_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)rotary_dim * sizeof(float);
+  if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
+  const int block = 256;
+  if (dtype == kFloat32)
+    rope_kv_write_kernel<float><<<tokens, block, smem, stream>>>(
+        (float*)qkv, positions, seq_of_token, block_table, table_stride, (float*)k_pool, (float*)v_pool, inv_freq,
+        heads, kv_heads, head_dim, rotary_dim, page_size, num_pages);
+  else
+    rope_kv_write_kernel<bf16><<<tokens, block, smem, stream>>>(
+        (bf16*)qkv, positions, seq_of_token, block_table, table_stride, (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads,
+        kv_heads, head_dim, rotary_dim, page_size, num_pages);
+  LI_LAUNCH_CHECK();
+}

@@ -1,0 +1,28 @@
+"""From a model folder to a `ModelRunner`: the one way every entry point builds the engine's core."""
+
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from liteinfer_b200.cache.manager import CacheManager
+from liteinfer_b200.engine.runner import ModelRunner
+from liteinfer_b200.weights.loader import load_model
+
+
+def resolve_model_path(model: str | Path) -> Path:
+    """A local folder only (liteinfer/hub.py:26-28 returns a local directory as it is;
+    its download branch needs a network and is not built)."""
+    path = Path(model)
+    if not path.is_dir():
+        raise FileNotFoundError(f"model folder {model!r} does not exist (models are read from local folders only)")
+    return path
+
+
+def build_runner(model_dir: str | Path, dtype: torch.dtype, device: torch.device | str, page_size: int,
+                 num_pages: int, max_requests: int, decode_splits: int | None = None) -> ModelRunner:
+    device = torch.device(device)
+    model, _ = load_model(resolve_model_path(model_dir), dtype, device)
+    cache = CacheManager(model.cache_needs(), model.schedule, page_size, num_pages, max_requests, dtype, device)
+    return ModelRunner(model, cache, decode_splits)

@@ -1,0 +1,266 @@
+"""Python faces of the CUDA kernels in `liteinfer_b200/csrc`.
+
+Every function checks its tensors (device, dtype, contiguity, shapes), launches
+on torch's current stream and raises when the launch is refused.  None of them
+has a CPU or library path: a tensor that is not on a CUDA device raises
+`KernelLibraryError`.  The parts of a model call these functions through the
+module (`from liteinfer_b200 import ops` then `ops.rmsnorm(...)`), never by a
+bound name, so tests can stand in for a single kernel.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_size_t, c_void_p
+
+import torch
+
+from liteinfer_b200.ops.library import KernelLibraryError, load
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "gelu_tanh": 2, "relu": 3}
+
+_ERRORS = {
+    100001: "the kernel refuses these sizes (unsupported shape or option)",
+    100002: "the kernel needs 16-byte aligned rows",
+}
+
+_functions: dict[str, ctypes._CFuncPtr] = {}
+
+_SIGNATURES = {
+    "li_embedding": ("elementwise", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "li_rmsnorm": ("elementwise", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                                   c_int, c_void_p]),
+    "li_add": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "li_add_bias": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "li_act_mul": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
+    "li_rope_kv_write": ("rope_cache", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "li_paged_attention_generic": ("attention_generic", [
+        c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "li_gemm_simt": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "li_sample": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_void_p]),
+}
+
+
+def _fn(name: str):
+    fn = _functions.get(name)
+    if fn is None:
+        library, argtypes = _SIGNATURES[name]
+        fn = getattr(load(library), name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _functions[name] = fn
+    return fn
+
+
+def _check(code: int, name: str) -> None:
+    if code == 0:
+        return
+    if code in _ERRORS:
+        raise KernelLibraryError(f"{name}: {_ERRORS[code]}")
+    raise KernelLibraryError(f"{name}: CUDA error {code} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelLibraryError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}") from None
+
+
+def _on_gpu(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelLibraryError(
+                "liteinfer_b200 kernels run on a CUDA device only; there is no CPU path "
+                f"(got a tensor on {t.device})")
+        if not t.is_contiguous():
+            raise KernelLibraryError("kernels take contiguous tensors")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _int32(t: torch.Tensor | None, what: str) -> None:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelLibraryError(f"{what} must be int32, got {t.dtype}")
+
+
+# ------------------------------------------------------------------ row-wise
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+              error_flag: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = table[ids[t]].  An id outside the table sets `error_flag[0]` and gives a zero row."""
+    _on_gpu(ids, table, out, error_flag)
+    _int32(ids, "ids")
+    _int32(error_flag, "error_flag")
+    tokens, width = out.shape
+    assert ids.numel() == tokens and table.shape[1] == width and table.dtype == out.dtype
+    _check(_fn("li_embedding")(_code(out), ids.data_ptr(), table.data_ptr(), out.data_ptr(), tokens, width,
+                               table.shape[0], _ptr(error_flag), _stream()), "embedding")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            delta: torch.Tensor | None = None, rows: torch.Tensor | None = None,
+            write_residual: bool = False) -> torch.Tensor:
+    """out[r] = weight * rmsnorm(x[row] (+ delta[row])), row = rows[r] if rows is given else r.
+
+    With `write_residual` the sum x + delta is stored back into x (the residual
+    stream moves on in place); statistics and the sum are 32-bit.
+    """
+    _on_gpu(x, weight, out, delta, rows)
+    _int32(rows, "rows")
+    width = x.shape[-1]
+    out_rows = out.shape[0]
+    assert weight.numel() == width and out.shape[-1] == width and x.dtype == out.dtype == weight.dtype
+    assert delta is None or (delta.shape == x.shape and delta.dtype == x.dtype)
+    assert rows is not None or out_rows == x.shape[0]
+    assert rows is None or rows.numel() == out_rows
+    assert not (write_residual and delta is None)
+    _check(_fn("li_rmsnorm")(_code(x), x.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), _ptr(rows),
+                             out_rows, width, float(eps), int(write_residual), _stream()), "rmsnorm")
+    return out
+
+
+def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """x += delta, summed in 32-bit."""
+    _on_gpu(x, delta)
+    assert x.shape == delta.shape and x.dtype == delta.dtype
+    _check(_fn("li_add")(_code(x), x.data_ptr(), delta.data_ptr(), x.numel(), _stream()), "add")
+    return x
+
+
+def add_bias_(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    _on_gpu(out, bias)
+    assert out.shape[-1] == bias.numel() and out.dtype == bias.dtype
+    _check(_fn("li_add_bias")(_code(out), out.data_ptr(), bias.data_ptr(), out.numel() // bias.numel(),
+                              bias.numel(), _stream()), "add_bias")
+    return out
+
+
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> torch.Tensor:
+    """out = act(gate_up[:, :w]) * gate_up[:, w:], w = out.shape[1]."""
+    _on_gpu(gate_up, out)
+    rows, width = out.shape
+    assert gate_up.shape == (rows, 2 * width) and gate_up.dtype == out.dtype
+    if activation not in ACTIVATIONS:
+        raise KernelLibraryError(f"activation {activation!r} has no kernel; known: {sorted(ACTIVATIONS)}")
+    _check(_fn("li_act_mul")(_code(out), gate_up.data_ptr(), out.data_ptr(), rows, width, ACTIVATIONS[activation],
+                             _stream()), "act_mul")
+    return out
+
+
+# ------------------------------------------------------------- matrix product
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias).
+
+    float32 runs the FFMA kernel (a true 32-bit product: tensor cores have no such
+    mode).  bfloat16 hands the product to the library GEMM, as the reference's
+    `nn.Linear` does (liteinfer/models/llama.py:108-110,137-140), with 32-bit
+    accumulation.
+    """
+    _on_gpu(x, weight, out, bias)
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and out.shape == (M, N) and x.dtype == weight.dtype == out.dtype
+    if x.dtype == torch.float32:
+        _check(_fn("li_gemm_simt")(0, x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
+                                   _stream()), "gemm_simt")
+        return out
+    if M > 0:
+        torch.mm(x, weight.t(), out=out)
+        if bias is not None:
+            add_bias_(out, bias)
+    return out
+
+
+def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """The FFMA product for either dtype (32-bit accumulation, fixed summation order)."""
+    _on_gpu(x, weight, out, bias)
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and out.shape == (M, N) and x.dtype == weight.dtype == out.dtype
+    _check(_fn("li_gemm_simt")(_code(x), x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
+                               _stream()), "gemm_simt")
+    return out
+
+
+# ------------------------------------------------------------ cache and mixer
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                  block_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                  inv_freq: torch.Tensor | None, heads: int, kv_heads: int, head_dim: int,
+                  rotary_dim: int, store: bool = True) -> None:
+    """Rotates q (in place) and k, and stores k and v of every token into its page
+    (with `store` False only q is rotated; the pages are left alone).
+
+    qkv: [tokens, (heads + 2*kv_heads) * head_dim].  k_pool, v_pool:
+    [pages, kv_heads, page_size, head_dim].  block_table: [seqs, max_pages] int32.
+    """
+    _on_gpu(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv_freq)
+    _int32(positions, "positions"); _int32(seq_of_token, "seq_of_token"); _int32(block_table, "block_table")
+    tokens = qkv.shape[0]
+    pages, kvh, page_size, hd = k_pool.shape
+    assert (kvh, hd) == (kv_heads, head_dim) and v_pool.shape == k_pool.shape
+    assert qkv.shape[1] == (heads + 2 * kv_heads) * head_dim
+    assert k_pool.dtype == qkv.dtype == v_pool.dtype
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rotary_dim)
+    _check(_fn("li_rope_kv_write")(_code(qkv), qkv.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
+                                   block_table.data_ptr(), block_table.stride(0), k_pool.data_ptr(),
+                                   v_pool.data_ptr(), _ptr(inv_freq), tokens, heads, kv_heads, head_dim,
+                                   rotary_dim if inv_freq is not None else 0, page_size, pages if store else 0, _stream()),
+           "rope_kv_write")
+
+
+def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor,
+                    v_pool: torch.Tensor, block_table: torch.Tensor, query_start_loc: torch.Tensor,
+                    context_lens: torch.Tensor, num_seqs: int, max_q_len: int, heads: int, kv_heads: int,
+                    head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Attention of each sequence's newest queries over its pages (any mix of portions and single tokens).
+
+    q: the tensor holding the queries, head h of token t at q[t, h*head_dim:...]
+    with `q_row_stride` elements between tokens (the fused qkv buffer is passed as
+    it is).  out: [tokens, heads*head_dim].
+    """
+    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
+    _int32(block_table, "block_table"); _int32(query_start_loc, "query_start_loc"); _int32(context_lens, "context_lens")
+    pages, kvh, page_size, hd = k_pool.shape
+    assert (kvh, hd) == (kv_heads, head_dim) and q.dtype == out.dtype == k_pool.dtype == v_pool.dtype
+    _check(_fn("li_paged_attention_generic")(
+        _code(q), q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
+        num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale), int(window), _stream()),
+        "paged_attention")
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _on_gpu(logits, out)
+    _int32(out, "out")
+    rows, vocab = logits.shape
+    _check(_fn("li_argmax")(_code(logits), logits.data_ptr(), rows, vocab, out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniform: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """One token per row: temperature, top-k, top-p, then the draw `uniform[r]` in [0, 1)."""
+    _on_gpu(logits, temperature, top_k, top_p, uniform, out)
+    _int32(out, "out"); _int32(top_k, "top_k")
+    rows, vocab = logits.shape
+    for t in (temperature, top_p, uniform):
+        assert t.dtype == torch.float32 and t.numel() == rows
+    _check(_fn("li_sample")(_code(logits), logits.data_ptr(), rows, vocab, temperature.data_ptr(), top_k.data_ptr(),
+                            top_p.data_ptr(), uniform.data_ptr(), out.data_ptr(), _stream()), "sample")
+    return out

@@ -1,0 +1,73 @@
+"""What a part sees of one step, and of its layer's cache.
+
+`StepContext` is the batch as tensors on the device: a flat run of tokens, each
+sequence's queries laid end to end, plus where each sequence's context ends and
+which pages or state slot hold it.  Parts read it; only the step function
+builds it.  `LayerCache` is the slice of the cache manager's storage that
+belongs to one stop of the schedule.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """A mixer that keeps keys and values per token: `window` None keeps every
+    token, a number keeps the newest `window` of them."""
+
+    kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A mixer that keeps a fixed-size state per request, of `shape` per request.
+    `kind`: "weight" (engine dtype) or "f32"."""
+
+    shape: tuple[int, ...]
+    kind: str = "f32"
+
+
+@dataclass
+class KVCacheView:
+    k_pool: torch.Tensor       # [pages, kv_heads, page_size, head_dim] of this layer
+    v_pool: torch.Tensor
+    group: int                 # index into StepContext.block_tables
+    page_size: int
+
+
+@dataclass
+class LayerCache:
+    kv: KVCacheView | None = None
+    state: torch.Tensor | None = None   # [slots, *StateNeed.shape] of this layer
+    read_only: bool = False             # this stop reads another stop's cache and stores nothing
+
+
+@dataclass
+class StepContext:
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor          # [T] int32
+    positions: torch.Tensor          # [T] int32, position of each token in its sequence
+    seq_of_token: torch.Tensor       # [T] int32, row of the batch each token belongs to
+    query_start_loc: torch.Tensor    # [B+1] int32, prefix sums of the sequences' query counts
+    context_lens: torch.Tensor       # [B] int32, tokens each sequence holds after this step
+    block_tables: list[torch.Tensor]  # per KV group: [B, max_pages] int32, page of each logical block (-1: none)
+    state_slots: torch.Tensor        # [B] int32, fixed-size state slot of each sequence
+    logit_rows: torch.Tensor         # [R] int32, token rows whose logits are wanted
+    num_logit_rows: int
+    max_query_len: int
+    max_context_len: int
+    query_lens: tuple[int, ...] = ()       # host copy
+    host_context_lens: tuple[int, ...] = ()  # host copy
+    decode_splits: int | None = None       # EngineConfig.paged_decode_splits
+    extras: dict = field(default_factory=dict)
+
+    @property
+    def is_decode_only(self) -> bool:
+        return self.max_query_len == 1

@@ -1,0 +1,58 @@
+"""Feed-forward parts.  Interface of a feed-forward:
+
+    tensor_specs() / bind(tensors)
+    forward(x, ctx) -> Tensor [tokens, hidden]
+"""
+
+from __future__ import annotations
+
+import torch
+
+from liteinfer_b200 import ops
+from liteinfer_b200.parts.context import StepContext
+from liteinfer_b200.parts.registry import register_feed_forward
+from liteinfer_b200.parts.spec import TensorSpec
+
+
+class GatedMLP:
+    """down(act(gate(x)) * up(x)) — liteinfer/models/llama.py:105-114.
+
+    gate and up are one product against the concatenated weights; the activation
+    and the multiply are one kernel.
+    """
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str, dtype: torch.dtype,
+                 device: torch.device, bias: bool = False) -> None:
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} has no kernel; known: {sorted(ops.ACTIVATIONS)}")
+        self.hidden_size, self.intermediate_size, self.activation, self.bias = (
+            hidden_size, intermediate_size, activation, bias)
+        self.gate_up_weight = self.gate_up_bias = self.down_weight = self.down_bias = None
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        i, h = self.intermediate_size, self.hidden_size
+        specs = {"gate_proj.weight": TensorSpec((i, h)), "up_proj.weight": TensorSpec((i, h)),
+                 "down_proj.weight": TensorSpec((h, i))}
+        if self.bias:
+            specs.update({"gate_proj.bias": TensorSpec((i,), init="zeros"), "up_proj.bias": TensorSpec((i,), init="zeros"),
+                          "down_proj.bias": TensorSpec((h,), init="zeros")})
+        return specs
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.gate_up_weight = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]])
+        self.down_weight = tensors["down_proj.weight"]
+        if self.bias:
+            self.gate_up_bias = torch.cat([tensors["gate_proj.bias"], tensors["up_proj.bias"]])
+            self.down_bias = tensors["down_proj.bias"]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        tokens = x.shape[0]
+        gate_up = torch.empty((tokens, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
+        ops.linear(x, self.gate_up_weight, gate_up, self.gate_up_bias)
+        hidden = torch.empty((tokens, self.intermediate_size), dtype=x.dtype, device=x.device)
+        ops.act_mul(gate_up, hidden, self.activation)
+        out = torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device)
+        return ops.linear(hidden, self.down_weight, out, self.down_bias)
+
+
+register_feed_forward("gated_mlp", GatedMLP)

@@ -1,0 +1,191 @@
+"""Plain torch stand-ins for the CUDA kernels, with the kernels' own signatures.
+
+Two uses, both in tests only.  (1) `-m gpu` kernel tests compare each CUDA
+kernel with the function of the same name here, on inputs of other sizes than
+the engine's.  (2) `-m "not gpu"` tests patch these functions over
+`liteinfer_b200.ops` (the `cpu_kernels` fixture) so that the step function, the
+cache and the scheduler can be driven on a CPU; the product itself has no such
+path.  Everything computes in float32 and rounds where the kernels round.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+def _r(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    return x.to(dtype).float()
+
+
+def embedding(ids, table, out, error_flag=None):
+    bad = (ids < 0) | (ids >= table.shape[0])
+    out.copy_(table[ids.long().clamp(0, table.shape[0] - 1)])
+    out[bad] = 0
+    if error_flag is not None and bool(bad.any()):
+        error_flag.fill_(1)
+    return out
+
+
+def rmsnorm(x, weight, eps, out, delta=None, rows=None, write_residual=False):
+    dtype = x.dtype
+    src = x if rows is None else x[rows.long()]
+    v = src.float()
+    if delta is not None:
+        d = delta if rows is None else delta[rows.long()]
+        v = _r(v + d.float(), dtype)
+        if write_residual:
+            x.copy_(v.to(dtype))
+    inv = 1.0 / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    out.copy_((weight.float() * _r(v * inv, dtype)).to(dtype))
+    return out
+
+
+def add_(x, delta):
+    x.copy_((x.float() + delta.float()).to(x.dtype))
+    return x
+
+
+def add_bias_(out, bias):
+    out.copy_((out.float() + bias.float()).to(out.dtype))
+    return out
+
+
+def _activate(x, activation):
+    if activation == "silu":
+        return x / (1.0 + torch.exp(-x))
+    if activation == "gelu":
+        return 0.5 * x * (1.0 + torch.erf(x / math.sqrt(2.0)))
+    if activation in ("gelu_pytorch_tanh", "gelu_tanh"):
+        return 0.5 * x * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x ** 3)))
+    if activation == "relu":
+        return torch.relu(x)
+    raise ValueError(activation)
+
+
+def act_mul(gate_up, out, activation):
+    w = out.shape[1]
+    g, u = gate_up[:, :w].float(), gate_up[:, w:].float()
+    out.copy_((_r(_activate(g, activation), out.dtype) * u).to(out.dtype))
+    return out
+
+
+def linear(x, weight, out, bias=None):
+    y = x.float() @ weight.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    out.copy_(y.to(out.dtype))
+    return out
+
+
+gemm_simt = linear
+
+
+def rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv_freq, heads, kv_heads,
+                  head_dim, rotary_dim, store=True):
+    T = qkv.shape[0]
+    dtype = qkv.dtype
+    page_size = k_pool.shape[2]
+    q = qkv[:, :heads * head_dim].float().view(T, heads, head_dim)
+    k = qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].float().view(T, kv_heads, head_dim)
+    v = qkv[:, (heads + kv_heads) * head_dim:].view(T, kv_heads, head_dim)
+    if inv_freq is not None and rotary_dim > 0:
+        half = rotary_dim // 2
+        angle = positions.float()[:, None] * inv_freq.float()[None, :]
+        cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+
+        def rot(x):
+            a, b = x[..., :half], x[..., half:rotary_dim]
+            return torch.cat((a * cos - b * sin, b * cos + a * sin, x[..., rotary_dim:]), dim=-1)
+
+        q, k = rot(q), rot(k)
+    qkv[:, :heads * head_dim] = q.reshape(T, -1).to(dtype)
+    if not store:
+        return
+    pos = positions.long()
+    pages = block_table.long()[seq_of_token.long(), pos // page_size]
+    ok = (pages >= 0) & (pages < k_pool.shape[0])
+    slot = pos % page_size
+    k_pool[pages[ok], :, slot[ok], :] = k.to(dtype)[ok]
+    v_pool[pages[ok], :, slot[ok], :] = v[ok]
+
+
+def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens, num_seqs,
+                    max_q_len, heads, kv_heads, head_dim, scale, window=0):
+    dtype = out.dtype
+    page_size = k_pool.shape[2]
+    groups = heads // kv_heads
+    qsl = query_start_loc.tolist()
+    ctx = context_lens.tolist()
+    qmat = q[:, :heads * head_dim].float().view(-1, heads, head_dim)
+    for s in range(num_seqs):
+        q0, q1 = qsl[s], qsl[s + 1]
+        n, c = q1 - q0, ctx[s]
+        if n == 0:
+            continue
+        first = 0 if window <= 0 else max(0, (c - n) - window + 1)
+        kpos = torch.arange(first, c, device=q.device)
+        pages = block_table[s].long()[kpos // page_size]
+        # keys / values [keys, kv_heads, head_dim]
+        keys = k_pool[pages, :, kpos % page_size, :].float()
+        vals = v_pool[pages, :, kpos % page_size, :].float()
+        keys = keys.repeat_interleave(groups, dim=1)
+        vals = vals.repeat_interleave(groups, dim=1)
+        scores = torch.einsum("qhd,khd->hqk", qmat[q0:q1], keys) * scale
+        qpos = torch.arange(c - n, c, device=q.device)
+        hidden = kpos[None, :] > qpos[:, None]
+        if window > 0:
+            hidden = hidden | (kpos[None, :] <= qpos[:, None] - window)
+        hidden = hidden | (pages < 0)[None, :]
+        scores = scores.masked_fill(hidden[None], float("-inf"))
+        m = scores.amax(-1, keepdim=True)
+        p = torch.exp(scores - m)
+        denom = p.sum(-1, keepdim=True)
+        o = torch.einsum("hqk,khd->qhd", _r(p, dtype), vals) / denom.permute(1, 0, 2)
+        out[q0:q1] = o.reshape(n, heads * head_dim).to(dtype)
+    return out
+
+
+def argmax(logits, out):
+    out.copy_(torch.argmax(logits.float(), dim=-1).to(torch.int32))
+    return out
+
+
+def sample_row(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, uniform: float) -> int:
+    """The sampling kernel's rule for one row (liteinfer/sampling/sampler.py:50-97), in float64 where it sums."""
+    logits = logits.float()
+    if not temperature > 0 or top_k == 1:
+        return int(torch.argmax(logits))
+    x = logits / temperature
+    n = x.numel()
+    order = sorted(range(n), key=lambda i: (-float(x[i]), i))   # descending, equal values by index
+    keep = order[:top_k] if 0 < top_k < n else order
+    w = torch.exp(x - x.max()).double()
+    if 0.0 < top_p < 1.0:
+        total = float(sum(w[i] for i in keep))
+        kept, before = [], 0.0
+        for i in keep:
+            if before > top_p * total:
+                break
+            kept.append(i)
+            before += float(w[i])
+        keep = kept
+    keep = sorted(keep)
+    total = float(sum(w[i] for i in keep))
+    target, run = uniform * total, 0.0
+    for i in keep:
+        run += float(w[i])
+        if run > target:
+            return i
+    return keep[-1]
+
+
+def sample(logits, temperature, top_k, top_p, uniform, out):
+    for r in range(logits.shape[0]):
+        out[r] = sample_row(logits[r], float(temperature[r]), int(top_k[r]), float(top_p[r]), float(uniform[r]))
+    return out
+
+
+ALL = ("embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "linear", "gemm_simt", "rope_kv_write",
+       "paged_attention", "argmax", "sample")
