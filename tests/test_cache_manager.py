@@ -1,0 +1,172 @@
+"""The cache manager's bookkeeping: no page lost, held twice or freed twice, under random orders of requests;
+all-or-nothing reservations; windows give pages back; state slots."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+import torch
+
+from liteinfer_b200.cache.manager import CacheManager
+from liteinfer_b200.cache.pages import CacheExhaustedError, OutOfPagesError, PageAllocator
+from liteinfer_b200.parts.context import KVNeed, StateNeed
+from liteinfer_b200.parts.spec import ScheduleEntry
+
+
+def _manager(needs, schedule=None, page_size=4, num_pages=16, max_requests=4, storage=False):
+    schedule = schedule or tuple(ScheduleEntry(i) for i in range(len(needs)))
+    return CacheManager(needs, schedule, page_size, num_pages, max_requests, torch.float32, "cpu",
+                        allocate_storage=storage)
+
+
+FULL = (KVNeed(2, 8),)
+WINDOW = (KVNeed(2, 8, window=6),)
+
+
+def test_page_allocator_is_lifo_and_strict():
+    pages = PageAllocator(4)
+    a = pages.allocate(3)
+    assert a == [0, 1, 2] and pages.num_free == 1
+    pages.free([1])
+    assert pages.allocate(1) == [1]            # the page given back is the next one handed out
+    with pytest.raises(OutOfPagesError):
+        pages.allocate(2)
+    assert pages.num_free == 1                 # a refused allocation takes nothing
+    pages.free([0])
+    with pytest.raises(ValueError, match="not held"):
+        pages.free([0])
+    with pytest.raises(ValueError, match="does not exist"):
+        pages.free([9])
+
+
+def test_reserve_is_all_or_nothing_across_requests_and_groups():
+    m = _manager([FULL, WINDOW, FULL], num_pages=5)
+    assert len(m.groups) == 2 and m.groups[0].stops == [0, 2] and m.groups[1].stops == [1]
+    m.reserve(["a"], [9])                      # 3 pages in each group
+    m.commit("a", 9)
+    with pytest.raises(OutOfPagesError):
+        m.reserve(["a", "b"], [10, 12])        # b alone needs 3, only 2 free
+    assert not m.has("b") and m.length("a") == 9
+    assert [g.allocator.num_free for g in m.groups] == [2, 3]    # the window group already gave one back
+    m.check_invariants()
+    m.reserve(["a", "b"], [10, 8])
+    m.check_invariants()
+
+
+def test_window_pages_come_back_after_the_window_has_passed():
+    m = _manager([WINDOW], page_size=4, num_pages=4)
+    total = 0
+    for step in range(40):                     # 40 tokens through 4 pages of 4 with a window of 6
+        m.reserve(["a"], [total + 1])
+        total += 1
+        m.commit("a", total)
+        table = m.block_table(0, "a")
+        first_needed = max(0, total - 6 + 1) // 4
+        assert all(p == -1 for p in table[:first_needed]) and all(p >= 0 for p in table[first_needed:])
+        assert m.groups[0].allocator.num_held <= 3
+        m.check_invariants()
+    m.release("a")
+    assert m.groups[0].allocator.num_free == 4
+
+
+def test_a_portion_larger_than_the_window_keeps_what_its_first_query_sees():
+    m = _manager([WINDOW], page_size=4, num_pages=8)
+    m.reserve(["a"], [10]); m.commit("a", 10)
+    held_before = [p for p in m.block_table(0, "a") if p >= 0]
+    m.reserve(["a"], [21])                     # the query at position 10 still reads keys 5..10
+    assert all(p in m.block_table(0, "a") for p in held_before)
+    m.commit("a", 21)
+    assert m.block_table(0, "a")[:4] == [-1, -1, -1, -1]
+
+
+def test_rollback_gives_back_only_the_new_pages():
+    m = _manager([FULL], num_pages=8)
+    m.reserve(["a"], [6]); m.commit("a", 6)
+    m.reserve(["a", "b"], [13, 5])
+    m.rollback(["a", "b"])
+    assert m.length("a") == 6 and len(m.block_table(0, "a")) == 2 and not m.has("b")
+    assert m.groups[0].allocator.num_held == 2 and m.slots.num_held == 1
+    m.check_invariants()
+
+
+def test_state_slots_are_taken_at_admission_zeroed_on_reuse_and_limited():
+    needs = [(StateNeed((3,), "f32"),), FULL]
+    m = _manager(needs, max_requests=2, storage=True)
+    m.reserve(["a", "b"], [1, 1])
+    caches = m.layer_caches()
+    assert caches[0].state.shape == (2, 3) and caches[0].kv is None and caches[1].kv is not None
+    caches[0].state[m.state_slot("a")] = 7.0
+    with pytest.raises(CacheExhaustedError, match="state slots"):
+        m.reserve(["c"], [1])
+    slot = m.state_slot("a")
+    m.release("a")
+    m.reserve(["c"], [1])
+    assert m.state_slot("c") == slot and float(caches[0].state[slot].abs().sum()) == 0.0
+
+
+def test_schedule_may_share_a_cache_and_repeat_a_layer():
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_of=1))
+    m = _manager([FULL, FULL], schedule=schedule, storage=True)
+    assert m.groups[0].stops == [0, 1, 2] and m.groups[0].pool.shape[0] == 3
+    caches = m.layer_caches()
+    assert caches[3].read_only and caches[3].kv.k_pool.data_ptr() == caches[1].kv.k_pool.data_ptr()
+    assert caches[2].kv.k_pool.data_ptr() != caches[0].kv.k_pool.data_ptr()
+
+
+def test_misuse_is_refused():
+    m = _manager([FULL])
+    with pytest.raises(ValueError, match="twice"):
+        m.reserve(["a", "a"], [1, 2])
+    m.reserve(["a"], [5]); m.commit("a", 5)
+    with pytest.raises(ValueError, match="shrink"):
+        m.reserve(["a"], [3])
+    m.release("zzz")                           # releasing an unknown request is a no-op
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_orders_keep_the_books(seed):
+    rng = random.Random(seed)
+    m = _manager([FULL, WINDOW, (StateNeed((2,)),)], page_size=rng.choice([1, 3, 4, 8]),
+                 num_pages=rng.choice([6, 13, 40]), max_requests=4)
+    lengths: dict[str, int] = {}
+    counter = 0
+    for _ in range(400):
+        action = rng.random()
+        if action < 0.25 and len(lengths) < 6:
+            counter += 1
+            ids, totals = [f"r{counter}"], [rng.randint(1, 30)]
+        elif action < 0.8 and lengths:
+            ids = rng.sample(sorted(lengths), rng.randint(1, len(lengths)))
+            totals = [lengths[r] + rng.choice([1, 1, 1, 2, 9]) for r in ids]
+        elif lengths:
+            victim = rng.choice(sorted(lengths))
+            m.release(victim)
+            del lengths[victim]
+            m.check_invariants()
+            continue
+        else:
+            continue
+        before = ([g.allocator.num_free for g in m.groups], m.slots.num_free, dict(lengths))
+        try:
+            m.reserve(ids, totals)
+        except CacheExhaustedError:
+            assert ([g.allocator.num_free for g in m.groups], m.slots.num_free) == before[:2]
+            m.check_invariants()
+            continue
+        if rng.random() < 0.15:                # the step failed after its reservation
+            m.rollback(ids)
+            for r in ids:
+                assert m.length(r) == before[2].get(r, 0)
+        else:
+            for r, t in zip(ids, totals):
+                m.commit(r, t)
+                lengths[r] = t
+        m.check_invariants()
+        for r, t in lengths.items():
+            assert m.length(r) == t
+            full = m.block_table(0, r)
+            assert len(full) == -(-t // m.page_size) and all(p >= 0 for p in full)
+    for r in list(lengths):
+        m.release(r)
+    assert all(g.allocator.num_held == 0 for g in m.groups) and m.slots.num_held == 0

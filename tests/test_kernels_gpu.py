@@ -1,0 +1,278 @@
+"""Each CUDA kernel alone against its plain torch reference (tests/torch_kernels.py), at other sizes
+than the engine's tiny models: widths that are no power of two, head sizes in steps of 16,
+odd group sizes, pages of odd length."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import torch_kernels as ref
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2 ** -7, atol=2 ** -7)
+
+
+def _randn(*shape, dtype, seed=0, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [64, 100, 2048, 3000])
+def test_embedding(dtype, width):
+    from liteinfer_b200 import ops
+
+    table = _randn(777, width, dtype=dtype)
+    ids = torch.tensor([0, 776, 5, 5, 123, 1000, -1], dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.embedding(ids, table, torch.empty(7, width, dtype=dtype, device="cuda"), flag)
+    assert torch.equal(out[:5], table[ids[:5].long()])
+    assert torch.equal(out[5:], torch.zeros_like(out[5:])) and int(flag) == 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [64, 100, 2048, 5000])
+def test_rmsnorm_variants(dtype, width):
+    from liteinfer_b200 import ops
+
+    x = _randn(37, width, dtype=dtype, seed=1, scale=3.0)
+    delta = _randn(37, width, dtype=dtype, seed=2)
+    w = (1 + 0.1 * _randn(width, dtype=torch.float32, seed=3)).to(dtype)
+    rows = torch.tensor([36, 0, 5, 5], dtype=torch.int32, device="cuda")
+    for kwargs in ({}, {"delta": delta, "write_residual": True}, {"delta": delta, "rows": rows}, {"rows": rows}):
+        xa, xb = x.clone(), x.clone()
+        n = 4 if "rows" in kwargs else 37
+        got = ops.rmsnorm(xa, w, 1e-5, torch.empty(n, width, dtype=dtype, device="cuda"), **kwargs)
+        want = ref.rmsnorm(xb, w, 1e-5, torch.empty(n, width, dtype=dtype, device="cuda"), **kwargs)
+        torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
+        torch.testing.assert_close(xa.float(), xb.float(), **_tol(dtype))   # the residual stream moved on (or not)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["silu", "gelu", "gelu_pytorch_tanh", "relu"])
+@pytest.mark.parametrize("width", [176, 100, 8192])
+def test_act_mul(dtype, act, width):
+    from liteinfer_b200 import ops
+
+    gu = _randn(19, 2 * width, dtype=dtype, scale=2.0)
+    got = ops.act_mul(gu, torch.empty(19, width, dtype=dtype, device="cuda"), act)
+    want = ref.act_mul(gu, torch.empty(19, width, dtype=dtype, device="cuda"), act)
+    torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_and_bias(dtype):
+    from liteinfer_b200 import ops
+
+    x, d, b = _randn(9, 100, dtype=dtype), _randn(9, 100, dtype=dtype, seed=5), _randn(100, dtype=dtype, seed=6)
+    torch.testing.assert_close(ops.add_(x.clone(), d).float(), (x.float() + d.float()).to(dtype).float())
+    torch.testing.assert_close(ops.add_bias_(x.clone(), b).float(), (x.float() + b.float()).to(dtype).float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (7, 1000, 96), (130, 100, 50), (64, 128256 // 64, 2048), (3, 5, 7)])
+def test_gemm_simt(dtype, M, N, K):
+    from liteinfer_b200 import ops
+
+    x, w, b = _randn(M, K, dtype=dtype), _randn(N, K, dtype=dtype, seed=1, scale=0.05), _randn(N, dtype=dtype, seed=2)
+    got = ops.gemm_simt(x, w, torch.empty(M, N, dtype=dtype, device="cuda"), b)
+    want = (x.double() @ w.double().t() + b.double())
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2 ** -7, atol=2 ** -7)
+    torch.testing.assert_close(got.double(), want, **tol)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    from liteinfer_b200 import ops
+
+    x, w = _randn(70, 320, dtype=torch.float32), _randn(1000, 320, dtype=torch.float32, seed=1)
+    full = ops.gemm_simt(x, w, torch.empty(70, 1000, device="cuda"))
+    one = ops.gemm_simt(x[33:34].contiguous(), w, torch.empty(1, 1000, device="cuda"))
+    assert torch.equal(full[33:34], one)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 2048, 8192), (64, 1000, 96), (300, 512, 64), (2048, 256, 2048)])
+def test_linear_bfloat16(M, N, K):
+    from liteinfer_b200 import ops
+
+    x, w = _randn(M, K, dtype=torch.bfloat16), _randn(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    got = ops.linear(x, w, torch.empty(M, N, dtype=torch.bfloat16, device="cuda"))
+    want = x.double() @ w.double().t()
+    torch.testing.assert_close(got.double(), want, rtol=2 ** -7, atol=2 ** -7)
+
+
+def _paged_case(dtype, heads, kv_heads, head_dim, page_size, q_lens, ctx_lens, seed=0, poison=True):
+    """Random pool, shuffled pages, sequences with given new-query and context lengths."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(q_lens)
+    pages_per = [-(-c // page_size) for c in ctx_lens]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    width = max(pages_per) + 2
+    table = torch.full((B, width), -1, dtype=torch.int32)
+    at = 0
+    for s, n in enumerate(pages_per):
+        table[s, :n] = torch.tensor(perm[at:at + n], dtype=torch.int32)
+        at += n
+    T = sum(q_lens)
+    row = (heads + 2 * kv_heads) * head_dim
+    qkv = _randn(T, row, dtype=dtype, seed=seed + 1)
+    fill = float("nan") if poison else 0.0
+    k_pool = torch.full((num_pages, kv_heads, page_size, head_dim), fill, dtype=dtype, device="cuda")
+    v_pool = torch.full_like(k_pool, fill)
+    # Earlier tokens of every context: random keys and values written straight into the pages.
+    for s in range(B):
+        old = ctx_lens[s] - q_lens[s]
+        kk = _randn(old, kv_heads, head_dim, dtype=dtype, seed=seed + 10 + s)
+        vv = _randn(old, kv_heads, head_dim, dtype=dtype, seed=seed + 50 + s)
+        for p in range(old):
+            page = int(table[s, p // page_size])
+            k_pool[page, :, p % page_size] = kk[p]
+            v_pool[page, :, p % page_size] = vv[p]
+    qsl = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32, device="cuda")
+    positions = torch.cat([torch.arange(c - q, c) for q, c in zip(q_lens, ctx_lens)]).to(torch.int32).cuda()
+    seq_of = torch.cat([torch.full((q,), s) for s, q in enumerate(q_lens)]).to(torch.int32).cuda()
+    return dict(qkv=qkv, k_pool=k_pool, v_pool=v_pool, table=table.cuda(), qsl=qsl, ctx=ctx, positions=positions,
+                seq_of=seq_of, B=B, T=T)
+
+
+ATTENTION_SHAPES = [  # heads, kv_heads, head_dim, page_size
+    (4, 2, 16, 16), (6, 3, 48, 8), (10, 2, 80, 5), (8, 8, 64, 16), (32, 8, 128, 16), (3, 1, 32, 64), (2, 1, 256, 16),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", ATTENTION_SHAPES)
+@pytest.mark.parametrize("window", [0, 7])
+def test_rope_write_then_attention(dtype, heads, kv_heads, head_dim, page_size, window):
+    """Portions, whole prompts and single tokens in one launch, over shuffled pages with NaN in every unwritten slot."""
+    from liteinfer_b200 import ops
+
+    q_lens, ctx_lens = [1, 40, 1, 7, 33, 2], [90, 60, 3, 7, 33, 65]
+    case = _paged_case(dtype, heads, kv_heads, head_dim, page_size, q_lens, ctx_lens)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, head_dim, 2).float() / head_dim))).cuda()
+    outs = []
+    for impl in (ops, ref):
+        qkv, k_pool, v_pool = case["qkv"].clone(), case["k_pool"].clone(), case["v_pool"].clone()
+        impl.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_pool, v_pool, inv_freq, heads,
+                           kv_heads, head_dim, head_dim)
+        out = torch.empty(case["T"], heads * head_dim, dtype=dtype, device="cuda")
+        impl.paged_attention(qkv, qkv.shape[1], out, k_pool, v_pool, case["table"], case["qsl"], case["ctx"],
+                             case["B"], max(q_lens), heads, kv_heads, head_dim, head_dim ** -0.5, window)
+        outs.append((qkv, k_pool, v_pool, out))
+    for got, want in zip(outs[0], outs[1]):
+        written = ~torch.isnan(want.float())
+        assert torch.equal(torch.isnan(got.float()), ~written)      # nothing written outside the requests' slots
+        torch.testing.assert_close(got.float()[written], want.float()[written], **_tol(dtype))
+    assert torch.isfinite(outs[0][3].float()).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dtype):
+    """One key among hundreds is made to dominate: the output must be that key's value, wherever its page lies."""
+    from liteinfer_b200 import ops
+
+    heads, kv_heads, d, page = 4, 2, 64, 16
+    ctx = 700
+    for far in (0, 15, 16, 333, 698):
+        case = _paged_case(dtype, heads, kv_heads, d, page, [1], [ctx], seed=far, poison=True)
+        qkv, k_pool, v_pool = case["qkv"], case["k_pool"], case["v_pool"]
+        # the new token's own key/value must be in the pool too (position ctx-1)
+        ops.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_pool, v_pool, None, heads,
+                          kv_heads, d, 0)
+        q = qkv[:, :heads * d].view(1, heads, d)
+        pg, off = int(case["table"][0, far // page]), far % page
+        for h in range(kv_heads):
+            k_pool[pg, h, off] = (q[0, h * 2].float() * 8).to(dtype)    # aligned with the first head of the group
+        out = torch.empty(1, heads * d, dtype=dtype, device="cuda")
+        ops.paged_attention(qkv, qkv.shape[1], out, k_pool, v_pool, case["table"], case["qsl"], case["ctx"], 1, 1,
+                            heads, kv_heads, d, 1.0)
+        for h in range(kv_heads):
+            torch.testing.assert_close(out.view(heads, d)[h * 2].float(), v_pool[pg, h, off].float(),
+                                       rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(dtype):
+    """With a window of w the key at distance w-1 is seen and the key at distance w is not."""
+    from liteinfer_b200 import ops
+
+    heads, kv_heads, d, page, w, ctx = 2, 1, 32, 8, 11, 50
+    for distance, seen in ((w - 1, True), (w, False)):
+        case = _paged_case(dtype, heads, kv_heads, d, page, [1], [ctx], seed=3, poison=False)
+        qkv, k_pool, v_pool = case["qkv"], case["k_pool"], case["v_pool"]
+        ops.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_pool, v_pool, None, heads,
+                          kv_heads, d, 0)
+        far = ctx - 1 - distance
+        pg, off = int(case["table"][0, far // page]), far % page
+        k_pool[pg, 0, off] = (qkv[0, :d].float() * 10).to(dtype)
+        v_pool[pg, 0, off] = 100.0
+        out = torch.empty(1, heads * d, dtype=dtype, device="cuda")
+        ops.paged_attention(qkv, qkv.shape[1], out, k_pool, v_pool, case["table"], case["qsl"], case["ctx"], 1, 1,
+                            heads, kv_heads, d, 1.0, w)
+        assert (out[0, :d].float().mean() > 50) == seen
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab", [512, 1000, 128256])
+def test_argmax(dtype, vocab):
+    from liteinfer_b200 import ops
+
+    logits = _randn(5, vocab, dtype=dtype)
+    logits[2, vocab - 1] = 50.0
+    logits[3, 7] = logits[3, 300] = 60.0     # equal values: the lower index wins
+    got = ops.argmax(logits, torch.empty(5, dtype=torch.int32, device="cuda"))
+    want = ref.argmax(logits.cpu(), torch.empty(5, dtype=torch.int32))
+    assert got.cpu().tolist() == want.tolist() and got[2] == vocab - 1 and got[3] == 7
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab", [50, 1000])
+def test_sample_matches_the_rule(dtype, vocab):
+    """Temperature, top-k and top-p, with ties at the boundaries, against the row-by-row rule."""
+    from liteinfer_b200 import ops
+
+    g = torch.Generator().manual_seed(0)
+    rows = 24
+    logits = (torch.randn(rows, vocab, generator=g) * 2).to(dtype)
+    logits[1, 3] = logits[1, 17] = logits[1, 30] = logits[1].float().max() + 1     # ties at the top
+    logits[2] = logits[2].float().round().to(dtype)                               # many ties everywhere
+    temps = torch.tensor([0.0, 1.0, 0.7, 2.5] * 6)
+    top_k = torch.tensor([0, 1, 2, 5, 0, 40, 3, 0, vocab, vocab + 5, 7, 0] * 2, dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.9, 0.5, 1.0, 0.1, 0.95] * 4)
+    for trial in range(4):
+        u = torch.rand(rows, generator=g)
+        got = ops.sample(logits.cuda(), temps.cuda(), top_k.cuda(), top_p.cuda(), u.cuda(),
+                         torch.empty(rows, dtype=torch.int32, device="cuda")).cpu()
+        for r in range(rows):
+            want = ref.sample_row(logits[r], float(temps[r]), int(top_k[r]), float(top_p[r]), float(u[r]))
+            if int(got[r]) != want:
+                # A draw that lands within rounding of a boundary of the running sum may fall either side of it.
+                lo = ref.sample_row(logits[r], float(temps[r]), int(top_k[r]), float(top_p[r]), max(0.0, float(u[r]) - 1e-5))
+                hi = ref.sample_row(logits[r], float(temps[r]), int(top_k[r]), float(top_p[r]), min(0.999999, float(u[r]) + 1e-5))
+                assert int(got[r]) in (lo, hi), f"row {r}: got {int(got[r])}, rule gives {want}"
+
+
+def test_sample_distribution():
+    """Many draws of one row follow softmax(logits / T) restricted to the top-k."""
+    from liteinfer_b200 import ops
+
+    vocab, n = 40, 20000
+    g = torch.Generator().manual_seed(1)
+    row = torch.randn(vocab, generator=g)
+    logits = row.repeat(n, 1).cuda()
+    u = torch.rand(n, generator=g).cuda()
+    got = ops.sample(logits, torch.full((n,), 0.8).cuda(), torch.full((n,), 10, dtype=torch.int32).cuda(),
+                     torch.ones(n).cuda(), u, torch.empty(n, dtype=torch.int32, device="cuda")).cpu()
+    keep = torch.topk(row, 10).indices
+    p = torch.zeros(vocab)
+    p[keep] = torch.softmax(row[keep] / 0.8, -1)
+    freq = torch.bincount(got.long(), minlength=vocab).float() / n
+    assert float((freq - p).abs().max()) < 0.015
+    assert set(got.tolist()) <= set(keep.tolist())
