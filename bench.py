@@ -1,0 +1,265 @@
+"""Headline benchmark: decode tokens/s of the Llama 3.2 1B shape on one B200, with prefill and roofline figures.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 with every
+sequence near the benchmark context (4,096), timed on the device over K decode
+steps of the engine's own step function and sampler.  `e2e` is the same measured
+through the Python entry point (`LLM.generate`: host token ids in, host token
+ids out, one host-to-device copy of the step's inputs and one device-to-host read
+of the sampled tokens every step).  `prefill` times one 2,048-token prompt,
+`roofline` relates the decode step to the bytes it must read, `points` holds
+decode at batch 1 and 64.  Weights are random (seeded) and token ids synthetic.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "vocab_size": 128256, "hidden_size": 2048, "intermediate_size": 8192,
+    "num_hidden_layers": 16, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": True, "max_position_embeddings": 131072, "hidden_act": "silu",
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE = 16
+# A40 decode step of the reference at batch 8 (docs/benchmarks.md:749-753: 6.41 ms -> 1,248 tok/s).
+BASELINE_DECODE_B8_TOKS = 1248.0
+
+
+def measured_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        raw = json.loads(path.read_text())
+        return {"hbm_gbs": float(raw.get("hbm_gbs", 6650.0)),
+                "bf16_tflops": float(raw.get("bf16_tflops_sustained", raw.get("bf16_tflops", 1590.0))),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.samples: list[list[str]] = []
+        self._proc = None
+
+    def start(self) -> None:
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self._proc = None
+
+    def _read(self) -> None:
+        for line in self._proc.stdout:
+            self.samples.append([f.strip() for f in line.split(",")])
+
+    def stop(self) -> dict:
+        if self._proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self._proc.terminate()
+        rows = [s for s in self.samples if len(s) >= 6 and s[0].isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": statistics.median(int(r[0]) for r in rows), "sm_max_mhz": int(rows[0][1]),
+                "reasons": reasons, "samples": len(rows)}
+
+
+def _fill_cache(runner, ids: list[str], lengths: list[int]) -> None:
+    """Gives every request `length` tokens of cache without computing them: pages are taken through the
+    cache manager and hold small random values (a decode step's time does not depend on what they are)."""
+    runner.cache.reserve(ids, lengths)
+    for request_id, n in zip(ids, lengths):
+        runner.cache.commit(request_id, n)
+
+
+def _decode_rate(runner, sampler, params, batch: int, start_len: int, steps: int, warmup: int, vocab: int):
+    """(tokens/s, ms per step, launches of own kernels per step) of `steps` decode steps at `batch`."""
+    import torch
+
+    from liteinfer_b200.engine.runner import StepEntry
+    from liteinfer_b200.ops import kernels
+
+    ids = [f"b{batch}-{i}" for i in range(batch)]
+    _fill_cache(runner, ids, [start_len] * batch)
+    g = torch.Generator().manual_seed(batch)
+    tokens = torch.randint(0, vocab, (batch,), generator=g).tolist()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    for i in range(warmup + steps):
+        if i == warmup:
+            torch.cuda.synchronize()
+            launches = kernels.launch_count + getattr(runner, "graph_launches", 0)
+            start.record()
+        logits = runner.step([StepEntry(r, [t], (0,)) for r, t in zip(ids, tokens)])
+        sampled = sampler(logits, [params] * batch, ids)
+        tokens = sampled.tolist()
+    stop.record()
+    torch.cuda.synchronize()
+    launches = kernels.launch_count + getattr(runner, "graph_launches", 0) - launches
+    ms = start.elapsed_time(stop) / steps
+    for r in ids:
+        runner.release(r)
+    return batch / ms * 1e3, ms, launches // steps
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from liteinfer_b200 import LLM, SamplingParams
+    from liteinfer_b200.engine.runner import StepEntry
+    from liteinfer_b200.ops import kernels
+    from liteinfer_b200.sampling.sampler import Sampler
+    from liteinfer_b200.weights.random_init import write_random_model
+
+    cfg = dict(LLAMA_1B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    peaks = measured_peaks()
+    steps, warmup, batch = args.steps, max(3, args.warmup), 8
+    greedy = SamplingParams(temperature=0.0, max_tokens=warmup + steps + 1, ignore_eos=True)
+
+    with tempfile.TemporaryDirectory() as tmp:
+        model_dir = write_random_model(cfg, Path(tmp) / "llama-1b", seed=0)
+        decode_start = CONTEXT - (warmup + steps) - 1
+        llm = LLM(str(model_dir), dtype="bfloat16", device="cuda:0", max_num_seqs=64, max_model_len=CONTEXT + 1,
+                  block_size=PAGE, max_num_batched_tokens=8192, gpu_memory_utilization=0.5)
+        runner = llm.engine.runner
+        model = runner.model
+        for group in runner.cache.groups:                      # random cache contents
+            group.pool.normal_(0.0, 0.5)
+        vocab, hidden = cfg["vocab_size"], cfg["hidden_size"]
+        sampler = Sampler(0)
+
+        # ---- prefill: one prompt of 2,048 tokens, logits at its last token
+        g = torch.Generator().manual_seed(7)
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+        times = []
+        for i in range(3 + 3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            runner.step([StepEntry("prefill", prompt, (PREFILL_TOKENS - 1,))])
+            b.record()
+            torch.cuda.synchronize()
+            runner.release("prefill")
+            if i >= 3:
+                times.append(a.elapsed_time(b))
+        prefill_ms = statistics.median(times)
+        layers = cfg["num_hidden_layers"]
+        q, kv, inter = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"], cfg["intermediate_size"]
+        linear_params = layers * (hidden * (q + 2 * kv) + q * hidden + 3 * hidden * inter)
+        attn_flops = layers * 4 * cfg["num_attention_heads"] * cfg["head_dim"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) / 2
+        prefill_flops = 2 * linear_params * PREFILL_TOKENS + attn_flops + 2 * hidden * vocab
+        prefill = {"value": PREFILL_TOKENS / prefill_ms * 1e3, "tokens": PREFILL_TOKENS, "ms": prefill_ms,
+                   "frac": prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
+
+        # ---- decode, device-timed
+        clocks = ClockSampler()
+        clocks.start()
+        value, ms, launches = _decode_rate(runner, sampler, greedy, batch, decode_start, steps, warmup, vocab)
+        clock_record = clocks.stop()
+        b1, _, _ = _decode_rate(runner, sampler, greedy, 1, decode_start, steps, warmup, vocab)
+        b64, _, _ = _decode_rate(runner, sampler, greedy, 64, decode_start, steps, warmup, vocab)
+
+        # ---- roofline of the batch-8 decode step: every weight once, plus the live requests' cache
+        element = 2
+        weight_bytes = (linear_params + hidden * vocab + (2 * layers + 1) * hidden) * element
+        mean_ctx = decode_start + warmup + steps / 2
+        kv_bytes = batch * mean_ctx * layers * 2 * kv * element
+        achieved = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / peaks["hbm_gbs"], "of": peaks["source"]}
+
+        # ---- end to end through LLM.generate: host ids in, host ids out
+        prompts = [torch.randint(0, vocab, (decode_start,), generator=g).tolist() for _ in range(batch)]
+        llm.stats.steps.clear()
+        outs = llm.generate(prompts, greedy)
+        assert all(len(o.token_ids) == warmup + steps + 1 for o in outs)
+        decode_steps = [s for s in llm.stats.steps if s.phase == "decode" and s.num_seqs == batch][-steps:]
+        e2e_ms = sum(s.wall_time_s for s in decode_steps) / len(decode_steps) * 1e3
+        pages = -(-CONTEXT // PAGE)
+        e2e = {"value": batch / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": 4 * (3 * batch + (batch + 1) + 3 * batch + batch * pages),
+               "d2h_bytes_per_step": 4 * batch}
+        llm.close()
+
+    return {
+        "metric": "decode tok/s at batch 8 (Llama 3.2 1B shape)", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": value / BASELINE_DECODE_B8_TOKS, "dtype": "bf16", "data": "synthetic ids, random weights",
+        "impl": "ours",
+        "config": {"model": "llama-3.2-1b-shape", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+                   "hidden": hidden, "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": inter, "vocab": vocab, "global_batch": batch,
+                   "seq_len": CONTEXT, "page_size": PAGE, "parallelism": "single-gpu",
+                   "l2": "inputs larger than L2 (weights 2.5 GB + cache read every step)",
+                   "baseline": "reference A40 batch-8 decode, 1248 tok/s"},
+        "clocks": clock_record, "e2e": e2e, "gpu_launches": launches * steps,
+        "prefill": prefill, "roofline": roofline, "points": {"decode_b1": b1, "decode_b64": b64},
+    }
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference through its own public API, if `baseline/_ref` holds an install of it.
+
+    The one offline install (`pip install --no-index --no-build-isolation --find-links /opt/wheelhouse
+    --target baseline/_ref <reference>`) fails where this was built: the reference's build backend,
+    hatchling, is neither installed nor in the wheelhouse.  Without an install the arm is unavailable.
+    """
+    if not (ROOT / "baseline" / "_ref" / "liteinfer").is_dir():
+        return {"impl": "reference", "unavailable": "reference not installed: its build backend hatchling is "
+                "missing from the offline wheelhouse, so pip cannot build it (--no-deps does not help)"}
+    try:
+        sys.path.insert(0, str(ROOT / "baseline"))
+        from reference_arm import run  # noqa: PLC0415
+        return run(args, LLAMA_1B, CONTEXT, PAGE)
+    except Exception as error:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"{type(error).__name__}: {str(error)[:200]}"}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print("liteinfer_b200 is a single-GPU engine: bench.py runs at --gpus 1 only")
+        return 2
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,363 @@
+// Paged attention on tensor cores for bfloat16, head sizes 64 and 128: whole
+// prompts, portions of prompts and single decoded tokens, with the keys of one
+// sequence optionally split over several blocks (decode at small batch), plus the
+// kernel that merges the splits.
+//
+// Rule as in attention_generic.cu (liteinfer/models/attention.py:24-27,69-84): a
+// sequence's queries are the last q_len positions of its context; query head h
+// reads KV head h / groups.  A block owns a tile of 64 rows for one KV head, a
+// row being (query token, head of the group): grouped heads share every K/V
+// tile that is loaded (liteinfer/models/paged_kernels.py:291-371 packs the group
+// into its query rows the same way).  Scores, running maximum and sum, the
+// accumulator, split partials and their log-sum-exp are 32-bit; probabilities
+// are rounded to bfloat16 for P.V (paged_kernels.py:282-284).
+//
+// Data path: K and V tiles of 64 keys are gathered page by page with cp.async
+// into swizzled shared memory, double buffered; fragments come from ldmatrix;
+// the products are mma.sync m16n8k16 (bf16 in, f32 out).  Keys outside the
+// visible range are zero-filled in shared memory and masked to -inf, so an
+// unwritten page cannot leak.
+#include "common.cuh"
+
+namespace li {
+
+constexpr int kBlockM = 64;   // rows (query token x head in group) per block
+constexpr int kBlockN = 64;   // keys per tile
+constexpr int kWarps = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+  const bf16* q;
+  int q_row_stride;
+  bf16* out;
+  int out_row_stride;
+  const bf16* k_pool;
+  const bf16* v_pool;
+  const int* block_table;
+  int table_stride;
+  const int* query_start_loc;
+  const int* context_lens;
+  const int* seq_index;   // optional: batch row of each launched sequence
+  int heads, kv_heads, page_size, num_pages;
+  float scale_log2;       // scale * log2(e)
+  int window;
+  int num_splits;
+  float* partial_out;     // [tokens * heads * splits, D] when num_splits > 1
+  float* partial_lse;     // [tokens * heads * splits]
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;   // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Tile [rows][D] of bf16 in shared memory; the 16-byte chunk c of row r lives at chunk c ^ (r & 7).
+template <int D> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
+  return base + row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+template <int D>
+__device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParams& p, const int* table, int kvh,
+                                             int tile_start, int lo, int hi) {
+  constexpr int kChunks = D / 8;
+  for (int c = threadIdx.x; c < kBlockN * kChunks; c += kWarps * 32) {
+    const int key = c / kChunks, chunk = c % kChunks;
+    const int kpos = tile_start + key;
+    bool valid = kpos >= lo && kpos < hi;
+    size_t off = 0;
+    if (valid) {
+      const int page = table[kpos / p.page_size];
+      valid = page >= 0 && page < p.num_pages;
+      if (valid) off = (((size_t)page * p.kv_heads + kvh) * p.page_size + kpos % p.page_size) * D + chunk * 8;
+    }
+    cp_async16(tile_ptr<D>(ks, key, chunk), p.k_pool + off, valid);
+    cp_async16(tile_ptr<D>(vs, key, chunk), p.v_pool + off, valid);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kWarps * 32)
+attention_mma_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);           // [64][D]
+  bf16* kbuf = qs + kBlockM * D;                          // 2 x [64][D]
+  bf16* vbuf = kbuf + 2 * kBlockN * D;                    // 2 x [64][D]
+
+  const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
+  const int kvh = blockIdx.y;
+  const int split = blockIdx.x % p.num_splits, qtile = blockIdx.x / p.num_splits;
+  const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
+  const int groups = p.heads / p.kv_heads;
+  const int tq = kBlockM / groups;                        // query tokens per tile
+  const int q0 = qtile * tq;
+  if (q0 >= q_len) return;
+  const int ctx = p.context_lens[seq];
+  const int tile_q = min(tq, q_len - q0);
+  const int rows_used = tile_q * groups;
+  const int* table = p.block_table + (size_t)seq * p.table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  constexpr int kChunks = D / 8;
+
+  // Visible keys of this tile: [lo, hi).
+  const int first_qpos = ctx - q_len + q0, last_qpos = first_qpos + tile_q - 1;
+  const int hi = last_qpos + 1;
+  const int lo = (p.window > 0 && first_qpos - p.window + 1 > 0) ? first_qpos - p.window + 1 : 0;
+  const int tile_lo = lo / kBlockN, tile_hi = (hi + kBlockN - 1) / kBlockN;   // key tiles [tile_lo, tile_hi)
+  const int ntiles = tile_hi - tile_lo;
+  const int per_split = (ntiles + p.num_splits - 1) / p.num_splits;
+  const int my_lo = tile_lo + split * per_split, my_hi = min(tile_hi, my_lo + per_split);
+
+  // ---- Q tile -> shared (zero rows beyond rows_used), then A fragments in registers.
+  for (int c = threadIdx.x; c < kBlockM * kChunks; c += kWarps * 32) {
+    const int row = c / kChunks, chunk = c % kChunks;
+    const bool valid = row < rows_used;
+    const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+    const bf16* src = p.q + (valid ? (size_t)(q_begin + qi) * p.q_row_stride + (size_t)head * D + chunk * 8 : 0);
+    cp_async16(tile_ptr<D>(qs, row, chunk), src, valid);
+  }
+  cp_async_commit();
+  if (my_lo < my_hi) load_kv_tile<D>(kbuf, vbuf, p, table, kvh, my_lo * kBlockN, lo, hi);
+  cp_async_commit();
+  cp_async_wait<1>();
+  __syncthreads();
+
+  unsigned qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk)
+    ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3],
+                tile_ptr<D>(qs, warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
+
+  // Rows of this thread: warp*16 + g and + 8.
+  int qpos[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = warp * 16 + g + 8 * h;
+    qpos[h] = row < rows_used ? first_qpos + row / groups : -1;   // -1: a padding row sees nothing
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+
+  for (int tile = my_lo; tile < my_hi; ++tile) {
+    const int buf = (tile - my_lo) & 1;
+    bf16* ks = kbuf + buf * kBlockN * D;
+    bf16* vs = vbuf + buf * kBlockN * D;
+    if (tile + 1 < my_hi)
+      load_kv_tile<D>(kbuf + (buf ^ 1) * kBlockN * D, vbuf + (buf ^ 1) * kBlockN * D, p, table, kvh,
+                      (tile + 1) * kBlockN, lo, hi);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    // S = Q K^T for 16 rows x 64 keys.
+    float s[kBlockN / 8][4];
+#pragma unroll
+    for (int i = 0; i < kBlockN / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int nn = 0; nn < kBlockN / 16; ++nn) {
+        unsigned b0, b1, b2, b3;
+        const int mtx = lane >> 3;
+        ldmatrix_x4(b0, b1, b2, b3, tile_ptr<D>(ks, nn * 16 + (mtx >> 1) * 8 + (lane & 7), kk * 2 + (mtx & 1)));
+        mma_bf16(s[nn * 2], qf[kk], b0, b1);
+        mma_bf16(s[nn * 2 + 1], qf[kk], b2, b3);
+      }
+    }
+
+    // Scale, mask, online softmax.
+    const int key0 = tile * kBlockN;
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < kBlockN / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kpos = key0 + i * 8 + 2 * t + (j & 1);
+        const int qp = qpos[j >> 1];
+        const bool visible = kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
+        s[i][j] = visible ? s[i][j] * p.scale_log2 : -INFINITY;
+        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], s[i][j]);
+      }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+      const float m_new = fmaxf(m[h], tile_max[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[h] = exp2f(m[h] - m_use[h]);   // m = -inf gives 0
+      m[h] = m_new;
+    }
+    float row_sum[2] = {0.f, 0.f};
+    unsigned pf[kBlockN / 16][4];
+#pragma unroll
+    for (int i = 0; i < kBlockN / 8; ++i) {
+      float e[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        e[j] = exp2f(s[i][j] - m_use[j >> 1]);
+        row_sum[j >> 1] += e[j];
+      }
+      pf[i >> 1][(i & 1) * 2] = pack_bf16(e[0], e[1]);
+      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(e[2], e[3]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l[h] = l[h] * alpha[h] + row_sum[h];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+
+    // O += P V.
+#pragma unroll
+    for (int kb = 0; kb < kBlockN / 16; ++kb) {
+#pragma unroll
+      for (int dd = 0; dd < D / 16; ++dd) {
+        unsigned b0, b1, b2, b3;
+        const int mtx = lane >> 3;
+        ldmatrix_x4_trans(b0, b1, b2, b3, tile_ptr<D>(vs, kb * 16 + (mtx & 1) * 8 + (lane & 7), dd * 2 + (mtx >> 1)));
+        mma_bf16(o[dd * 2], pf[kb], b0, b1);
+        mma_bf16(o[dd * 2 + 1], pf[kb], b2, b3);
+      }
+    }
+    __syncthreads();   // this buffer is overwritten by the load issued in the next iteration
+  }
+  cp_async_wait<0>();
+
+  // ---- finish: row sums across the quad, normalise, store.
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = warp * 16 + g + 8 * h;
+    if (row >= rows_used) continue;
+    const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+    const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+    if (p.num_splits == 1) {
+      bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<unsigned*>(dst + i * 8 + 2 * t) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+    } else {
+      const size_t slot = ((size_t)(q_begin + qi) * p.heads + head) * p.num_splits + split;
+      float* dst = p.partial_out + slot * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<float2*>(dst + i * 8 + 2 * t) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      // log-sum-exp in base 2 of the scaled scores; -inf marks a split that saw no key
+      if (t == 0) p.partial_lse[slot] = l[h] > 0.f ? m[h] + log2f(l[h]) : -INFINITY;
+    }
+  }
+}
+
+// out[token, head] = sum_s w_s * partial[token, head, s], w_s = 2^(lse_s - max) / sum.
+template <int D>
+__global__ void combine_splits_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
+                                      bf16* __restrict__ out, int out_row_stride, const int* __restrict__ token_index,
+                                      int heads, int num_splits) {
+  const int token = token_index ? token_index[blockIdx.x] : blockIdx.x;
+  const int head = blockIdx.y;
+  const size_t base = ((size_t)token * heads + head) * num_splits;
+  float mx = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, partial_lse[base + s]);
+  float denom = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float v = partial_lse[base + s];
+    denom += v == -INFINITY ? 0.f : exp2f(v - mx);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float v = partial_lse[base + s];
+      if (v == -INFINITY) continue;
+      acc += exp2f(v - mx) * partial_out[(base + s) * D + d];
+    }
+    out[(size_t)token * out_row_stride + (size_t)head * D + d] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
+  }
+}
+
+template <int D>
+int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, const int* token_index, int num_tokens,
+                     cudaStream_t stream) {
+  const int groups = p.heads / p.kv_heads;
+  const int tq = kBlockM / groups;
+  const size_t smem = (size_t)(kBlockM + 4 * kBlockN) * D * sizeof(bf16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const dim3 grid(((max_q_len + tq - 1) / tq) * p.num_splits, p.kv_heads, num_seqs);
+  attention_mma_kernel<D><<<grid, kWarps * 32, smem, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (p.num_splits > 1) {
+    combine_splits_kernel<D><<<dim3(num_tokens, p.heads), D / 2 < 32 ? 32 : D / 2, 0, stream>>>(
+        p.partial_out, p.partial_lse, p.out, p.out_row_stride, token_index, p.heads, p.num_splits);
+  }
+  LI_LAUNCH_CHECK();
+}
+
+}  // namespace li
+
+using namespace li;
+
+// Tensor-core paged attention (bfloat16; head_dim 64 or 128; groups dividing into 64 rows).
+// seq_index (optional, [num_seqs]): the batch rows to run, so that a mixed step can send its
+// single-token sequences through a split launch and the others through an unsplit one.
+// num_splits > 1 needs partial_out [tokens*heads*splits, head_dim] and partial_lse
+// [tokens*heads*splits] (float32) and token_index/num_tokens: the token rows to merge.
+LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                     const void* k_pool, const void* v_pool, const int* block_table,
+                                     int table_stride, const int* query_start_loc, const int* context_lens,
+                                     const int* seq_index, int num_seqs, int max_q_len, int heads, int kv_heads,
+                                     int head_dim, int page_size, int num_pages, float scale, int window,
+                                     int num_splits, float* partial_out, float* partial_lse,
+                                     const int* token_index, int num_tokens, cudaStream_t stream) {
+  if (num_seqs == 0 || max_q_len == 0) return 0;
+  if (kv_heads < 1 || heads % kv_heads) return LI_ERR_UNSUPPORTED;
+  const int groups = heads / kv_heads;
+  if (groups > kBlockM || (head_dim != 64 && head_dim != 128)) return LI_ERR_UNSUPPORTED;
+  if (kv_heads > 65535 || num_seqs > 65535 || num_splits < 1) return LI_ERR_UNSUPPORTED;
+  if (num_splits > 1 && (!partial_out || !partial_lse)) return LI_ERR_UNSUPPORTED;
+  if ((q_row_stride % 8) || (out_row_stride % 2) || !aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool))
+    return LI_ERR_ALIGNMENT;
+  AttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
+               block_table, table_stride, query_start_loc, context_lens, seq_index, heads, kv_heads, page_size,
+               num_pages, scale * kLog2e, window, num_splits, partial_out, partial_lse};
+  return head_dim == 64 ? launch_attention<64>(p, num_seqs, max_q_len, token_index, num_tokens, stream)
+                        : launch_attention<128>(p, num_seqs, max_q_len, token_index, num_tokens, stream);
+}

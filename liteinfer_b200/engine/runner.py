@@ -11,6 +11,12 @@ has the same contract on `Sequence` objects and returns one row per sequence;
 here the batch is plain token ids so that the scheduler's engine and the
 trace-replay program drive the very same function, and rows are computed only
 where `want` asks.
+
+A step that holds only single decoded tokens, each wanting its logits, can be
+replayed from a CUDA graph (one graph per batch width, captured on first use,
+as liteinfer/engine/cuda_graphs.py:105-260 does): the batch is then written
+into buffers of fixed size and place, and the kernels read their bounds from
+those buffers.
 """
 
 from __future__ import annotations
@@ -22,8 +28,11 @@ import numpy as np
 import torch
 
 from liteinfer_b200.cache.manager import CacheManager
-from liteinfer_b200.parts.context import StepContext
+from liteinfer_b200.ops import kernels
+from liteinfer_b200.parts.context import AttentionPlan, StepContext
 from liteinfer_b200.parts.model import Model
+
+_MAX_GRAPHS = 128   # liteinfer/engine/cuda_graphs.py:68
 
 
 @dataclass
@@ -35,6 +44,107 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=tuple)
 
 
+class _Batch:
+    """Where each array of a step lies in the one int32 staging buffer."""
+
+    def __init__(self, B: int, T: int, R: int, widths: list[int], n_decode: int, n_prefill: int) -> None:
+        self.B, self.T, self.R, self.widths = B, T, R, widths
+        self.n_decode, self.n_prefill = n_decode, n_prefill
+        sizes = [T, T, T, B + 1, B, B, R, n_decode, n_decode, n_prefill] + [B * w for w in widths]
+        # Every array starts on a 16-byte boundary.
+        self.sizes = sizes
+        self.offsets = []
+        at = 0
+        for n in sizes:
+            self.offsets.append(at)
+            at += -(-n // 4) * 4
+        self.total = max(at, 4)
+
+    def views(self, flat):
+        """The arrays as slices of `flat` (a numpy array or a tensor)."""
+        return [flat[o:o + n] for o, n in zip(self.offsets, self.sizes)]
+
+
+def _fill(batch: _Batch, flat: np.ndarray, entries: list[StepEntry], cache: CacheManager,
+          starts: list[int]) -> None:
+    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = batch.views(flat)
+    cursor = row_cursor = nd = npf = 0
+    qsl[0] = 0
+    for i, entry in enumerate(entries):
+        n = len(entry.tokens)
+        tok[cursor:cursor + n] = entry.tokens
+        pos[cursor:cursor + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
+        seq[cursor:cursor + n] = i
+        for place in entry.want:
+            rows[row_cursor] = cursor + place
+            row_cursor += 1
+        if n == 1:
+            dseq[nd], dtok[nd] = i, cursor
+            nd += 1
+        else:
+            pseq[npf] = i
+            npf += 1
+        cursor += n
+        qsl[i + 1] = cursor
+        ctxl[i] = starts[i] + n
+        slots[i] = cache.state_slot(entry.request_id)
+    for g, width in enumerate(batch.widths):
+        if not width:
+            continue
+        table = tables[g].reshape(batch.B, width)
+        table.fill(-1)
+        for i, entry in enumerate(entries):
+            blocks = cache.block_table(g, entry.request_id)
+            table[i, :len(blocks)] = blocks
+
+
+def _context(batch: _Batch, dev: torch.Tensor, device, counts, totals, decode_splits, decode_bound) -> StepContext:
+    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = batch.views(dev)
+    B = batch.B
+    tables = [t.view(B, w) if w else torch.full((B, 1), -1, dtype=torch.int32, device=device)
+              for t, w in zip(tables, batch.widths)]
+    prefill_lens = [c for c in counts if c > 1]
+    plan = AttentionPlan(
+        num_decode=batch.n_decode, decode_seqs=dseq, decode_tokens=dtok, num_prefill=batch.n_prefill,
+        prefill_seqs=pseq, max_prefill_query_len=max(prefill_lens, default=0), max_decode_context_len=decode_bound)
+    return StepContext(
+        num_tokens=batch.T, num_seqs=B, token_ids=tok, positions=pos, seq_of_token=seq, query_start_loc=qsl,
+        context_lens=ctxl, block_tables=tables, state_slots=slots, logit_rows=rows, num_logit_rows=batch.R,
+        max_query_len=max(counts), max_context_len=max(totals), query_lens=tuple(counts),
+        host_context_lens=tuple(totals), decode_splits=decode_splits, plan=plan)
+
+
+class _DecodeGraph:
+    """One captured decode forward for exactly `width` sequences."""
+
+    def __init__(self, runner: ModelRunner, width: int, max_model_len: int) -> None:
+        cache = runner.cache
+        pages = -(-max_model_len // cache.page_size)
+        self.batch = _Batch(width, width, width, [pages] * len(cache.groups), width, 0)
+        self.host = torch.empty(self.batch.total, dtype=torch.int32, pin_memory=True)
+        self.device_buffer = torch.zeros(self.batch.total, dtype=torch.int32, device=runner.device)
+        counts, totals = [1] * width, [max_model_len] * width
+        self.ctx = _context(self.batch, self.device_buffer, runner.device, counts, totals, runner.decode_splits,
+                            max_model_len)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.launches = 0
+
+    def capture(self, runner: ModelRunner) -> None:
+        """Called with the buffers holding a real batch: one eager pass on a side stream, then the capture."""
+        stream = torch.cuda.Stream(device=runner.device)
+        stream.wait_stream(torch.cuda.current_stream(runner.device))
+        with torch.cuda.stream(stream):
+            runner.model.forward(self.ctx, runner.layer_caches)
+        torch.cuda.current_stream(runner.device).wait_stream(stream)
+        torch.cuda.synchronize(runner.device)
+        before = kernels.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=runner.graph_pool):
+            self.logits = runner.model.forward(self.ctx, runner.layer_caches)
+        self.launches = kernels.launch_count - before
+
+
 class ModelRunner:
     def __init__(self, model: Model, cache: CacheManager, decode_splits: int | None = None) -> None:
         self.model, self.cache = model, cache
@@ -43,6 +153,11 @@ class ModelRunner:
         self.layer_caches = cache.layer_caches()
         self._pinned = self.device.type == "cuda"
         self.num_steps = 0
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graph_limits: tuple[int, int] | None = None
+        self.graph_pool = None
+        self.graph_launches = 0     # launches of this package's kernels replayed from graphs
+        self.graph_replays = 0
 
     # ---------------------------------------------------------------- batch
     def _validate(self, entries: list[StepEntry]) -> None:
@@ -69,49 +184,50 @@ class ModelRunner:
         starts = [cache.length(e.request_id) for e in entries]
         counts = [len(e.tokens) for e in entries]
         totals = [s + c for s, c in zip(starts, counts)]
-        B, T = len(entries), sum(counts)
-        R = sum(len(e.want) for e in entries)
         widths = [max(len(cache.block_table(g, e.request_id)) for e in entries) for g in range(len(cache.groups))]
-
-        sizes = [T, T, T, B + 1, B, B, R] + [B * w for w in widths]
-        offsets = np.concatenate(([0], np.cumsum(sizes)))
-        host = torch.empty(int(offsets[-1]), dtype=torch.int32, pin_memory=self._pinned)
-        flat = host.numpy()
-        tok, pos, seq, qsl, ctxl, slots, rows = (flat[offsets[i]:offsets[i + 1]] for i in range(7))
-        cursor = 0
-        row_cursor = 0
-        qsl[0] = 0
-        for i, entry in enumerate(entries):
-            n = counts[i]
-            tok[cursor:cursor + n] = entry.tokens
-            pos[cursor:cursor + n] = np.arange(starts[i], totals[i], dtype=np.int32)
-            seq[cursor:cursor + n] = i
-            for place in entry.want:
-                rows[row_cursor] = cursor + place
-                row_cursor += 1
-            cursor += n
-            qsl[i + 1] = cursor
-            ctxl[i] = totals[i]
-            slots[i] = cache.state_slot(entry.request_id)
-        for g, width in enumerate(widths):
-            table = flat[offsets[7 + g]:offsets[8 + g]].reshape(B, width) if width else None
-            if table is None:
-                continue
-            table.fill(-1)
-            for i, entry in enumerate(entries):
-                blocks = cache.block_table(g, entry.request_id)
-                table[i, :len(blocks)] = blocks
-
+        n_decode = sum(1 for c in counts if c == 1)
+        batch = _Batch(len(entries), sum(counts), sum(len(e.want) for e in entries), widths, n_decode,
+                       len(entries) - n_decode)
+        host = torch.empty(batch.total, dtype=torch.int32, pin_memory=self._pinned)
+        _fill(batch, host.numpy(), entries, cache, starts)
         dev = host.to(self.device, non_blocking=True)
-        part = [dev[int(offsets[i]):int(offsets[i + 1])] for i in range(len(sizes))]
-        tables = [part[7 + g].view(B, widths[g]) if widths[g] else
-                  torch.full((B, 1), -1, dtype=torch.int32, device=self.device) for g in range(len(widths))]
-        return StepContext(
-            num_tokens=T, num_seqs=B, token_ids=part[0], positions=part[1], seq_of_token=part[2],
-            query_start_loc=part[3], context_lens=part[4], block_tables=tables, state_slots=part[5],
-            logit_rows=part[6], num_logit_rows=R, max_query_len=max(counts), max_context_len=max(totals),
-            query_lens=tuple(counts), host_context_lens=tuple(totals), decode_splits=self.decode_splits,
-        )
+        decode_bound = max((t for t, c in zip(totals, counts) if c == 1), default=0)
+        return _context(batch, dev, self.device, counts, totals, self.decode_splits, decode_bound)
+
+    # --------------------------------------------------------------- graphs
+    def enable_decode_graphs(self, max_num_seqs: int, max_model_len: int) -> None:
+        """Replay steps that hold single decoded tokens only from CUDA graphs."""
+        if self.device.type != "cuda":
+            raise ValueError("CUDA graphs need a CUDA device")
+        self._graph_limits = (max_num_seqs, max_model_len)
+        self.graph_pool = torch.cuda.graph_pool_handle()
+
+    def _graph_for(self, entries: list[StepEntry], totals: list[int]) -> _DecodeGraph | None:
+        if self._graph_limits is None:
+            return None
+        max_seqs, max_len = self._graph_limits
+        width = len(entries)
+        if width > max_seqs or max(totals) > max_len:
+            return None
+        if any(len(e.tokens) != 1 or tuple(e.want) != (0,) for e in entries):
+            return None
+        graph = self._graphs.get(width)
+        if graph is None:
+            if len(self._graphs) >= _MAX_GRAPHS:
+                return None
+            graph = self._graphs[width] = _DecodeGraph(self, width, max_len)
+        return graph
+
+    def _replay(self, graph: _DecodeGraph, entries: list[StepEntry]) -> torch.Tensor:
+        starts = [self.cache.length(e.request_id) for e in entries]
+        _fill(graph.batch, graph.host.numpy(), entries, self.cache, starts)
+        graph.device_buffer.copy_(graph.host, non_blocking=True)
+        if graph.graph is None:
+            graph.capture(self)
+        graph.graph.replay()
+        self.graph_launches += graph.launches
+        self.graph_replays += 1
+        return graph.logits.clone()
 
     # ----------------------------------------------------------------- step
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
@@ -121,8 +237,11 @@ class ModelRunner:
         totals = [self.cache.length(e.request_id) + len(e.tokens) for e in entries]
         self.cache.reserve(ids, totals)   # raises before anything changes
         try:
-            ctx = self.build_context(entries)
-            logits = self.model.forward(ctx, self.layer_caches)
+            graph = self._graph_for(entries, totals)
+            if graph is not None:
+                logits = self._replay(graph, entries)
+            else:
+                logits = self.model.forward(self.build_context(entries), self.layer_caches)
         except BaseException:
             self.cache.rollback(ids)
             raise
@@ -130,10 +249,6 @@ class ModelRunner:
             self.cache.commit(request_id, total)
         self.num_steps += 1
         return logits
-
-    def enable_decode_graphs(self, max_num_seqs: int, max_model_len: int) -> None:
-        """Replay steps that hold single decoded tokens only from CUDA graphs."""
-        self._graphs_wanted = (max_num_seqs, max_model_len)
 
     def release(self, request_id: str) -> None:
         """The request is finished: what it holds is given back."""

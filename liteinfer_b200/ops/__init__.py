@@ -7,9 +7,14 @@ from liteinfer_b200.ops.kernels import (  # noqa: F401
     add_bias_,
     argmax,
     embedding,
+    decode_splits_for,
     gemm_simt,
+    gemm_skinny,
+    mma_attention_supports,
     linear,
     paged_attention,
+    paged_attention_generic,
+    paged_attention_mma,
     rmsnorm,
     rope_kv_write,
     sample,

@@ -39,6 +39,11 @@ _SIGNATURES = {
     "li_paged_attention_generic": ("attention_generic", [
         c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "li_paged_attention_mma": ("attention_mma", [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+        c_int, c_void_p]),
+    "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_gemm_simt": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "li_sample": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -57,8 +62,14 @@ def _fn(name: str):
     return fn
 
 
+# Launches of this package's own kernels since import (library products are not counted).
+launch_count = 0
+
+
 def _check(code: int, name: str) -> None:
+    global launch_count
     if code == 0:
+        launch_count += 1
         return
     if code in _ERRORS:
         raise KernelLibraryError(f"{name}: {_ERRORS[code]}")
@@ -178,10 +189,30 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch
         _check(_fn("li_gemm_simt")(0, x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
                                    _stream()), "gemm_simt")
         return out
+    if 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and K >= 8:
+        _check(_fn("li_gemm_skinny")(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
+                                     _stream()), "gemm_skinny")
+        return out
     if M > 0:
         torch.mm(x, weight.t(), out=out)
         if bias is not None:
             add_bias_(out, bias)
+    return out
+
+
+# Rows of x up to which the weight-streaming kernel runs the bfloat16 product.
+SKINNY_MAX_ROWS = 64
+NUM_SMS = 148
+
+
+def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """The weight-streaming bfloat16 product for at most 64 rows of x."""
+    _on_gpu(x, weight, out, bias)
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and out.shape == (M, N) and x.dtype == weight.dtype == out.dtype == torch.bfloat16
+    _check(_fn("li_gemm_skinny")(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, _stream()),
+           "gemm_skinny")
     return out
 
 
@@ -222,25 +253,85 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
            "rope_kv_write")
 
 
+def decode_splits_for(num_decode: int, kv_heads: int, max_context_len: int) -> int:
+    """Blocks that share one sequence's keys in a decode launch: enough to fill the GPU when the
+    batch is narrow, never fewer than two key tiles each, at most 32
+    (liteinfer/engine/model_runner.py:250-272 and paged_kernels.py:645-693 choose likewise)."""
+    tiles = -(-max_context_len // 64)
+    if tiles < 4:
+        return 1
+    return max(1, min(4 * NUM_SMS // max(1, num_decode * kv_heads), tiles // 2, 32))
+
+
+def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
+                            num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0) -> torch.Tensor:
+    """The plain SIMT kernel: any dtype, head size up to 256, any grouping."""
+    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
+    pages, kvh, page_size, hd = k_pool.shape
+    _check(_fn("li_paged_attention_generic")(
+        _code(q), q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
+        num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale), int(window), _stream()),
+        "paged_attention_generic")
+    return out
+
+
+def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
+                        seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0, num_splits=1,
+                        token_index=None, num_tokens=0) -> torch.Tensor:
+    """The tensor-core kernel (bfloat16, head size 64 or 128); `num_splits` > 1 splits every sequence's keys."""
+    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index, token_index)
+    pages, kvh, page_size, hd = k_pool.shape
+    partial_out = partial_lse = None
+    if num_splits > 1:
+        total = q.shape[0] * heads * num_splits
+        partial_out = torch.empty((total, head_dim), dtype=torch.float32, device=q.device)
+        partial_lse = torch.empty((total,), dtype=torch.float32, device=q.device)
+    _check(_fn("li_paged_attention_mma")(
+        q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
+        _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
+        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(token_index), num_tokens,
+        _stream()), "paged_attention_mma")
+    return out
+
+
+def mma_attention_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and heads // kv_heads <= 64
+
+
 def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: torch.Tensor,
                     v_pool: torch.Tensor, block_table: torch.Tensor, query_start_loc: torch.Tensor,
                     context_lens: torch.Tensor, num_seqs: int, max_q_len: int, heads: int, kv_heads: int,
-                    head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+                    head_dim: int, scale: float, window: int = 0, plan=None,
+                    decode_splits: int | None = None) -> torch.Tensor:
     """Attention of each sequence's newest queries over its pages (any mix of portions and single tokens).
 
     q: the tensor holding the queries, head h of token t at q[t, h*head_dim:...]
     with `q_row_stride` elements between tokens (the fused qkv buffer is passed as
-    it is).  out: [tokens, heads*head_dim].
+    it is).  out: [tokens, heads*head_dim].  bfloat16 with head size 64 or 128 runs
+    on tensor cores; with a `plan` (AttentionPlan) the sequences that bring one
+    token go through a launch that splits their keys over several blocks, the
+    others through an unsplit one.  Everything else runs the plain SIMT kernel.
     """
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
     _int32(block_table, "block_table"); _int32(query_start_loc, "query_start_loc"); _int32(context_lens, "context_lens")
     pages, kvh, page_size, hd = k_pool.shape
     assert (kvh, hd) == (kv_heads, head_dim) and q.dtype == out.dtype == k_pool.dtype == v_pool.dtype
-    _check(_fn("li_paged_attention_generic")(
-        _code(q), q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
-        block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
-        num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale), int(window), _stream()),
-        "paged_attention")
+    if not mma_attention_supports(q.dtype, heads, kv_heads, head_dim):
+        return paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc,
+                                       context_lens, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window)
+    common = (q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
+    if plan is None:
+        return paged_attention_mma(*common, None, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window)
+    if plan.num_prefill:
+        paged_attention_mma(*common, plan.prefill_seqs, plan.num_prefill, plan.max_prefill_query_len, heads,
+                            kv_heads, head_dim, scale, window)
+    if plan.num_decode:
+        bound = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window)
+        splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound)
+        paged_attention_mma(*common, plan.decode_seqs, plan.num_decode, 1, heads, kv_heads, head_dim, scale,
+                            window, splits, plan.decode_tokens, plan.num_decode)
     return out
 
 

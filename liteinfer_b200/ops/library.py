@@ -35,7 +35,7 @@ NVCC_FLAGS = [
 ]
 
 # Source file (without .cu) of every library.
-SOURCES = ("elementwise", "rope_cache", "attention_generic", "gemm_simt", "sampling")
+SOURCES = ("elementwise", "rope_cache", "attention_generic", "attention_mma", "gemm_simt", "gemm_skinny", "sampling")
 
 
 class KernelLibraryError(RuntimeError):

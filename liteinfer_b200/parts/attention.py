@@ -95,7 +95,8 @@ class Attention:
         attended = torch.empty((tokens, q_width), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, qkv.shape[1], attended, kv.k_pool, kv.v_pool, table, ctx.query_start_loc,
                             ctx.context_lens, ctx.num_seqs, ctx.max_query_len, self.heads, self.kv_heads,
-                            self.head_dim, self.scale, self.window or 0)
+                            self.head_dim, self.scale, self.window or 0, plan=ctx.plan,
+                            decode_splits=ctx.decode_splits)
         out = torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device)
         return ops.linear(attended, self.o_weight, out, self.o_bias)
 

@@ -49,6 +49,20 @@ class LayerCache:
 
 
 @dataclass
+class AttentionPlan:
+    """How a step's sequences are dealt to the attention kernels: those that bring one
+    token (their keys may be split over several blocks) and those that bring more."""
+
+    num_decode: int = 0
+    decode_seqs: torch.Tensor | None = None     # [num_decode] int32 batch rows with one query
+    decode_tokens: torch.Tensor | None = None   # [num_decode] int32 their token rows
+    num_prefill: int = 0
+    prefill_seqs: torch.Tensor | None = None    # [num_prefill] int32 batch rows with several queries
+    max_prefill_query_len: int = 0
+    max_decode_context_len: int = 0             # host bound on the decode rows' context (sizes the splits)
+
+
+@dataclass
 class StepContext:
     num_tokens: int
     num_seqs: int
@@ -66,6 +80,7 @@ class StepContext:
     query_lens: tuple[int, ...] = ()       # host copy
     host_context_lens: tuple[int, ...] = ()  # host copy
     decode_splits: int | None = None       # EngineConfig.paged_decode_splits
+    plan: AttentionPlan | None = None
     extras: dict = field(default_factory=dict)
 
     @property

@@ -276,3 +276,111 @@ def test_sample_distribution():
     freq = torch.bincount(got.long(), minlength=vocab).float() / n
     assert float((freq - p).abs().max()) < 0.015
     assert set(got.tolist()) <= set(keep.tolist())
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(3072, 2048), (2048, 8192), (1000, 96), (17, 40), (128256 // 8, 2048)])
+def test_gemm_skinny(M, N, K):
+    from liteinfer_b200 import ops
+
+    x, w = _randn(M, K, dtype=torch.bfloat16), _randn(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    b = _randn(N, dtype=torch.bfloat16, seed=2)
+    got = ops.gemm_skinny(x, w, torch.empty(M, N, dtype=torch.bfloat16, device="cuda"), b)
+    want = x.double() @ w.double().t() + b.double()
+    torch.testing.assert_close(got.double(), want, rtol=2 ** -7, atol=2 ** -7)
+
+
+def test_gemm_skinny_rows_do_not_depend_on_the_batch():
+    from liteinfer_b200 import ops
+
+    x, w = _randn(64, 2048, dtype=torch.bfloat16), _randn(555, 2048, dtype=torch.bfloat16, seed=1, scale=0.05)
+    full = ops.gemm_skinny(x, w, torch.empty(64, 555, dtype=torch.bfloat16, device="cuda"))
+    for rows in (1, 8, 20):
+        part = ops.gemm_skinny(x[:rows].contiguous(), w, torch.empty(rows, 555, dtype=torch.bfloat16, device="cuda"))
+        assert torch.equal(part, full[:rows])
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do():
+    from liteinfer_b200 import ops
+    from liteinfer_b200.ops import KernelLibraryError
+
+    x, w = _randn(65, 64, dtype=torch.bfloat16), _randn(16, 64, dtype=torch.bfloat16)
+    with pytest.raises(KernelLibraryError, match="refuses"):
+        ops.gemm_skinny(x, w, torch.empty(65, 16, dtype=torch.bfloat16, device="cuda"))
+    x, w = _randn(2, 100, dtype=torch.bfloat16), _randn(16, 100, dtype=torch.bfloat16)
+    with pytest.raises(KernelLibraryError, match="refuses"):
+        ops.gemm_skinny(x, w, torch.empty(2, 16, dtype=torch.bfloat16, device="cuda"))
+    # ...while `linear` takes any shape, by handing what the kernel refuses to the library product.
+    out = ops.linear(x, w, torch.empty(2, 16, dtype=torch.bfloat16, device="cuda"))
+    torch.testing.assert_close(out.double(), x.double() @ w.double().t(), rtol=2 ** -7, atol=2 ** -7)
+
+
+def _plan_for(q_lens, ctx_lens):
+    from liteinfer_b200.parts.context import AttentionPlan
+
+    dec = [i for i, q in enumerate(q_lens) if q == 1]
+    pre = [i for i, q in enumerate(q_lens) if q > 1]
+    starts = [0]
+    for q in q_lens:
+        starts.append(starts[-1] + q)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    return AttentionPlan(num_decode=len(dec), decode_seqs=i32(dec), decode_tokens=i32([starts[i] for i in dec]),
+                         num_prefill=len(pre), prefill_seqs=i32(pre),
+                         max_prefill_query_len=max([q_lens[i] for i in pre], default=0),
+                         max_decode_context_len=max([ctx_lens[i] for i in dec], default=0))
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [(4, 2, 64, 16), (8, 8, 64, 8), (32, 8, 128, 16),
+                                                               (6, 2, 128, 5), (64, 1, 64, 32), (5, 1, 64, 16)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("splits", [None, 1, 3, 32])
+def test_tensor_core_attention_against_the_plain_kernel(heads, kv_heads, head_dim, page_size, window, splits):
+    """Portions and single tokens, planned (split decode rows beside unsplit portions) or not, over
+    contexts that straddle the 64-key tiles, with NaN in every slot no request owns."""
+    from liteinfer_b200 import ops
+
+    q_lens = [1, 130, 1, 7, 64, 1, 1, 2]
+    ctx_lens = [700, 190, 1, 7, 64, 63, 65, 129]
+    case = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page_size, q_lens, ctx_lens)
+    qkv, k_pool, v_pool = case["qkv"], case["k_pool"], case["v_pool"]
+    ops.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_pool, v_pool, None, heads, kv_heads,
+                      head_dim, 0)
+    args = (qkv, qkv.shape[1])
+    rest = (k_pool, v_pool, case["table"], case["qsl"], case["ctx"], case["B"], max(q_lens), heads, kv_heads,
+            head_dim, head_dim ** -0.5, window)
+    want = ref.paged_attention(*args, torch.empty(case["T"], heads * head_dim, dtype=torch.bfloat16, device="cuda"), *rest)
+    out = torch.full((case["T"], heads * head_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+    plan = None if splits is None else _plan_for(q_lens, ctx_lens)
+    got = ops.paged_attention(*args, out, *rest, plan=plan, decode_splits=splits if splits and splits > 1 else None)
+    assert torch.isfinite(got.float()).all()
+    torch.testing.assert_close(got.float(), want.float(), rtol=2 ** -6, atol=2 ** -6)
+
+
+def test_tensor_core_attention_finds_one_far_key_under_splits():
+    from liteinfer_b200 import ops
+
+    heads, kv_heads, d, page, ctx = 8, 2, 128, 16, 3000
+    for far in (0, 63, 64, 1500, 2998):
+        case = _paged_case(torch.bfloat16, heads, kv_heads, d, page, [1], [ctx], seed=far)
+        qkv, k_pool, v_pool = case["qkv"], case["k_pool"], case["v_pool"]
+        ops.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_pool, v_pool, None, heads,
+                          kv_heads, d, 0)
+        q = qkv[:, :heads * d].view(1, heads, d)
+        pg, off = int(case["table"][0, far // page]), far % page
+        for h in range(kv_heads):
+            k_pool[pg, h, off] = (q[0, h * 4].float() * 4).to(torch.bfloat16)
+        out = torch.empty(1, heads * d, dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention(qkv, qkv.shape[1], out, k_pool, v_pool, case["table"], case["qsl"], case["ctx"], 1, 1,
+                            heads, kv_heads, d, 1.0, 0, plan=_plan_for([1], [ctx]))
+        for h in range(kv_heads):
+            torch.testing.assert_close(out.view(heads, d)[h * 4].float(), v_pool[pg, h, off].float(),
+                                       rtol=2e-2, atol=2e-2)
+
+
+def test_split_policy():
+    from liteinfer_b200.ops import decode_splits_for
+
+    assert decode_splits_for(1, 8, 100) == 1            # fewer than four key tiles: nothing to split
+    assert decode_splits_for(1, 8, 4096) == 32
+    assert 2 <= decode_splits_for(8, 8, 4096) <= 16
+    assert decode_splits_for(64, 8, 4096) == 1

@@ -19,7 +19,7 @@ def _requests(vocab: int, lengths, seed0: int = 0) -> dict[str, list[int]]:
 
 
 @pytest.mark.parametrize("name,lengths", [("tiny_a", (5, 17, 33, 70)), ("tiny_b", (1, 9, 40, 64, 100)),
-                                           ("tiny_c", (3, 50))])
+                                           ("tiny_c", (3, 50)), ("tiny_d", (2, 70, 130))])
 def test_all_cuts_match_plain_on_cpu(cpu_kernels, model_dirs, name, lengths):
     from liteinfer_b200.engine.loading import build_runner
 

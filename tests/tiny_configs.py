@@ -33,8 +33,19 @@ TINY_C = {
 }
 TINY_C_SEED, TINY_C_PAGE = 2, 4
 
+# Head size 64 and groups of two: what the tensor-core attention kernel takes, at toy width.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "vocab_size": 300, "hidden_size": 128, "intermediate_size": 96,
+    "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 128},
+    "tie_word_embeddings": True, "max_position_embeddings": 1024, "hidden_act": "silu",
+}
+TINY_D_SEED, TINY_D_PAGE = 3, 16
+
 ALL = {"tiny_a": (TINY_A, TINY_A_SEED, TINY_A_PAGE), "tiny_b": (TINY_B, TINY_B_SEED, TINY_B_PAGE),
-       "tiny_c": (TINY_C, TINY_C_SEED, TINY_C_PAGE)}
+       "tiny_c": (TINY_C, TINY_C_SEED, TINY_C_PAGE), "tiny_d": (TINY_D, TINY_D_SEED, TINY_D_PAGE)}
 
 
 def prompt(vocab: int, length: int, seed: int) -> list[int]:

@@ -112,7 +112,7 @@ def rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv
 
 
 def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens, num_seqs,
-                    max_q_len, heads, kv_heads, head_dim, scale, window=0):
+                    max_q_len, heads, kv_heads, head_dim, scale, window=0, plan=None, decode_splits=None):
     dtype = out.dtype
     page_size = k_pool.shape[2]
     groups = heads // kv_heads
