@@ -18,6 +18,7 @@ def test_graph_replay_equals_eager(model_dirs, name, dtype):
     config, _, page = tiny_configs.ALL[name]
     vocab = config["vocab_size"]
     prompts = {f"r{i}": tiny_configs.prompt(vocab, n, i) for i, n in enumerate((5, 40, 290))}
+    forced = {r: tiny_configs.prompt(vocab, 20, 50 + i) for i, r in enumerate(prompts)}
     runs = []
     for graphs in (False, True):
         runner = build_runner(model_dirs[name], dtype, "cuda:0", page, 80, 4)
@@ -28,14 +29,16 @@ def test_graph_replay_equals_eager(model_dirs, name, dtype):
         for step in range(20):
             if step == 8:
                 runner.release(live.pop(0))            # the batch narrows: another graph
-            tokens = [int(torch.argmax(rows[-1][i])) for i in range(len(live))]
+            tokens = [forced[r][step] for r in live]      # forced tokens keep both runs on one path
             rows.append(runner.step([StepEntry(r, [t], (0,)) for r, t in zip(live, tokens)]))
-            if step == 8:
-                rows[-1] = rows[-1]
         runs.append(rows)
         if graphs:
             assert runner.graph_replays == 20 and len(runner._graphs) == 2
     for eager, replayed in zip(*runs):
-        if eager.shape != replayed.shape:      # greedy tokens of the narrowed batch are re-indexed identically
-            raise AssertionError("shapes differ")
-        assert torch.equal(eager, replayed)
+        assert eager.shape == replayed.shape
+        if name == "tiny_d":
+            # A graph splits the keys by the longest context it may ever see, the eager step by the one
+            # it has: the same sums in another order.
+            torch.testing.assert_close(eager.float(), replayed.float(), rtol=2 ** -6, atol=2 ** -6)
+        else:
+            assert torch.equal(eager, replayed)
