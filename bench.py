@@ -157,8 +157,14 @@ def run_ours(args) -> dict:
         vocab, hidden = cfg["vocab_size"], cfg["hidden_size"]
         sampler = Sampler(0)
 
-        # ---- prefill: one prompt of 2,048 tokens, logits at its last token
         g = torch.Generator().manual_seed(7)
+        if args.section == "decode":
+            value, ms, launches = _decode_rate(runner, sampler, greedy, args.batch, decode_start, steps, warmup, vocab)
+            llm.close()
+            return {"section": "decode", "batch": args.batch, "value": value, "ms_per_step": ms,
+                    "gpu_launches": launches * steps}
+
+        # ---- prefill: one prompt of 2,048 tokens, logits at its last token
         prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
         times = []
         for i in range(3 + 3):
@@ -179,6 +185,9 @@ def run_ours(args) -> dict:
         prefill_flops = 2 * linear_params * PREFILL_TOKENS + attn_flops + 2 * hidden * vocab
         prefill = {"value": PREFILL_TOKENS / prefill_ms * 1e3, "tokens": PREFILL_TOKENS, "ms": prefill_ms,
                    "frac": prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
+        if args.section == "prefill":
+            llm.close()
+            return {"section": "prefill", **prefill}
 
         # ---- decode, device-timed
         clocks = ClockSampler()
@@ -251,6 +260,9 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    parser.add_argument("--section", default="all", choices=["all", "decode", "prefill"],
+                        help="run one part only (for profiling); the JSON line then lacks the other parts")
+    parser.add_argument("--batch", type=int, default=8, help="decode batch of --section decode")
     args = parser.parse_args()
     if args.gpus != 1:
         if int(os.environ.get("RANK", "0")) == 0:

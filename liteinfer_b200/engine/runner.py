@@ -121,7 +121,6 @@ class _DecodeGraph:
         cache = runner.cache
         pages = -(-max_model_len // cache.page_size)
         self.batch = _Batch(width, width, width, [pages] * len(cache.groups), width, 0)
-        self.host = torch.empty(self.batch.total, dtype=torch.int32, pin_memory=True)
         self.device_buffer = torch.zeros(self.batch.total, dtype=torch.int32, device=runner.device)
         counts, totals = [1] * width, [max_model_len] * width
         self.ctx = _context(self.batch, self.device_buffer, runner.device, counts, totals, runner.decode_splits,
@@ -220,8 +219,11 @@ class ModelRunner:
 
     def _replay(self, graph: _DecodeGraph, entries: list[StepEntry]) -> torch.Tensor:
         starts = [self.cache.length(e.request_id) for e in entries]
-        _fill(graph.batch, graph.host.numpy(), entries, self.cache, starts)
-        graph.device_buffer.copy_(graph.host, non_blocking=True)
+        # A fresh pinned buffer every step: the copy below is asynchronous, and the host may be
+        # filling the next step's batch before the device has read this one.
+        host = torch.empty(graph.batch.total, dtype=torch.int32, pin_memory=True)
+        _fill(graph.batch, host.numpy(), entries, self.cache, starts)
+        graph.device_buffer.copy_(host, non_blocking=True)
         if graph.graph is None:
             graph.capture(self)
         graph.graph.replay()
