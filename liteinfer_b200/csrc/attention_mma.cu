@@ -12,6 +12,16 @@
 // accumulator, split partials and their log-sum-exp are 32-bit; probabilities
 // are rounded to bfloat16 for P.V (paged_kernels.py:282-284).
 //
+// Two shapes of block.  With several query tokens per sequence each of the four
+// warps owns 16 of the tile's 64 rows and walks all 64 keys of a K/V tile.  With
+// one token per sequence (decode) the rows of a tile are just the heads of one
+// group (at most 16), so all four warps share those rows and each takes 16 of
+// the tile's 64 keys; their four running softmax states are merged through
+// shared memory at the end.  When the keys are split over several blocks, each
+// block leaves its partial result in scratch memory and bumps a counter; the
+// block that arrives last merges the splits (in split order) and resets the
+// counter, so no second launch and no waiting is needed.
+//
 // Data path: K and V tiles of 64 keys are gathered page by page with cp.async
 // into swizzled shared memory, double buffered; fragments come from ldmatrix;
 // the products are mma.sync m16n8k16 (bf16 in, f32 out).  Keys outside the
@@ -44,6 +54,7 @@ struct AttnParams {
   int num_splits;
   float* partial_out;     // [tokens * heads * splits, D] when num_splits > 1
   float* partial_lse;     // [tokens * heads * splits]
+  unsigned* counters;     // [grid.z * kv_heads * query tiles], zero between launches, when num_splits > 1
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -98,20 +109,22 @@ __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParam
   }
 }
 
-template <int D>
+// kDecode: every launched sequence brings one token and the group has at most 16 heads.
+template <int D, bool kDecode>
 __global__ void __launch_bounds__(kWarps * 32)
 attention_mma_kernel(const AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);           // [64][D]
   bf16* kbuf = qs + kBlockM * D;                          // 2 x [64][D]
   bf16* vbuf = kbuf + 2 * kBlockN * D;                    // 2 x [64][D]
+  __shared__ bool is_last;
 
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
   const int kvh = blockIdx.y;
   const int split = blockIdx.x % p.num_splits, qtile = blockIdx.x / p.num_splits;
   const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
   const int groups = p.heads / p.kv_heads;
-  const int tq = kBlockM / groups;                        // query tokens per tile
+  const int tq = (kDecode ? 16 : kBlockM) / groups;       // query tokens per tile
   const int q0 = qtile * tq;
   if (q0 >= q_len) return;
   const int ctx = p.context_lens[seq];
@@ -120,6 +133,9 @@ attention_mma_kernel(const AttnParams p) {
   const int* table = p.block_table + (size_t)seq * p.table_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   constexpr int kChunks = D / 8;
+  constexpr int kGroupsPerWarp = kDecode ? 1 : kBlockN / 16;   // 16-key groups of a tile that a warp walks
+  const int row_base = kDecode ? 0 : warp * 16;               // first tile row of this warp
+  const int key_group0 = kDecode ? warp : 0;                  // first 16-key group of this warp
 
   // Visible keys of this tile: [lo, hi).
   const int first_qpos = ctx - q_len + q0, last_qpos = first_qpos + tile_q - 1;
@@ -131,7 +147,8 @@ attention_mma_kernel(const AttnParams p) {
   const int my_lo = tile_lo + split * per_split, my_hi = min(tile_hi, my_lo + per_split);
 
   // ---- Q tile -> shared (zero rows beyond rows_used), then A fragments in registers.
-  for (int c = threadIdx.x; c < kBlockM * kChunks; c += kWarps * 32) {
+  constexpr int kQRows = kDecode ? 16 : kBlockM;
+  for (int c = threadIdx.x; c < kQRows * kChunks; c += kWarps * 32) {
     const int row = c / kChunks, chunk = c % kChunks;
     const bool valid = row < rows_used;
     const int qi = q0 + row / groups, head = kvh * groups + row % groups;
@@ -148,13 +165,13 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk)
     ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3],
-                tile_ptr<D>(qs, warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
+                tile_ptr<D>(qs, row_base + (lane & 15), kk * 2 + (lane >> 4)));
 
-  // Rows of this thread: warp*16 + g and + 8.
+  // Rows of this thread: row_base + g and + 8.
   int qpos[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    const int row = warp * 16 + g + 8 * h;
+    const int row = row_base + g + 8 * h;
     qpos[h] = row < rows_used ? first_qpos + row / groups : -1;   // -1: a padding row sees nothing
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -175,29 +192,30 @@ attention_mma_kernel(const AttnParams p) {
     cp_async_wait<1>();
     __syncthreads();
 
-    // S = Q K^T for 16 rows x 64 keys.
-    float s[kBlockN / 8][4];
+    // S = Q K^T for 16 rows x (16 keys per group).
+    float s[kGroupsPerWarp * 2][4];
 #pragma unroll
-    for (int i = 0; i < kBlockN / 8; ++i)
+    for (int i = 0; i < kGroupsPerWarp * 2; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
 #pragma unroll
-      for (int nn = 0; nn < kBlockN / 16; ++nn) {
+      for (int nn = 0; nn < kGroupsPerWarp; ++nn) {
         unsigned b0, b1, b2, b3;
         const int mtx = lane >> 3;
-        ldmatrix_x4(b0, b1, b2, b3, tile_ptr<D>(ks, nn * 16 + (mtx >> 1) * 8 + (lane & 7), kk * 2 + (mtx & 1)));
+        ldmatrix_x4(b0, b1, b2, b3,
+                    tile_ptr<D>(ks, (key_group0 + nn) * 16 + (mtx >> 1) * 8 + (lane & 7), kk * 2 + (mtx & 1)));
         mma_bf16(s[nn * 2], qf[kk], b0, b1);
         mma_bf16(s[nn * 2 + 1], qf[kk], b2, b3);
       }
     }
 
     // Scale, mask, online softmax.
-    const int key0 = tile * kBlockN;
+    const int key0 = tile * kBlockN + key_group0 * 16;
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < kBlockN / 8; ++i)
+    for (int i = 0; i < kGroupsPerWarp * 2; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kpos = key0 + i * 8 + 2 * t + (j & 1);
@@ -217,9 +235,9 @@ attention_mma_kernel(const AttnParams p) {
       m[h] = m_new;
     }
     float row_sum[2] = {0.f, 0.f};
-    unsigned pf[kBlockN / 16][4];
+    unsigned pf[kGroupsPerWarp][4];
 #pragma unroll
-    for (int i = 0; i < kBlockN / 8; ++i) {
+    for (int i = 0; i < kGroupsPerWarp * 2; ++i) {
       float e[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -239,12 +257,13 @@ attention_mma_kernel(const AttnParams p) {
 
     // O += P V.
 #pragma unroll
-    for (int kb = 0; kb < kBlockN / 16; ++kb) {
+    for (int kb = 0; kb < kGroupsPerWarp; ++kb) {
 #pragma unroll
       for (int dd = 0; dd < D / 16; ++dd) {
         unsigned b0, b1, b2, b3;
         const int mtx = lane >> 3;
-        ldmatrix_x4_trans(b0, b1, b2, b3, tile_ptr<D>(vs, kb * 16 + (mtx & 1) * 8 + (lane & 7), dd * 2 + (mtx >> 1)));
+        ldmatrix_x4_trans(b0, b1, b2, b3,
+                          tile_ptr<D>(vs, (key_group0 + kb) * 16 + (mtx & 1) * 8 + (lane & 7), dd * 2 + (mtx >> 1)));
         mma_bf16(o[dd * 2], pf[kb], b0, b1);
         mma_bf16(o[dd * 2 + 1], pf[kb], b2, b3);
       }
@@ -253,81 +272,125 @@ attention_mma_kernel(const AttnParams p) {
   }
   cp_async_wait<0>();
 
-  // ---- finish: row sums across the quad, normalise, store.
+  // Row sums across the quad.
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
     l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
   }
+
+  if (kDecode) {
+    // ---- merge the four warps' states (each saw a quarter of the keys) through shared memory.
+    __syncthreads();
+    float* os = reinterpret_cast<float*>(kbuf);            // [4 warps][16 rows][D]
+    float* ms = os + kWarps * 16 * D;                      // [4][16]
+    float* ls = ms + kWarps * 16;                          // [4][16]
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int row = warp * 16 + g + 8 * h;
-    if (row >= rows_used) continue;
+    for (int h = 0; h < 2; ++h) {
+      const int row = g + 8 * h;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<float2*>(os + ((size_t)warp * 16 + row) * D + i * 8 + 2 * t) =
+            make_float2(o[i][2 * h], o[i][2 * h + 1]);
+      if (t == 0) {
+        ms[warp * 16 + row] = m[h];
+        ls[warp * 16 + row] = l[h];
+      }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < rows_used * D; e += kWarps * 32) {
+      const int row = e / D, d = e % D;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, ms[w * 16 + row]);
+      float denom = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const float mw = ms[w * 16 + row];
+        const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - mx);
+        denom += wgt * ls[w * 16 + row];
+        acc += wgt * os[((size_t)w * 16 + row) * D + d];
+      }
+      const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+      const float value = denom > 0.f ? acc / denom : 0.f;
+      if (p.num_splits == 1) {
+        p.out[(size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d] = __float2bfloat16_rn(value);
+      } else {
+        const size_t slot = ((size_t)(q_begin + qi) * p.heads + head) * p.num_splits + split;
+        p.partial_out[slot * D + d] = value;
+        if (d == 0) p.partial_lse[slot] = denom > 0.f ? mx + log2f(denom) : -INFINITY;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = row_base + g + 8 * h;
+      if (row >= rows_used) continue;
+      const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+      const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+      if (p.num_splits == 1) {
+        bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+          *reinterpret_cast<unsigned*>(dst + i * 8 + 2 * t) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      } else {
+        const size_t slot = ((size_t)(q_begin + qi) * p.heads + head) * p.num_splits + split;
+        float* dst = p.partial_out + slot * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+          *reinterpret_cast<float2*>(dst + i * 8 + 2 * t) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+        // log-sum-exp in base 2 of the scaled scores; -inf marks a split that saw no key
+        if (t == 0) p.partial_lse[slot] = l[h] > 0.f ? m[h] + log2f(l[h]) : -INFINITY;
+      }
+    }
+  }
+  if (p.num_splits == 1) return;
+
+  // ---- the block that arrives last merges the splits of this (sequence, KV head, query tile).
+  __threadfence();
+  __syncthreads();
+  const unsigned counter_index = ((unsigned)blockIdx.z * gridDim.y + blockIdx.y) * (gridDim.x / p.num_splits) + qtile;
+  if (threadIdx.x == 0) {
+    const unsigned arrived = atomicAdd(&p.counters[counter_index], 1u);
+    is_last = arrived == (unsigned)p.num_splits - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int e = threadIdx.x; e < rows_used * D; e += kWarps * 32) {
+    const int row = e / D, d = e % D;
     const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-    const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
-    if (p.num_splits == 1) {
-      bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i)
-        *reinterpret_cast<unsigned*>(dst + i * 8 + 2 * t) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
-    } else {
-      const size_t slot = ((size_t)(q_begin + qi) * p.heads + head) * p.num_splits + split;
-      float* dst = p.partial_out + slot * D;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i)
-        *reinterpret_cast<float2*>(dst + i * 8 + 2 * t) = make_float2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
-      // log-sum-exp in base 2 of the scaled scores; -inf marks a split that saw no key
-      if (t == 0) p.partial_lse[slot] = l[h] > 0.f ? m[h] + log2f(l[h]) : -INFINITY;
-    }
-  }
-}
-
-// out[token, head] = sum_s w_s * partial[token, head, s], w_s = 2^(lse_s - max) / sum.
-template <int D>
-__global__ void combine_splits_kernel(const float* __restrict__ partial_out, const float* __restrict__ partial_lse,
-                                      bf16* __restrict__ out, int out_row_stride, const int* __restrict__ token_index,
-                                      int heads, int num_splits) {
-  const int token = token_index ? token_index[blockIdx.x] : blockIdx.x;
-  const int head = blockIdx.y;
-  const size_t base = ((size_t)token * heads + head) * num_splits;
-  float mx = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, partial_lse[base + s]);
-  float denom = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    const float v = partial_lse[base + s];
-    denom += v == -INFINITY ? 0.f : exp2f(v - mx);
-  }
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float v = partial_lse[base + s];
+    const size_t base = ((size_t)(q_begin + qi) * p.heads + head) * p.num_splits;
+    float mx = -INFINITY;
+    for (int sidx = 0; sidx < p.num_splits; ++sidx) mx = fmaxf(mx, __ldcg(p.partial_lse + base + sidx));
+    float denom = 0.f, acc = 0.f;
+    for (int sidx = 0; sidx < p.num_splits; ++sidx) {
+      const float v = __ldcg(p.partial_lse + base + sidx);
       if (v == -INFINITY) continue;
-      acc += exp2f(v - mx) * partial_out[(base + s) * D + d];
+      const float wgt = exp2f(v - mx);
+      denom += wgt;
+      acc += wgt * __ldcg(p.partial_out + (base + sidx) * D + d);
     }
-    out[(size_t)token * out_row_stride + (size_t)head * D + d] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
+    p.out[(size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d] =
+        __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
   }
+  if (threadIdx.x == 0) p.counters[counter_index] = 0;   // ready for the next launch
 }
 
-template <int D>
-int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, const int* token_index, int num_tokens,
-                     cudaStream_t stream) {
+template <int D, bool kDecode>
+int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
   const int groups = p.heads / p.kv_heads;
-  const int tq = kBlockM / groups;
+  const int tq = (kDecode ? 16 : kBlockM) / groups;
   const size_t smem = (size_t)(kBlockM + 4 * kBlockN) * D * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D, kDecode>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const dim3 grid(((max_q_len + tq - 1) / tq) * p.num_splits, p.kv_heads, num_seqs);
-  attention_mma_kernel<D><<<grid, kWarps * 32, smem, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  if (p.num_splits > 1) {
-    combine_splits_kernel<D><<<dim3(num_tokens, p.heads), D / 2 < 32 ? 32 : D / 2, 0, stream>>>(
-        p.partial_out, p.partial_lse, p.out, p.out_row_stride, token_index, p.heads, p.num_splits);
-  }
+  attention_mma_kernel<D, kDecode><<<grid, kWarps * 32, smem, stream>>>(p);
   LI_LAUNCH_CHECK();
 }
 
@@ -335,29 +398,42 @@ int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, const int
 
 using namespace li;
 
-// Tensor-core paged attention (bfloat16; head_dim 64 or 128; groups dividing into 64 rows).
+// Counters the launch needs when num_splits > 1 (unsigned, all zero before the first launch).
+LI_EXPORT int li_paged_attention_mma_counters(int num_seqs, int max_q_len, int heads, int kv_heads) {
+  const int groups = heads / kv_heads;
+  const bool decode = max_q_len == 1 && groups <= 16;
+  const int tq = (decode ? 16 : kBlockM) / groups;
+  return num_seqs * kv_heads * ((max_q_len + tq - 1) / tq);
+}
+
+// Tensor-core paged attention (bfloat16; head_dim 64 or 128; groups of at most 64 heads).
 // seq_index (optional, [num_seqs]): the batch rows to run, so that a mixed step can send its
 // single-token sequences through a split launch and the others through an unsplit one.
-// num_splits > 1 needs partial_out [tokens*heads*splits, head_dim] and partial_lse
-// [tokens*heads*splits] (float32) and token_index/num_tokens: the token rows to merge.
+// num_splits > 1 needs scratch: partial_out [tokens*heads*splits, head_dim] and partial_lse
+// [tokens*heads*splits] (float32, tokens = rows of q), and `counters`
+// (li_paged_attention_mma_counters(...) unsigned values, zero; the kernel leaves them zero).
 LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out, int out_row_stride,
                                      const void* k_pool, const void* v_pool, const int* block_table,
                                      int table_stride, const int* query_start_loc, const int* context_lens,
                                      const int* seq_index, int num_seqs, int max_q_len, int heads, int kv_heads,
                                      int head_dim, int page_size, int num_pages, float scale, int window,
-                                     int num_splits, float* partial_out, float* partial_lse,
-                                     const int* token_index, int num_tokens, cudaStream_t stream) {
+                                     int num_splits, float* partial_out, float* partial_lse, unsigned* counters,
+                                     cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (kv_heads < 1 || heads % kv_heads) return LI_ERR_UNSUPPORTED;
   const int groups = heads / kv_heads;
   if (groups > kBlockM || (head_dim != 64 && head_dim != 128)) return LI_ERR_UNSUPPORTED;
   if (kv_heads > 65535 || num_seqs > 65535 || num_splits < 1) return LI_ERR_UNSUPPORTED;
-  if (num_splits > 1 && (!partial_out || !partial_lse)) return LI_ERR_UNSUPPORTED;
+  if (num_splits > 1 && (!partial_out || !partial_lse || !counters)) return LI_ERR_UNSUPPORTED;
   if ((q_row_stride % 8) || (out_row_stride % 2) || !aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool))
     return LI_ERR_ALIGNMENT;
   AttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                block_table, table_stride, query_start_loc, context_lens, seq_index, heads, kv_heads, page_size,
-               num_pages, scale * kLog2e, window, num_splits, partial_out, partial_lse};
-  return head_dim == 64 ? launch_attention<64>(p, num_seqs, max_q_len, token_index, num_tokens, stream)
-                        : launch_attention<128>(p, num_seqs, max_q_len, token_index, num_tokens, stream);
+               num_pages, scale * kLog2e, window, num_splits, partial_out, partial_lse, counters};
+  const bool decode = max_q_len == 1 && groups <= 16;
+  if (head_dim == 64)
+    return decode ? launch_attention<64, true>(p, num_seqs, max_q_len, stream)
+                  : launch_attention<64, false>(p, num_seqs, max_q_len, stream);
+  return decode ? launch_attention<128, true>(p, num_seqs, max_q_len, stream)
+                : launch_attention<128, false>(p, num_seqs, max_q_len, stream);
 }

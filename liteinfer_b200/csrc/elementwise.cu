@@ -129,6 +129,23 @@ __global__ void act_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict_
   }
 }
 
+// gate_up [rows, 2*width] with columns interleaved in eights: columns [16b, 16b+8) are gate columns
+// [8b, 8b+8), columns [16b+8, 16b+16) the matching up columns (the layout of the fused product's weights).
+template <typename T>
+__global__ void act_mul_interleaved_kernel(const T* __restrict__ gate_up, T* __restrict__ out, size_t rows, int width,
+                                           int act) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t n = rows * (size_t)width, stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const size_t r = i / width;
+    const int c = (int)(i - r * width);
+    const size_t base = r * 2 * width + (size_t)(c / 8) * 16 + (c % 8);
+    const float g = to_float(gate_up[base]);
+    const float u = to_float(gate_up[base + 8]);
+    out[i] = from_float<T>(round_to<T>(activate(g, act)) * u);
+  }
+}
+
 static int grid_for(size_t n, int block) {
   size_t g = (n + block - 1) / block;
   const size_t cap = 148 * 16;
@@ -210,4 +227,19 @@ LI_EXPORT int li_act_mul(int dtype, const void* gate_up, void* out, size_t rows,
   if (act < 0 || act > 3) return LI_ERR_UNSUPPORTED;
   return dtype == kFloat32 ? launch_act_mul<float>(gate_up, out, rows, width, act, stream)
                            : launch_act_mul<bf16>(gate_up, out, rows, width, act, stream);
+}
+
+// As li_act_mul for a gate_up interleaved in eights; width must be a multiple of 8.
+LI_EXPORT int li_act_mul_interleaved(int dtype, const void* gate_up, void* out, size_t rows, int width, int act,
+                                     cudaStream_t stream) {
+  if (act < 0 || act > 3 || (width % 8)) return LI_ERR_UNSUPPORTED;
+  if (rows == 0) return 0;
+  const size_t n = rows * (size_t)width;
+  if (dtype == kFloat32)
+    act_mul_interleaved_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, rows,
+                                                                            width, act);
+  else
+    act_mul_interleaved_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, rows,
+                                                                          width, act);
+  LI_LAUNCH_CHECK();
 }

@@ -6,16 +6,28 @@
 // are its 8-wide operand, so no tensor-core work is wasted on padding M.  Each
 // thread reads its weights straight from global memory as 16-byte vectors in
 // fragment order (the k index inside a 32-wide block is permuted the same way
-// for both operands, which a sum over k does not notice), with many loads in
-// flight and no shared-memory staging; x comes through L1/L2.  A block owns 16
-// rows of w; its warps take interleaved 32-wide k blocks and add their partial
-// sums through shared memory in a fixed order (32-bit).
+// for both operands, which a sum over k does not notice), all loads of a block
+// in flight at once, no shared-memory staging; x comes through L1/L2.
+//
+// Work unit: one block = 16 rows of w x one slice of k.  The four warps of a
+// block take interleaved 32-wide k blocks and add their partial sums through
+// shared memory in a fixed order.  When k is cut into several slices (few rows
+// of w, long k: the down and output projections) every block writes its 16 x M
+// partial tile to scratch memory and bumps the tile's counter; the block that
+// arrives last adds the slices in slice order, writes the result and resets the
+// counter.  Nothing waits on anything, and the order of every sum is fixed, so a
+// row's result depends neither on the batch nor on which block came last.
+//
+// Optional epilogue for a gated feed-forward: with `gated_act >= 0` the rows of w
+// are interleaved in groups of eight (eight gate rows, then their eight up rows),
+// and the block writes act(gate) * up, N/2 columns wide.
 #include "common.cuh"
 
 namespace li {
 
-constexpr int kSkinnyWarps = 8;
-constexpr int kUnroll = 4;
+constexpr int kSkinnyWarps = 4;
+constexpr int kBlocksPerWarp = 8;                                  // 32-wide k blocks per warp and pass
+constexpr int kSlicePass = kSkinnyWarps * kBlocksPerWarp * 32;      // 1024 k per pass
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -31,19 +43,46 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], unsigned a0, unsigned a
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ float gated(float gate, float up, int act) {
+  float a;
+  switch (act) {
+    case 0: a = gate / (1.0f + expf(-gate)); break;
+    case 1: a = 0.5f * gate * (1.0f + erff(gate * 0.70710678118654752440f)); break;
+    case 2: a = 0.5f * gate * (1.0f + tanhf(0.79788456080286535588f * (gate + 0.044715f * gate * gate * gate))); break;
+    default: a = fmaxf(gate, 0.f);
+  }
+  return __bfloat162float(__float2bfloat16_rn(a)) * up;   // the activation is rounded before the multiply
+}
+
+struct SkinnyParams {
+  const bf16* x;
+  const bf16* w;
+  const bf16* bias;
+  bf16* out;
+  int M, N, K;
+  int slice_k;        // k per slice, a multiple of 32
+  int num_slices;
+  int gated_act;      // -1: plain product
+  float* scratch;     // [tiles][num_slices][16][NT*8] partial tiles, when num_slices > 1
+  unsigned* counters; // [tiles], zero between launches
+};
+
 template <int NT>   // NT tiles of 8 rows of x
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
-gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ bias,
-                   bf16* __restrict__ out, int M, int N, int K) {
-  __shared__ float partial[kSkinnyWarps][16][NT * 8 + 1];
+gemm_skinny_kernel(const SkinnyParams p) {
+  constexpr int kCols = NT * 8;
+  __shared__ float partial[kSkinnyWarps][16][kCols + 1];
+  __shared__ bool is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * 16;
+  const int tile = blockIdx.x, slice = blockIdx.y;
+  const int row0 = tile * 16;
+  const int K = p.K, M = p.M, N = p.N;
   // Rows past N read the last row again; their results are not stored.
-  const bf16* w_lo = w + (size_t)min(row0 + g, N - 1) * K;
-  const bf16* w_hi = w + (size_t)min(row0 + g + 8, N - 1) * K;
+  const bf16* w_lo = p.w + (size_t)min(row0 + g, N - 1) * K;
+  const bf16* w_hi = p.w + (size_t)min(row0 + g + 8, N - 1) * K;
   const bf16* xr[NT];
 #pragma unroll
-  for (int j = 0; j < NT; ++j) xr[j] = x + (size_t)min(j * 8 + g, M - 1) * K;
+  for (int j = 0; j < NT; ++j) xr[j] = p.x + (size_t)min(j * 8 + g, M - 1) * K;
 
   float acc[NT][4];
 #pragma unroll
@@ -51,21 +90,21 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
 
-  const int kblocks = (K + 31) / 32;
+  const int k_begin = slice * p.slice_k, k_end = min(K, k_begin + p.slice_k);
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int kb0 = warp; kb0 < kblocks; kb0 += kSkinnyWarps * kUnroll) {
-    uint4 wl[kUnroll], wh[kUnroll];
+  for (int pass = k_begin; pass < k_end; pass += kSlicePass) {
+    uint4 wl[kBlocksPerWarp], wh[kBlocksPerWarp];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int k = (kb0 + u * kSkinnyWarps) * 32 + 8 * t;
-      const bool in = k < K;
+    for (int u = 0; u < kBlocksPerWarp; ++u) {
+      const int k = pass + (u * kSkinnyWarps + warp) * 32 + 8 * t;
+      const bool in = k < k_end;
       wl[u] = in ? ldg_stream(w_lo + k) : zero;
       wh[u] = in ? ldg_stream(w_hi + k) : zero;
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int k = (kb0 + u * kSkinnyWarps) * 32 + 8 * t;
-      const bool in = k < K;
+    for (int u = 0; u < kBlocksPerWarp; ++u) {
+      const int k = pass + (u * kSkinnyWarps + warp) * 32 + 8 * t;
+      const bool in = k < k_end;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         const uint4 xv = (in && j * 8 + g < M) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
@@ -84,22 +123,70 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     partial[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < 16 * NT * 8; e += kSkinnyWarps * 32) {
-    const int r = e % 16, m = e / 16;     // consecutive threads write consecutive output columns
-    const int n = row0 + r;
-    if (m >= M || n >= N) continue;
+
+  // Sum of the four warps, kept in partial[0].
+  for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
+    const int r = e % 16, m = e / 16;
     float sum = 0.f;
 #pragma unroll
     for (int wv = 0; wv < kSkinnyWarps; ++wv) sum += partial[wv][r][m];
-    if (bias) sum += __bfloat162float(bias[n]);
-    out[(size_t)m * N + n] = __float2bfloat16_rn(sum);
+    partial[0][r][m] = sum;   // each element is read and written by this thread only
+  }
+
+  if (p.num_slices > 1) {
+    float* mine = p.scratch + ((size_t)tile * p.num_slices + slice) * (16 * kCols);
+    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) mine[e] = partial[0][e % 16][e / 16];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned arrived = atomicAdd(&p.counters[tile], 1u);
+      is_last = arrived == (unsigned)p.num_slices - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float* all = p.scratch + (size_t)tile * p.num_slices * (16 * kCols);
+    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
+      float sum = 0.f;
+      for (int s = 0; s < p.num_slices; ++s) sum += __ldcg(all + (size_t)s * (16 * kCols) + e);
+      partial[0][e % 16][e / 16] = sum;
+    }
+    if (threadIdx.x == 0) p.counters[tile] = 0;   // ready for the next launch
+  }
+  __syncthreads();
+
+  if (p.gated_act < 0) {
+    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
+      const int r = e % 16, m = e / 16;     // consecutive threads write consecutive output columns
+      const int n = row0 + r;
+      if (m >= M || n >= N) continue;
+      float sum = partial[0][r][m];
+      if (p.bias) sum += __bfloat162float(p.bias[n]);
+      p.out[(size_t)m * N + n] = __float2bfloat16_rn(sum);
+    }
+  } else {
+    const int half = N / 2;                 // rows [0, 8) of the tile are gate rows, [8, 16) their up rows
+    for (int e = threadIdx.x; e < 8 * kCols; e += kSkinnyWarps * 32) {
+      const int r = e % 8, m = e / 8;
+      const int n = tile * 8 + r;
+      if (m >= M || n >= half) continue;
+      float gate = partial[0][r][m], up = partial[0][r + 8][m];
+      if (p.bias) {
+        gate += __bfloat162float(p.bias[row0 + r]);
+        up += __bfloat162float(p.bias[row0 + r + 8]);
+      }
+      // The products are rounded to bfloat16 before the activation, as a separate kernel would see them.
+      gate = __bfloat162float(__float2bfloat16_rn(gate));
+      up = __bfloat162float(__float2bfloat16_rn(up));
+      p.out[(size_t)m * half + n] = __float2bfloat16_rn(gated(gate, up, p.gated_act));
+    }
   }
 }
 
 template <int NT>
-int launch_skinny(const void* x, const void* w, const void* bias, void* out, int M, int N, int K, cudaStream_t s) {
-  gemm_skinny_kernel<NT><<<(N + 15) / 16, kSkinnyWarps * 32, 0, s>>>((const bf16*)x, (const bf16*)w,
-                                                                   (const bf16*)bias, (bf16*)out, M, N, K);
+int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
+  const dim3 grid((p.N + 15) / 16, p.num_slices);
+  gemm_skinny_kernel<NT><<<grid, kSkinnyWarps * 32, 0, s>>>(p);
   LI_LAUNCH_CHECK();
 }
 
@@ -107,14 +194,50 @@ int launch_skinny(const void* x, const void* w, const void* bias, void* out, int
 
 using namespace li;
 
-// bfloat16 only; 1 <= M <= 64; K a multiple of 8 and 16-byte aligned rows.
+// How the kernel would cut k for these sizes: (slices, k per slice).  Slices are at least 512 wide and are
+// used only while there are too few 16-row tiles to occupy the GPU.
+LI_EXPORT int li_gemm_skinny_slices(int N, int K, int* slice_k) {
+  const int tiles = (N + 15) / 16;
+  int slices = 1024 / tiles;
+  const int most = K / 512;
+  if (slices > most) slices = most;
+  if (slices < 1) slices = 1;
+  int per = (K + slices - 1) / slices;
+  per = (per + 31) / 32 * 32;
+  slices = (K + per - 1) / per;
+  if (slice_k) *slice_k = per;
+  return slices;
+}
+
+// bfloat16 only; 1 <= M <= 64; K a multiple of 8 and 16-byte aligned rows.  scratch (float) and counters
+// (unsigned, all zero) are needed when li_gemm_skinny_slices(N, K) > 1: scratch_floats must be at least
+// tiles * slices * 16 * 8 * ceil(M/8) and num_counters at least tiles, with tiles = ceil(N/16).
+// gated_act: -1 plain; 0 silu, 1 gelu, 2 gelu-tanh, 3 relu on rows interleaved in eights (N a multiple of 16);
+// out is then [M, N/2].
 LI_EXPORT int li_gemm_skinny(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                             cudaStream_t stream) {
+                             int gated_act, float* scratch, size_t scratch_floats, unsigned* counters,
+                             int num_counters, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (M > 64 || K < 8 || (K % 8)) return LI_ERR_UNSUPPORTED;
+  if (gated_act > 3 || (gated_act >= 0 && (N % 16))) return LI_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(w)) return LI_ERR_ALIGNMENT;
-  if (M <= 8) return launch_skinny<1>(x, w, bias, out, M, N, K, stream);
-  if (M <= 16) return launch_skinny<2>(x, w, bias, out, M, N, K, stream);
-  if (M <= 32) return launch_skinny<4>(x, w, bias, out, M, N, K, stream);
-  return launch_skinny<8>(x, w, bias, out, M, N, K, stream);
+  SkinnyParams p{(const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)out, M, N, K, 0, 1, gated_act,
+                 scratch, counters};
+  p.num_slices = li_gemm_skinny_slices(N, K, &p.slice_k);
+  const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+  const int tiles = (N + 15) / 16;
+  if (p.num_slices > 1) {
+    const size_t need = (size_t)tiles * p.num_slices * 16 * 8 * nt;
+    if (!scratch || !counters || scratch_floats < need || num_counters < tiles) {
+      // Not enough scratch: run unsplit, which needs none.
+      p.num_slices = 1;
+      p.slice_k = (K + 31) / 32 * 32;
+    }
+  }
+  switch (nt) {
+    case 1: return launch_skinny<1>(p, stream);
+    case 2: return launch_skinny<2>(p, stream);
+    case 4: return launch_skinny<4>(p, stream);
+    default: return launch_skinny<8>(p, stream);
+  }
 }

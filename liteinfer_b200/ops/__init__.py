@@ -3,13 +3,17 @@
 from liteinfer_b200.ops.kernels import (  # noqa: F401
     ACTIVATIONS,
     act_mul,
+    act_mul_interleaved,
     add_,
     add_bias_,
     argmax,
     embedding,
     decode_splits_for,
     gemm_simt,
+    gated_linear,
+    gated_linear_supported,
     gemm_skinny,
+    gemm_skinny_slices,
     mma_attention_supports,
     linear,
     paged_attention,

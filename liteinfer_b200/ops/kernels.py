@@ -34,6 +34,7 @@ _SIGNATURES = {
     "li_add": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
     "li_add_bias": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "li_act_mul": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
+    "li_act_mul_interleaved": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
     "li_rope_kv_write": ("rope_cache", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "li_paged_attention_generic": ("attention_generic", [
@@ -42,8 +43,11 @@ _SIGNATURES = {
     "li_paged_attention_mma": ("attention_mma", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
-        c_int, c_void_p]),
-    "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+        c_void_p]),
+    "li_paged_attention_mma_counters": ("attention_mma", [c_int, c_int, c_int, c_int]),
+    "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_void_p, c_size_t, c_void_p, c_int, c_void_p]),
+    "li_gemm_skinny_slices": ("gemm_skinny", [c_int, c_int, c_void_p]),
     "li_gemm_simt": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "li_sample": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -97,6 +101,32 @@ def _on_gpu(*tensors: torch.Tensor | None) -> None:
                 f"(got a tensor on {t.device})")
         if not t.is_contiguous():
             raise KernelLibraryError("kernels take contiguous tensors")
+
+
+class _Scratch:
+    """Per-device scratch that split kernels leave partial results in, and their arrival counters.
+
+    The counters are zero between launches (the kernels reset them); the buffers live as long as the
+    process, so CUDA graphs may hold their addresses."""
+
+    GEMM_FLOATS = 1 << 21
+    GEMM_COUNTERS = 1 << 12
+    ATTENTION_COUNTERS = 1 << 16
+
+    def __init__(self, device: torch.device) -> None:
+        self.gemm = torch.empty(self.GEMM_FLOATS, dtype=torch.float32, device=device)
+        self.gemm_counters = torch.zeros(self.GEMM_COUNTERS, dtype=torch.int32, device=device)
+        self.attention_counters = torch.zeros(self.ATTENTION_COUNTERS, dtype=torch.int32, device=device)
+
+
+_scratch: dict[torch.device, _Scratch] = {}
+
+
+def scratch_for(device: torch.device) -> _Scratch:
+    found = _scratch.get(device)
+    if found is None:
+        found = _scratch[device] = _Scratch(device)
+    return found
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -190,9 +220,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch
                                    _stream()), "gemm_simt")
         return out
     if 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and K >= 8:
-        _check(_fn("li_gemm_skinny")(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
-                                     _stream()), "gemm_skinny")
-        return out
+        return _skinny(x, weight, out, bias, -1)
     if M > 0:
         torch.mm(x, weight.t(), out=out)
         if bias is not None:
@@ -205,15 +233,23 @@ SKINNY_MAX_ROWS = 64
 NUM_SMS = 148
 
 
+def _skinny(x, weight, out, bias, gated_act: int) -> torch.Tensor:
+    M, K = x.shape
+    N = weight.shape[0]
+    ws = scratch_for(x.device)
+    _check(_fn("li_gemm_skinny")(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, gated_act,
+                                 ws.gemm.data_ptr(), ws.gemm.numel(), ws.gemm_counters.data_ptr(),
+                                 ws.gemm_counters.numel(), _stream()), "gemm_skinny")
+    return out
+
+
 def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """The weight-streaming bfloat16 product for at most 64 rows of x."""
     _on_gpu(x, weight, out, bias)
     M, K = x.shape
     N = weight.shape[0]
     assert weight.shape[1] == K and out.shape == (M, N) and x.dtype == weight.dtype == out.dtype == torch.bfloat16
-    _check(_fn("li_gemm_skinny")(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, _stream()),
-           "gemm_skinny")
-    return out
+    return _skinny(x, weight, out, bias, -1)
 
 
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
@@ -224,6 +260,39 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: to
     assert weight.shape[1] == K and out.shape == (M, N) and x.dtype == weight.dtype == out.dtype
     _check(_fn("li_gemm_simt")(_code(x), x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
                                _stream()), "gemm_simt")
+    return out
+
+
+def gemm_skinny_slices(N: int, K: int) -> int:
+    """Into how many slices the weight-streaming kernel cuts k for a weight of [N, K]."""
+    return int(_fn("li_gemm_skinny_slices")(N, K, None))
+
+
+def gated_linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    M, K = x.shape
+    return (x.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and K >= 8
+            and weight.shape[0] % 16 == 0)
+
+
+def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, activation: str,
+                 bias: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N/2] = act(gate) * up, where `weight` [N, K] holds gate and up rows interleaved in eights
+    (rows 16b..16b+7 are gate rows 8b..8b+7, rows 16b+8..16b+15 their up rows): product, activation and
+    multiply in one kernel.  bfloat16, at most 64 rows of x."""
+    _on_gpu(x, weight, out, bias)
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and out.shape == (M, N // 2) and gated_linear_supported(x, weight)
+    return _skinny(x, weight, out, bias, ACTIVATIONS[activation])
+
+
+def act_mul_interleaved(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> torch.Tensor:
+    """`act_mul` for a gate_up whose columns are interleaved in eights like `gated_linear`'s weight rows."""
+    _on_gpu(gate_up, out)
+    rows, width = out.shape
+    assert gate_up.shape == (rows, 2 * width) and gate_up.dtype == out.dtype and width % 8 == 0
+    _check(_fn("li_act_mul_interleaved")(_code(out), gate_up.data_ptr(), out.data_ptr(), rows, width,
+                                         ACTIVATIONS[activation], _stream()), "act_mul_interleaved")
     return out
 
 
@@ -277,22 +346,27 @@ def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, q
 
 
 def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
-                        seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0, num_splits=1,
-                        token_index=None, num_tokens=0) -> torch.Tensor:
-    """The tensor-core kernel (bfloat16, head size 64 or 128); `num_splits` > 1 splits every sequence's keys."""
-    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index, token_index)
+                        seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0,
+                        num_splits=1) -> torch.Tensor:
+    """The tensor-core kernel (bfloat16, head size 64 or 128); `num_splits` > 1 splits every sequence's keys
+    over that many blocks, the last of which merges the partial results."""
+    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
     pages, kvh, page_size, hd = k_pool.shape
-    partial_out = partial_lse = None
+    partial_out = partial_lse = counters = None
     if num_splits > 1:
         total = q.shape[0] * heads * num_splits
         partial_out = torch.empty((total, head_dim), dtype=torch.float32, device=q.device)
         partial_lse = torch.empty((total,), dtype=torch.float32, device=q.device)
+        need = int(_fn("li_paged_attention_mma_counters")(num_seqs, max_q_len, heads, kv_heads))
+        counters = scratch_for(q.device).attention_counters
+        if need > counters.numel():
+            counters = torch.zeros(need, dtype=torch.int32, device=q.device)
     _check(_fn("li_paged_attention_mma")(
         q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
         _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
-        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(token_index), num_tokens,
-        _stream()), "paged_attention_mma")
+        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters), _stream()),
+        "paged_attention_mma")
     return out
 
 
@@ -331,7 +405,7 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
         bound = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window)
         splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound)
         paged_attention_mma(*common, plan.decode_seqs, plan.num_decode, 1, heads, kv_heads, head_dim, scale,
-                            window, splits, plan.decode_tokens, plan.num_decode)
+                            window, splits)
     return out
 
 

@@ -28,6 +28,7 @@ class GatedMLP:
         self.hidden_size, self.intermediate_size, self.activation, self.bias = (
             hidden_size, intermediate_size, activation, bias)
         self.gate_up_weight = self.gate_up_bias = self.down_weight = self.down_bias = None
+        self.interleaved = False
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         i, h = self.intermediate_size, self.hidden_size
@@ -39,18 +40,35 @@ class GatedMLP:
         return specs
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.gate_up_weight = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]])
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        # bfloat16: gate and up rows interleaved in eights, the layout whose product, activation and
+        # multiply one decode kernel can do together; otherwise gate rows first, then up rows.
+        self.interleaved = gate.dtype == torch.bfloat16 and self.intermediate_size % 8 == 0
+        self.gate_up_weight = self._pair(gate, up)
         self.down_weight = tensors["down_proj.weight"]
         if self.bias:
-            self.gate_up_bias = torch.cat([tensors["gate_proj.bias"], tensors["up_proj.bias"]])
+            self.gate_up_bias = self._pair(tensors["gate_proj.bias"], tensors["up_proj.bias"])
             self.down_bias = tensors["down_proj.bias"]
+
+    def _pair(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        if not self.interleaved:
+            return torch.cat([gate, up])
+        rest = gate.shape[1:]
+        stacked = torch.stack([gate.reshape(-1, 8, *rest), up.reshape(-1, 8, *rest)], dim=1)
+        return stacked.reshape(2 * gate.shape[0], *rest).contiguous()
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         tokens = x.shape[0]
-        gate_up = torch.empty((tokens, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.linear(x, self.gate_up_weight, gate_up, self.gate_up_bias)
         hidden = torch.empty((tokens, self.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.act_mul(gate_up, hidden, self.activation)
+        if self.interleaved and ops.gated_linear_supported(x, self.gate_up_weight):
+            ops.gated_linear(x, self.gate_up_weight, hidden, self.activation, self.gate_up_bias)
+        else:
+            gate_up = torch.empty((tokens, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
+            ops.linear(x, self.gate_up_weight, gate_up, self.gate_up_bias)
+            if self.interleaved:
+                ops.act_mul_interleaved(gate_up, hidden, self.activation)
+            else:
+                ops.act_mul(gate_up, hidden, self.activation)
         out = torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device)
         return ops.linear(hidden, self.down_weight, out, self.down_bias)
 

@@ -384,3 +384,55 @@ def test_split_policy():
     assert decode_splits_for(1, 8, 4096) == 32
     assert 2 <= decode_splits_for(8, 8, 4096) <= 16
     assert decode_splits_for(64, 8, 4096) == 1
+
+
+def _interleave(gate, up):
+    rest = gate.shape[1:]
+    return torch.stack([gate.reshape(-1, 8, *rest), up.reshape(-1, 8, *rest)], dim=1).reshape(2 * gate.shape[0], *rest).contiguous()
+
+
+@pytest.mark.parametrize("M", [1, 8, 33])
+@pytest.mark.parametrize("inter,K,act", [(8192, 2048, "silu"), (112, 120, "gelu_pytorch_tanh"), (176, 64, "relu")])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gated_linear_is_product_activation_and_multiply_in_one(M, inter, K, act, with_bias):
+    from liteinfer_b200 import ops
+
+    dt = torch.bfloat16
+    x = _randn(M, K, dtype=dt)
+    gate, up = _randn(inter, K, dtype=dt, seed=1, scale=0.05), _randn(inter, K, dtype=dt, seed=2, scale=0.05)
+    bg, bu = _randn(inter, dtype=dt, seed=3), _randn(inter, dtype=dt, seed=4)
+    w = _interleave(gate, up)
+    b = _interleave(bg, bu) if with_bias else None
+    got = ops.gated_linear(x, w, torch.empty(M, inter, dtype=dt, device="cuda"), act, b)
+    # the same thing in two kernels, through the same layout: bit for bit
+    gu = ops.linear(x, w, torch.empty(M, 2 * inter, dtype=dt, device="cuda"), b)
+    two = ops.act_mul_interleaved(gu, torch.empty(M, inter, dtype=dt, device="cuda"), act)
+    assert torch.equal(got, two)
+    # and the plain formula on the plain layout
+    gu_plain = torch.cat([x.double() @ gate.double().t() + (bg.double() if with_bias else 0),
+                          x.double() @ up.double().t() + (bu.double() if with_bias else 0)], dim=1).to(dt)
+    want = ref.act_mul(gu_plain, torch.empty(M, inter, dtype=dt, device="cuda"), act)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2 ** -6, atol=2 ** -6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_act_mul_interleaved(dtype):
+    from liteinfer_b200 import ops
+
+    gu = _randn(5, 2 * 176, dtype=dtype, scale=2.0)
+    got = ops.act_mul_interleaved(gu, torch.empty(5, 176, dtype=dtype, device="cuda"), "silu")
+    want = ref.act_mul_interleaved(gu, torch.empty(5, 176, dtype=dtype, device="cuda"), "silu")
+    torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
+
+
+def test_skinny_slices_leave_their_counters_at_zero():
+    from liteinfer_b200 import ops
+    from liteinfer_b200.ops.kernels import scratch_for
+
+    assert ops.gemm_skinny_slices(2048, 8192) == 8 and ops.gemm_skinny_slices(16384, 2048) == 1
+    x, w = _randn(8, 8192, dtype=torch.bfloat16), _randn(2048, 8192, dtype=torch.bfloat16, seed=1, scale=0.02)
+    outs = [ops.gemm_skinny(x, w, torch.empty(8, 2048, dtype=torch.bfloat16, device="cuda")) for _ in range(3)]
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    torch.cuda.synchronize()
+    assert int(scratch_for(x.device).gemm_counters.abs().sum()) == 0
+    assert int(scratch_for(x.device).attention_counters.abs().sum()) == 0

@@ -71,6 +71,24 @@ def act_mul(gate_up, out, activation):
     return out
 
 
+def act_mul_interleaved(gate_up, out, activation):
+    rows, w = out.shape
+    pairs = gate_up.float().view(rows, w // 8, 2, 8)
+    g, u = pairs[:, :, 0].reshape(rows, w), pairs[:, :, 1].reshape(rows, w)
+    out.copy_((_r(_activate(g, activation), out.dtype) * u).to(out.dtype))
+    return out
+
+
+def gated_linear_supported(x, weight):
+    return False
+
+
+def gated_linear(x, weight, out, activation, bias=None):
+    gate_up = torch.empty(x.shape[0], weight.shape[0], dtype=x.dtype, device=x.device)
+    linear(x, weight, gate_up, bias)
+    return act_mul_interleaved(gate_up, out, activation)
+
+
 def linear(x, weight, out, bias=None):
     y = x.float() @ weight.float().t()
     if bias is not None:
@@ -187,5 +205,5 @@ def sample(logits, temperature, top_k, top_p, uniform, out):
     return out
 
 
-ALL = ("embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "linear", "gemm_simt", "rope_kv_write",
-       "paged_attention", "argmax", "sample")
+ALL = ("embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
+       "gated_linear", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
