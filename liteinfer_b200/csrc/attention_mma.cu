@@ -114,10 +114,14 @@ template <int D, bool kDecode>
 __global__ void __launch_bounds__(kWarps * 32)
 attention_mma_kernel(const AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* qs = reinterpret_cast<bf16*>(smem_raw);           // [64][D]
-  bf16* kbuf = qs + kBlockM * D;                          // 2 x [64][D]
-  bf16* vbuf = kbuf + 2 * kBlockN * D;                    // 2 x [64][D]
+  constexpr int kStages = kDecode ? (D == 64 ? 4 : 3) : 2;   // K/V tiles in flight per block
+  constexpr int kQRows = kDecode ? 16 : kBlockM;
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);           // [kQRows][D]
+  bf16* kbuf = qs + kQRows * D;                           // kStages x [64][D]
+  bf16* vbuf = kbuf + kStages * kBlockN * D;              // kStages x [64][D]
   __shared__ bool is_last;
+  grid_launch_dependents();
+  grid_dependency_wait();   // q and the newest keys and values come from the kernels before
 
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
   const int kvh = blockIdx.y;
@@ -147,7 +151,6 @@ attention_mma_kernel(const AttnParams p) {
   const int my_lo = tile_lo + split * per_split, my_hi = min(tile_hi, my_lo + per_split);
 
   // ---- Q tile -> shared (zero rows beyond rows_used), then A fragments in registers.
-  constexpr int kQRows = kDecode ? 16 : kBlockM;
   for (int c = threadIdx.x; c < kQRows * kChunks; c += kWarps * 32) {
     const int row = c / kChunks, chunk = c % kChunks;
     const bool valid = row < rows_used;
@@ -156,9 +159,14 @@ attention_mma_kernel(const AttnParams p) {
     cp_async16(tile_ptr<D>(qs, row, chunk), src, valid);
   }
   cp_async_commit();
-  if (my_lo < my_hi) load_kv_tile<D>(kbuf, vbuf, p, table, kvh, my_lo * kBlockN, lo, hi);
-  cp_async_commit();
-  cp_async_wait<1>();
+  // The first kStages-1 tiles are requested at once; a group is committed per tile even when it is empty.
+#pragma unroll
+  for (int st = 0; st < kStages - 1; ++st) {
+    if (my_lo + st < my_hi)
+      load_kv_tile<D>(kbuf + st * kBlockN * D, vbuf + st * kBlockN * D, p, table, kvh, (my_lo + st) * kBlockN, lo, hi);
+    cp_async_commit();
+  }
+  cp_async_wait<kStages - 1>();   // the Q tile has landed
   __syncthreads();
 
   unsigned qf[D / 16][4];
@@ -182,14 +190,16 @@ attention_mma_kernel(const AttnParams p) {
     for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
 
   for (int tile = my_lo; tile < my_hi; ++tile) {
-    const int buf = (tile - my_lo) & 1;
+    const int buf = (tile - my_lo) % kStages;
     bf16* ks = kbuf + buf * kBlockN * D;
     bf16* vs = vbuf + buf * kBlockN * D;
-    if (tile + 1 < my_hi)
-      load_kv_tile<D>(kbuf + (buf ^ 1) * kBlockN * D, vbuf + (buf ^ 1) * kBlockN * D, p, table, kvh,
-                      (tile + 1) * kBlockN, lo, hi);
+    {
+      const int ahead = tile + kStages - 1, abuf = (ahead - my_lo) % kStages;
+      if (ahead < my_hi)
+        load_kv_tile<D>(kbuf + abuf * kBlockN * D, vbuf + abuf * kBlockN * D, p, table, kvh, ahead * kBlockN, lo, hi);
+    }
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<kStages - 1>();   // all but the newest kStages-1 groups are complete: this tile is here
     __syncthreads();
 
     // S = Q K^T for 16 rows x (16 keys per group).
@@ -381,7 +391,8 @@ template <int D, bool kDecode>
 int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
   const int groups = p.heads / p.kv_heads;
   const int tq = (kDecode ? 16 : kBlockM) / groups;
-  const size_t smem = (size_t)(kBlockM + 4 * kBlockN) * D * sizeof(bf16);
+  constexpr int kStages = kDecode ? (D == 64 ? 4 : 3) : 2;
+  const size_t smem = (size_t)((kDecode ? 16 : kBlockM) + 2 * kStages * kBlockN) * D * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D, kDecode>,
@@ -390,8 +401,7 @@ int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, cudaStrea
     configured = true;
   }
   const dim3 grid(((max_q_len + tq - 1) / tq) * p.num_splits, p.kv_heads, num_seqs);
-  attention_mma_kernel<D, kDecode><<<grid, kWarps * 32, smem, stream>>>(p);
-  LI_LAUNCH_CHECK();
+  return (int)launch_pdl(attention_mma_kernel<D, kDecode>, grid, dim3(kWarps * 32), smem, stream, p);
 }
 
 }  // namespace li

@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define LI_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -90,6 +91,41 @@ template <typename T> __device__ __forceinline__ Vec16<T> load16(const T* p) {
 }
 template <typename T> __device__ __forceinline__ void store16(T* p, const Vec16<T>& v) {
   *reinterpret_cast<decltype(v.raw)*>(p) = v.raw;
+}
+
+// ---- programmatic dependent launch -------------------------------------------------------------
+// Every kernel of this library is launched so that it may start while the kernel before it in the
+// stream is still running.  What a kernel does before `grid_dependency_wait()` must not read what
+// earlier kernels write, nor write anything at all: only prefetches of weights belong there.  After the
+// wait, everything earlier kernels wrote is visible.  `grid_launch_dependents()` lets the next kernel
+// start its own prologue.  Both are no-ops when the kernel was launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" :::); }
+
+inline bool pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("LITEINFER_PDL");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+// Launches `kernel` with programmatic stream serialization (unless LITEINFER_PDL=0).
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -16,6 +16,8 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
                                  int width, int vocab, int* __restrict__ error_flag) {
   const int t = blockIdx.x;
+  grid_launch_dependents();
+  grid_dependency_wait();
   int id = ids[t];
   if (id < 0 || id >= vocab) {  // a token id outside the table: record it, write zeros, read nothing
     if (threadIdx.x == 0 && error_flag) atomicExch(error_flag, 1);
@@ -42,6 +44,8 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, c
                                int write_residual) {
   __shared__ float scratch[33];
   const int r = blockIdx.x;
+  grid_launch_dependents();
+  grid_dependency_wait();
   const size_t src_row = rows ? (size_t)rows[r] : (size_t)r;
   T* xr = x + src_row * width;
   const T* dr = delta ? delta + src_row * width : nullptr;
@@ -63,6 +67,61 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, c
     if (dr && !write_residual) v = round_to<T>(v + to_float(dr[i]));
     const float normed = round_to<T>(v * inv);
     outr[i] = from_float<T>(to_float(weight[i]) * normed);
+  }
+}
+
+// The same, with the row held in registers between the two passes: VPT 16-byte vectors per thread.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256)
+rmsnorm_reg_kernel(T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ weight, T* __restrict__ out,
+                   const int* __restrict__ rows, int width, float eps, int write_residual) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int vectors = width / N;
+  grid_launch_dependents();
+  Vec16<T> w[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) w[i] = load16(weight + v * N);      // the weight waits for nobody
+  }
+  grid_dependency_wait();
+  const size_t src_row = rows ? (size_t)rows[r] : (size_t)r;
+  T* xr = x + src_row * width;
+  const T* dr = delta ? delta + src_row * width : nullptr;
+  float vals[VPT][N];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) {
+      Vec16<T> xv = load16(xr + v * N);
+      if (dr) {
+        const Vec16<T> dv = load16(dr + v * N);
+#pragma unroll
+        for (int k = 0; k < N; ++k) xv.set(k, xv.get(k) + dv.get(k));    // rounded to T by set()
+        if (write_residual) store16(xr + v * N, xv);
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        vals[i][k] = xv.get(k);
+        ss += vals[i][k] * vals[i][k];
+      }
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  T* outr = out + (size_t)r * width;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) {
+      Vec16<T> o;
+#pragma unroll
+      for (int k = 0; k < N; ++k) o.set(k, w[i].get(k) * round_to<T>(vals[i][k] * inv));
+      store16(outr + v * N, o);
+    }
   }
 }
 
@@ -156,18 +215,27 @@ template <typename T>
 int launch_embedding(const int* ids, const void* table, void* out, int tokens, int width, int vocab,
                      int* error_flag, cudaStream_t s) {
   if (tokens == 0) return 0;
-  embedding_kernel<T><<<tokens, 128, 0, s>>>(ids, (const T*)table, (T*)out, width, vocab, error_flag);
-  LI_LAUNCH_CHECK();
+  return (int)launch_pdl(embedding_kernel<T>, dim3(tokens), dim3(128), 0, s, ids, (const T*)table, (T*)out, width,
+                         vocab, error_flag);
 }
 
 template <typename T>
 int launch_rmsnorm(void* x, const void* delta, const void* weight, void* out, const int* rows, int out_rows,
                    int width, float eps, int write_residual, cudaStream_t s) {
   if (out_rows == 0) return 0;
+  constexpr int N = Vec16<T>::N;
+  const bool vector_ok = width % N == 0 && aligned16(x) && aligned16(weight) && aligned16(out) &&
+                         (!delta || aligned16(delta)) && ((size_t)width * sizeof(T)) % 16 == 0;
+  const int need = vector_ok ? (width / N + 255) / 256 : 99;
+  T* xp = (T*)x;
+  const T *dp = (const T*)delta, *wp = (const T*)weight;
+  T* op = (T*)out;
+  if (need <= 1) return (int)launch_pdl(rmsnorm_reg_kernel<T, 1>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
+  if (need <= 2) return (int)launch_pdl(rmsnorm_reg_kernel<T, 2>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
+  if (need <= 4) return (int)launch_pdl(rmsnorm_reg_kernel<T, 4>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
   const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  rmsnorm_kernel<T><<<out_rows, block, 0, s>>>((T*)x, (const T*)delta, (const T*)weight, (T*)out, rows, width, eps,
-                                               write_residual);
-  LI_LAUNCH_CHECK();
+  return (int)launch_pdl(rmsnorm_kernel<T>, dim3(out_rows), dim3(block), 0, s, xp, dp, wp, op, rows, width, eps,
+                         write_residual);
 }
 
 template <typename T>

@@ -92,6 +92,8 @@ gemm_skinny_kernel(const SkinnyParams p) {
 
   const int k_begin = slice * p.slice_k, k_end = min(K, k_begin + p.slice_k);
   const uint4 zero = make_uint4(0, 0, 0, 0);
+  grid_launch_dependents();
+  bool waited = false;
   for (int pass = k_begin; pass < k_end; pass += kSlicePass) {
     uint4 wl[kBlocksPerWarp], wh[kBlocksPerWarp];
 #pragma unroll
@@ -100,6 +102,11 @@ gemm_skinny_kernel(const SkinnyParams p) {
       const bool in = k < k_end;
       wl[u] = in ? ldg_stream(w_lo + k) : zero;
       wh[u] = in ? ldg_stream(w_hi + k) : zero;
+    }
+    // The weights above depend on no earlier kernel and are already on their way; x does.
+    if (!waited) {
+      grid_dependency_wait();
+      waited = true;
     }
 #pragma unroll
     for (int u = 0; u < kBlocksPerWarp; ++u) {
@@ -114,6 +121,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
     }
   }
 
+  if (!waited) grid_dependency_wait();
   // acc[j]: c0,c1 = (w row g, x rows j*8 + 2t, +1); c2,c3 = (w row g+8, same x rows).
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
@@ -186,8 +194,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
 template <int NT>
 int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
   const dim3 grid((p.N + 15) / 16, p.num_slices);
-  gemm_skinny_kernel<NT><<<grid, kSkinnyWarps * 32, 0, s>>>(p);
-  LI_LAUNCH_CHECK();
+  return (int)launch_pdl(gemm_skinny_kernel<NT>, grid, dim3(kSkinnyWarps * 32), 0, s, p);
 }
 
 }  // namespace li

@@ -25,7 +25,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      int rotary_dim, int page_size, int num_pages) {
   extern __shared__ float cs[];  // cos[half], sin[half]
   const int t = blockIdx.x;
-  const int pos = positions[t];
+  grid_launch_dependents();
+  const int pos = positions[t];   // positions, tables and inv_freq are inputs of the step, not of a kernel
   const int half = rotary_dim / 2;
   float* cosv = cs;
   float* sinv = cs + half;
@@ -34,6 +35,9 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     cosv[i] = cosf(angle);
     sinv[i] = sinf(angle);
   }
+  const int seq = seq_of_token[t];
+  const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+  grid_dependency_wait();           // q, k and v come from the projection before this kernel
   __syncthreads();
 
   const int row_width = (heads + 2 * kv_heads) * head_dim;
@@ -51,8 +55,6 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
   (void)pass;
 
-  const int seq = seq_of_token[t];
-  const int page = block_table[(size_t)seq * table_stride + pos / page_size];
   if (page < 0 || page >= num_pages) return;
   const int slot = pos % page_size;
 
@@ -90,12 +92,10 @@ LI_EXPORT int li_rope_kv_write(int dtype, void* qkv, const int* positions, const
   if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
   const int block = 256;
   if (dtype == kFloat32)
-    rope_kv_write_kernel<float><<<tokens, block, smem, stream>>>(
-        (float*)qkv, positions, seq_of_token, block_table, table_stride, (float*)k_pool, (float*)v_pool, inv_freq,
-        heads, kv_heads, head_dim, rotary_dim, page_size, num_pages);
-  else
-    rope_kv_write_kernel<bf16><<<tokens, block, smem, stream>>>(
-        (bf16*)qkv, positions, seq_of_token, block_table, table_stride, (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads,
-        kv_heads, head_dim, rotary_dim, page_size, num_pages);
-  LI_LAUNCH_CHECK();
+    return (int)launch_pdl(rope_kv_write_kernel<float>, dim3(tokens), dim3(block), smem, stream, (float*)qkv,
+                           positions, seq_of_token, block_table, table_stride, (float*)k_pool, (float*)v_pool,
+                           inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size, num_pages);
+  return (int)launch_pdl(rope_kv_write_kernel<bf16>, dim3(tokens), dim3(block), smem, stream, (bf16*)qkv, positions,
+                         seq_of_token, block_table, table_stride, (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads,
+                         kv_heads, head_dim, rotary_dim, page_size, num_pages);
 }

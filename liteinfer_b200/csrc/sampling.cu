@@ -268,13 +268,74 @@ argmax_kernel(const T* __restrict__ logits, int vocab, int* __restrict__ out) {
   if (threadIdx.x == 0) out[blockIdx.x] = top.i;
 }
 
+// A row split over gridDim.y blocks: each finds the best of its chunk and leaves it in scratch; the block
+// that arrives last (a counter per row, reset by that block) picks the best of the chunks.
+constexpr int kArgmaxThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_split_kernel(const T* __restrict__ logits, int vocab, int chunk, float* __restrict__ part_value,
+                    int* __restrict__ part_index, unsigned* __restrict__ counters, int* __restrict__ out) {
+  __shared__ ArgMax scratch[32];
+  __shared__ bool is_last;
+  const int r = blockIdx.x, c = blockIdx.y, chunks = gridDim.y;
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const T* row = logits + (size_t)r * vocab;
+  const int lo = c * chunk, hi = min(vocab, lo + chunk);
+  ArgMax mine{-INFINITY, 0x7fffffff};
+  constexpr int N = Vec16<T>::N;
+  if ((((size_t)r * vocab + lo) * sizeof(T)) % 16 == 0 && aligned16(logits)) {
+    const int vec_hi = lo + (hi - lo) / N * N;
+    for (int i = lo + threadIdx.x * N; i < vec_hi; i += kArgmaxThreads * N) {
+      const Vec16<T> v = load16(row + i);
+#pragma unroll
+      for (int k = 0; k < N; ++k) mine = better(mine, ArgMax{v.get(k), i + k});
+    }
+    for (int i = vec_hi + threadIdx.x; i < hi; i += kArgmaxThreads) mine = better(mine, ArgMax{to_float(row[i]), i});
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += kArgmaxThreads) mine = better(mine, ArgMax{to_float(row[i]), i});
+  }
+  const ArgMax top = block_argmax(mine, scratch);
+  if (threadIdx.x == 0) {
+    part_value[(size_t)r * chunks + c] = top.v;
+    part_index[(size_t)r * chunks + c] = top.i;
+    __threadfence();
+    is_last = atomicAdd(&counters[r], 1u) == (unsigned)chunks - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (threadIdx.x == 0) {
+    ArgMax best{-INFINITY, 0x7fffffff};
+    for (int k = 0; k < chunks; ++k)
+      best = better(best, ArgMax{__ldcg(part_value + (size_t)r * chunks + k), __ldcg(part_index + (size_t)r * chunks + k)});
+    out[r] = best.i;
+    counters[r] = 0;
+  }
+}
+
 }  // namespace li
 
 using namespace li;
 
 // out[r] = index of the largest logit of row r (the lowest index among equals).
-LI_EXPORT int li_argmax(int dtype, const void* logits, int rows, int vocab, int* out, cudaStream_t stream) {
+// With scratch (part_value/part_index of rows*32 entries, counters of `rows` zeros) a row is split over
+// several blocks; without, one block scans a row.
+LI_EXPORT int li_argmax(int dtype, const void* logits, int rows, int vocab, int* out, float* part_value,
+                        int* part_index, unsigned* counters, int scratch_rows, cudaStream_t stream) {
   if (rows == 0) return 0;
+  int chunks = (vocab + 4095) / 4096;
+  if (chunks > 32) chunks = 32;
+  if (chunks > 1 && part_value && part_index && counters && rows <= scratch_rows && rows <= 65535) {
+    const int chunk = ((vocab + chunks - 1) / chunks + 7) / 8 * 8;
+    const dim3 grid(rows, (vocab + chunk - 1) / chunk);
+    if (dtype == kFloat32)
+      return (int)launch_pdl(argmax_split_kernel<float>, grid, dim3(kArgmaxThreads), 0, stream,
+                             (const float*)logits, vocab, chunk, part_value, part_index, counters, out);
+    return (int)launch_pdl(argmax_split_kernel<bf16>, grid, dim3(kArgmaxThreads), 0, stream, (const bf16*)logits,
+                           vocab, chunk, part_value, part_index, counters, out);
+  }
   if (dtype == kFloat32)
     argmax_kernel<float><<<rows, kThreads, 0, stream>>>((const float*)logits, vocab, out);
   else

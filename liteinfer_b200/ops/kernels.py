@@ -49,7 +49,8 @@ _SIGNATURES = {
                                        c_void_p, c_size_t, c_void_p, c_int, c_void_p]),
     "li_gemm_skinny_slices": ("gemm_skinny", [c_int, c_int, c_void_p]),
     "li_gemm_simt": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
-    "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_void_p]),
     "li_sample": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p]),
 }
@@ -112,11 +113,15 @@ class _Scratch:
     GEMM_FLOATS = 1 << 21
     GEMM_COUNTERS = 1 << 12
     ATTENTION_COUNTERS = 1 << 16
+    ARGMAX_ROWS = 4096
 
     def __init__(self, device: torch.device) -> None:
         self.gemm = torch.empty(self.GEMM_FLOATS, dtype=torch.float32, device=device)
         self.gemm_counters = torch.zeros(self.GEMM_COUNTERS, dtype=torch.int32, device=device)
         self.attention_counters = torch.zeros(self.ATTENTION_COUNTERS, dtype=torch.int32, device=device)
+        self.argmax_value = torch.empty(self.ARGMAX_ROWS * 32, dtype=torch.float32, device=device)
+        self.argmax_index = torch.empty(self.ARGMAX_ROWS * 32, dtype=torch.int32, device=device)
+        self.argmax_counters = torch.zeros(self.ARGMAX_ROWS, dtype=torch.int32, device=device)
 
 
 _scratch: dict[torch.device, _Scratch] = {}
@@ -329,7 +334,7 @@ def decode_splits_for(num_decode: int, kv_heads: int, max_context_len: int) -> i
     tiles = -(-max_context_len // 64)
     if tiles < 4:
         return 1
-    return max(1, min(4 * NUM_SMS // max(1, num_decode * kv_heads), tiles // 2, 32))
+    return max(1, min(3 * NUM_SMS // max(1, num_decode * kv_heads), tiles // 2, 32))
 
 
 def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
@@ -414,7 +419,10 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _on_gpu(logits, out)
     _int32(out, "out")
     rows, vocab = logits.shape
-    _check(_fn("li_argmax")(_code(logits), logits.data_ptr(), rows, vocab, out.data_ptr(), _stream()), "argmax")
+    ws = scratch_for(logits.device)
+    _check(_fn("li_argmax")(_code(logits), logits.data_ptr(), rows, vocab, out.data_ptr(), ws.argmax_value.data_ptr(),
+                            ws.argmax_index.data_ptr(), ws.argmax_counters.data_ptr(), ws.ARGMAX_ROWS, _stream()),
+           "argmax")
     return out
 
 
