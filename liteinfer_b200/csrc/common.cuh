@@ -128,6 +128,6 @@ inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 blo
   return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
 }
 
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+__host__ __device__ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace li
