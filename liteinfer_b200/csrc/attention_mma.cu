@@ -49,6 +49,7 @@ struct AttnParams {
   const int* context_lens;
   const int* seq_index;   // optional: batch row of each launched sequence
   int heads, kv_heads, page_size, num_pages;
+  int page_shift;         // log2(page_size) when it is a power of two, else -1
   float scale_log2;       // scale * log2(e)
   int window;
   int num_splits;
@@ -80,6 +81,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x for x <= 0 (and -inf -> 0) in one instruction; the argument is a score minus the running maximum.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -90,19 +97,27 @@ template <int D> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, 
   return base + row * D + ((chunk ^ (row & 7)) << 3);
 }
 
+// One K tile and one V tile of 64 keys -> shared memory.  A thread always copies the same 16-byte chunk
+// of a row and walks the keys in steps of (threads / chunks per row), so the index arithmetic of a tile
+// is a few instructions per copy; a page size that is a power of two is divided by shifting.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParams& p, const int* table, int kvh,
                                              int tile_start, int lo, int hi) {
   constexpr int kChunks = D / 8;
-  for (int c = threadIdx.x; c < kBlockN * kChunks; c += kWarps * 32) {
-    const int key = c / kChunks, chunk = c % kChunks;
+  constexpr int kKeysPerPass = kWarps * 32 / kChunks;
+  const int chunk = threadIdx.x % kChunks, key0 = threadIdx.x / kChunks;
+#pragma unroll
+  for (int pass = 0; pass < kBlockN / kKeysPerPass; ++pass) {
+    const int key = key0 + pass * kKeysPerPass;
     const int kpos = tile_start + key;
     bool valid = kpos >= lo && kpos < hi;
     size_t off = 0;
     if (valid) {
-      const int page = table[kpos / p.page_size];
+      const int block = p.page_shift >= 0 ? kpos >> p.page_shift : kpos / p.page_size;
+      const int slot = p.page_shift >= 0 ? kpos & (p.page_size - 1) : kpos - block * p.page_size;
+      const int page = table[block];
       valid = page >= 0 && page < p.num_pages;
-      if (valid) off = (((size_t)page * p.kv_heads + kvh) * p.page_size + kpos % p.page_size) * D + chunk * 8;
+      if (valid) off = (((size_t)page * p.kv_heads + kvh) * p.page_size + slot) * D + chunk * 8;
     }
     cp_async16(tile_ptr<D>(ks, key, chunk), p.k_pool + off, valid);
     cp_async16(tile_ptr<D>(vs, key, chunk), p.v_pool + off, valid);
@@ -114,13 +129,12 @@ template <int D, bool kDecode>
 __global__ void __launch_bounds__(kWarps * 32)
 attention_mma_kernel(const AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  constexpr int kStages = kDecode ? (D == 64 ? 4 : 3) : 2;   // K/V tiles in flight per block
+  constexpr int kStages = 2;   // K/V tiles in flight per block
   constexpr int kQRows = kDecode ? 16 : kBlockM;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);           // [kQRows][D]
   bf16* kbuf = qs + kQRows * D;                           // kStages x [64][D]
   bf16* vbuf = kbuf + kStages * kBlockN * D;              // kStages x [64][D]
   __shared__ bool is_last;
-  grid_launch_dependents();
   grid_dependency_wait();   // q and the newest keys and values come from the kernels before
 
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
@@ -224,16 +238,30 @@ attention_mma_kernel(const AttnParams p) {
     // Scale, mask, online softmax.
     const int key0 = tile * kBlockN + key_group0 * 16;
     float tile_max[2] = {-INFINITY, -INFINITY};
+    // A tile needs the mask only where it meets the diagonal or the window's start.  (Rows of padding hold
+    // zero queries: their scores are finite, and they are never stored.)
+    const bool all_visible = (tile + 1) * kBlockN - 1 <= first_qpos &&
+                             (p.window <= 0 || tile * kBlockN > last_qpos - p.window);
+    if (all_visible) {
 #pragma unroll
-    for (int i = 0; i < kGroupsPerWarp * 2; ++i)
+      for (int i = 0; i < kGroupsPerWarp * 2; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int kpos = key0 + i * 8 + 2 * t + (j & 1);
-        const int qp = qpos[j >> 1];
-        const bool visible = kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
-        s[i][j] = visible ? s[i][j] * p.scale_log2 : -INFINITY;
-        tile_max[j >> 1] = fmaxf(tile_max[j >> 1], s[i][j]);
-      }
+        for (int j = 0; j < 4; ++j) {
+          s[i][j] *= p.scale_log2;
+          tile_max[j >> 1] = fmaxf(tile_max[j >> 1], s[i][j]);
+        }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kGroupsPerWarp * 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kpos = key0 + i * 8 + 2 * t + (j & 1);
+          const int qp = qpos[j >> 1];
+          const bool visible = kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
+          s[i][j] = visible ? s[i][j] * p.scale_log2 : -INFINITY;
+          tile_max[j >> 1] = fmaxf(tile_max[j >> 1], s[i][j]);
+        }
+    }
     float alpha[2], m_use[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -241,7 +269,7 @@ attention_mma_kernel(const AttnParams p) {
       tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
       const float m_new = fmaxf(m[h], tile_max[h]);
       m_use[h] = m_new == -INFINITY ? 0.f : m_new;
-      alpha[h] = exp2f(m[h] - m_use[h]);   // m = -inf gives 0
+      alpha[h] = fast_exp2(m[h] - m_use[h]);   // m = -inf gives 0
       m[h] = m_new;
     }
     float row_sum[2] = {0.f, 0.f};
@@ -251,7 +279,7 @@ attention_mma_kernel(const AttnParams p) {
       float e[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        e[j] = exp2f(s[i][j] - m_use[j >> 1]);
+        e[j] = fast_exp2(s[i][j] - m_use[j >> 1]);
         row_sum[j >> 1] += e[j];
       }
       pf[i >> 1][(i & 1) * 2] = pack_bf16(e[0], e[1]);
@@ -259,10 +287,13 @@ attention_mma_kernel(const AttnParams p) {
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) l[h] = l[h] * alpha[h] + row_sum[h];
+    // The accumulator is rescaled only when some row of the warp saw a new maximum.
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      }
     }
 
     // O += P V.
@@ -281,6 +312,7 @@ attention_mma_kernel(const AttnParams p) {
     __syncthreads();   // this buffer is overwritten by the load issued in the next iteration
   }
   cp_async_wait<0>();
+  grid_launch_dependents();
 
   // Row sums across the quad.
 #pragma unroll
@@ -367,22 +399,64 @@ attention_mma_kernel(const AttnParams p) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int e = threadIdx.x; e < rows_used * D; e += kWarps * 32) {
-    const int row = e / D, d = e % D;
-    const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-    const size_t base = ((size_t)(q_begin + qi) * p.heads + head) * p.num_splits;
-    float mx = -INFINITY;
-    for (int sidx = 0; sidx < p.num_splits; ++sidx) mx = fmaxf(mx, __ldcg(p.partial_lse + base + sidx));
-    float denom = 0.f, acc = 0.f;
-    for (int sidx = 0; sidx < p.num_splits; ++sidx) {
-      const float v = __ldcg(p.partial_lse + base + sidx);
-      if (v == -INFINITY) continue;
-      const float wgt = exp2f(v - mx);
-      denom += wgt;
-      acc += wgt * __ldcg(p.partial_out + (base + sidx) * D + d);
+  // All loads of a phase are issued before any is used: the merge costs a few trips to L2, not one per split.
+  constexpr int kMaxSplits = 32;
+  float* wsm = reinterpret_cast<float*>(smem_raw);              // [64 rows][kMaxSplits + 1] weights
+  const int S = p.num_splits;
+  __syncthreads();
+  for (int e0 = 0; e0 < rows_used * S; e0 += kWarps * 32 * 4) {
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = e0 + j * kWarps * 32 + threadIdx.x;
+      if (e < rows_used * S) {
+        const int row = e / S, sidx = e - row * S;
+        const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+        v[j] = __ldcg(p.partial_lse + ((size_t)(q_begin + qi) * p.heads + head) * S + sidx);
+      }
     }
-    p.out[(size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d] =
-        __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = e0 + j * kWarps * 32 + threadIdx.x;
+      if (e < rows_used * S) wsm[(e / S) * (kMaxSplits + 1) + (e % S)] = v[j];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < rows_used) {
+    float* w = wsm + threadIdx.x * (kMaxSplits + 1);
+    float mx = -INFINITY;
+    for (int sidx = 0; sidx < S; ++sidx) mx = fmaxf(mx, w[sidx]);
+    float denom = 0.f;
+    for (int sidx = 0; sidx < S; ++sidx) {
+      const float e = w[sidx] == -INFINITY ? 0.f : exp2f(w[sidx] - mx);
+      w[sidx] = e;
+      denom += e;
+    }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    for (int sidx = 0; sidx < S; ++sidx) w[sidx] *= inv;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < rows_used * (D / 4); e += kWarps * 32) {
+    const int row = e / (D / 4), d4 = e % (D / 4);
+    const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+    const float4* src = reinterpret_cast<const float4*>(
+        p.partial_out + ((size_t)(q_begin + qi) * p.heads + head) * S * D) + d4;
+    const float* w = wsm + row * (kMaxSplits + 1);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < S; s0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < S) v[j] = __ldcg(src + (size_t)(s0 + j) * (D / 4));
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < S) {
+          const float wj = w[s0 + j];
+          acc.x += wj * v[j].x; acc.y += wj * v[j].y; acc.z += wj * v[j].z; acc.w += wj * v[j].w;
+        }
+    }
+    bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d4 * 4;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
   }
   if (threadIdx.x == 0) p.counters[counter_index] = 0;   // ready for the next launch
 }
@@ -391,7 +465,7 @@ template <int D, bool kDecode>
 int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
   const int groups = p.heads / p.kv_heads;
   const int tq = (kDecode ? 16 : kBlockM) / groups;
-  constexpr int kStages = kDecode ? (D == 64 ? 4 : 3) : 2;
+  constexpr int kStages = 2;
   const size_t smem = (size_t)((kDecode ? 16 : kBlockM) + 2 * kStages * kBlockN) * D * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
@@ -433,13 +507,17 @@ LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out,
   if (kv_heads < 1 || heads % kv_heads) return LI_ERR_UNSUPPORTED;
   const int groups = heads / kv_heads;
   if (groups > kBlockM || (head_dim != 64 && head_dim != 128)) return LI_ERR_UNSUPPORTED;
-  if (kv_heads > 65535 || num_seqs > 65535 || num_splits < 1) return LI_ERR_UNSUPPORTED;
+  if (kv_heads > 65535 || num_seqs > 65535 || num_splits < 1 || num_splits > 32) return LI_ERR_UNSUPPORTED;
+  if (num_splits > 1 && (out_row_stride % 4)) return LI_ERR_ALIGNMENT;
   if (num_splits > 1 && (!partial_out || !partial_lse || !counters)) return LI_ERR_UNSUPPORTED;
   if ((q_row_stride % 8) || (out_row_stride % 2) || !aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool))
     return LI_ERR_ALIGNMENT;
   AttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                block_table, table_stride, query_start_loc, context_lens, seq_index, heads, kv_heads, page_size,
-               num_pages, scale * kLog2e, window, num_splits, partial_out, partial_lse, counters};
+               num_pages, -1, scale * kLog2e, window, num_splits, partial_out, partial_lse, counters};
+  if ((page_size & (page_size - 1)) == 0)
+    for (int s = 0; s < 31; ++s)
+      if ((1 << s) == page_size) p.page_shift = s;
   const bool decode = max_q_len == 1 && groups <= 16;
   if (head_dim == 64)
     return decode ? launch_attention<64, true>(p, num_seqs, max_q_len, stream)

@@ -28,6 +28,7 @@ namespace li {
 constexpr int kSkinnyWarps = 4;
 constexpr int kBlocksPerWarp = 8;                                  // 32-wide k blocks per warp and pass
 constexpr int kSlicePass = kSkinnyWarps * kBlocksPerWarp * 32;      // 1024 k per pass
+constexpr int kMaxSlices = 16;
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -92,7 +93,6 @@ gemm_skinny_kernel(const SkinnyParams p) {
 
   const int k_begin = slice * p.slice_k, k_end = min(K, k_begin + p.slice_k);
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  grid_launch_dependents();
   bool waited = false;
   for (int pass = k_begin; pass < k_end; pass += kSlicePass) {
     uint4 wl[kBlocksPerWarp], wh[kBlocksPerWarp];
@@ -122,6 +122,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
   }
 
   if (!waited) grid_dependency_wait();
+  grid_launch_dependents();
   // acc[j]: c0,c1 = (w row g, x rows j*8 + 2t, +1); c2,c3 = (w row g+8, same x rows).
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
@@ -155,8 +156,15 @@ gemm_skinny_kernel(const SkinnyParams p) {
     __threadfence();
     const float* all = p.scratch + (size_t)tile * p.num_slices * (16 * kCols);
     for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
+      // Every slice's value is requested before the first is added: one trip to L2, not one per slice.
+      float v[kMaxSlices];
+#pragma unroll
+      for (int s = 0; s < kMaxSlices; ++s)
+        if (s < p.num_slices) v[s] = __ldcg(all + (size_t)s * (16 * kCols) + e);
       float sum = 0.f;
-      for (int s = 0; s < p.num_slices; ++s) sum += __ldcg(all + (size_t)s * (16 * kCols) + e);
+#pragma unroll
+      for (int s = 0; s < kMaxSlices; ++s)
+        if (s < p.num_slices) sum += v[s];
       partial[0][e % 16][e / 16] = sum;
     }
     if (threadIdx.x == 0) p.counters[tile] = 0;   // ready for the next launch
@@ -208,6 +216,7 @@ LI_EXPORT int li_gemm_skinny_slices(int N, int K, int* slice_k) {
   int slices = 1024 / tiles;
   const int most = K / 512;
   if (slices > most) slices = most;
+  if (slices > kMaxSlices) slices = kMaxSlices;
   if (slices < 1) slices = 1;
   int per = (K + slices - 1) / slices;
   per = (per + 31) / 32 * 32;

@@ -1,0 +1,146 @@
+"""Times single kernels at the sizes of a decode or prefill step: `python -m liteinfer_b200.kernel_bench`.
+
+Each case runs its kernel alone on inputs larger than the L2 cache (several
+copies of the operands are cycled through), times it with CUDA events after a
+warm-up, and prints one JSON line with the time, the bytes or flops the kernel
+must move or do, and what that is per second.  `--kernel` picks one case, which
+is what a profiler capture of a single kernel needs.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from liteinfer_b200 import ops
+from liteinfer_b200.parts.context import AttentionPlan
+
+
+def _time(fn, copies: int, iters: int = 20, warmup: int = 3) -> float:
+    """Median microseconds of one fn(i % copies), measured on the device: `copies` calls are captured into a
+    CUDA graph (so that the host's launch cost stays out of it) and the graph is replayed."""
+    for i in range(warmup):
+        fn(i % copies)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(copies):
+            fn(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3 / copies)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def skinny(M: int, N: int, K: int) -> dict:
+    copies = max(2, (300 << 20) // (N * K * 2) + 1)
+    w = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    us = _time(lambda i: ops.gemm_skinny(x, w[i], out), copies)
+    nbytes = N * K * 2 + M * K * 2 + M * N * 2
+    return {"kernel": "gemm_skinny", "M": M, "N": N, "K": K, "us": us, "GBps": nbytes / us / 1e3,
+            "slices": ops.gemm_skinny_slices(N, K)}
+
+
+def library_gemm(M: int, N: int, K: int) -> dict:
+    copies = max(2, (300 << 20) // (N * K * 2) + 1)
+    w = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    us = _time(lambda i: torch.mm(x, w[i].t(), out=out), copies)
+    return {"kernel": "library_mm", "M": M, "N": N, "K": K, "us": us, "GBps": (N * K * 2) / us / 1e3,
+            "TFLOPs": 2.0 * M * N * K / us / 1e6}
+
+
+def attention(batch: int, q_len: int, ctx: int, heads: int = 32, kv_heads: int = 8, head_dim: int = 64,
+              page: int = 16, splits: int | None = None) -> dict:
+    pages_per = -(-ctx // page)
+    copies = max(2, (300 << 20) // (batch * ctx * kv_heads * head_dim * 4) + 1)
+    num_pages = pages_per * batch
+    pools = [(torch.randn(num_pages, kv_heads, page, head_dim, device="cuda", dtype=torch.bfloat16),
+              torch.randn(num_pages, kv_heads, page, head_dim, device="cuda", dtype=torch.bfloat16))
+             for _ in range(copies)]
+    table = torch.randperm(num_pages, device="cuda").to(torch.int32).view(batch, pages_per)
+    T = batch * q_len
+    qkv = torch.randn(T, (heads + 2 * kv_heads) * head_dim, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, heads * head_dim, device="cuda", dtype=torch.bfloat16)
+    qsl = (torch.arange(batch + 1, device="cuda") * q_len).to(torch.int32)
+    ctxl = torch.full((batch,), ctx, device="cuda", dtype=torch.int32)
+    seqs = torch.arange(batch, device="cuda", dtype=torch.int32)
+    if q_len == 1:
+        plan = AttentionPlan(num_decode=batch, decode_seqs=seqs, decode_tokens=seqs, max_decode_context_len=ctx)
+    else:
+        plan = AttentionPlan(num_prefill=batch, prefill_seqs=seqs, max_prefill_query_len=q_len)
+
+    def run(i):
+        ops.paged_attention(qkv, qkv.shape[1], out, pools[i][0], pools[i][1], table, qsl, ctxl, batch, q_len, heads,
+                            kv_heads, head_dim, head_dim ** -0.5, 0, plan=plan, decode_splits=splits)
+
+    us = _time(run, copies)
+    kv_bytes = batch * ctx * kv_heads * head_dim * 2 * 2
+    flops = 4.0 * heads * head_dim * batch * (q_len * (ctx - q_len) + q_len * (q_len + 1) / 2)
+    return {"kernel": "paged_attention", "batch": batch, "q_len": q_len, "ctx": ctx, "heads": heads,
+            "kv_heads": kv_heads, "head_dim": head_dim, "us": us, "GBps": kv_bytes / us / 1e3,
+            "TFLOPs": flops / us / 1e6,
+            "splits": splits or (ops.decode_splits_for(batch, kv_heads, ctx) if q_len == 1 else 1)}
+
+
+def rmsnorm(rows: int, width: int) -> dict:
+    x = torch.randn(rows, width, device="cuda", dtype=torch.bfloat16)
+    d = torch.randn(rows, width, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(width, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(x)
+    us = _time(lambda i: ops.rmsnorm(x, w, 1e-5, out, delta=d, write_residual=True), 8)
+    return {"kernel": "add_rmsnorm", "rows": rows, "width": width, "us": us, "GBps": rows * width * 2 * 4 / us / 1e3}
+
+
+CASES = {
+    "decode_attention_b8": lambda: attention(8, 1, 4096),
+    "decode_attention_b1": lambda: attention(1, 1, 4096),
+    "decode_attention_b64": lambda: attention(64, 1, 4096),
+    "prefill_attention_2048": lambda: attention(1, 2048, 2048),
+    "skinny_qkv_b8": lambda: skinny(8, 3072, 2048),
+    "skinny_o_b8": lambda: skinny(8, 2048, 2048),
+    "skinny_gate_up_b8": lambda: skinny(8, 16384, 2048),
+    "skinny_down_b8": lambda: skinny(8, 2048, 8192),
+    "skinny_head_b8": lambda: skinny(8, 128256, 2048),
+    "skinny_gate_up_b16": lambda: skinny(16, 16384, 2048),
+    "library_gate_up_b16": lambda: library_gemm(16, 16384, 2048),
+    "skinny_gate_up_b32": lambda: skinny(32, 16384, 2048),
+    "library_gate_up_b32": lambda: library_gemm(32, 16384, 2048),
+    "skinny_gate_up_b64": lambda: skinny(64, 16384, 2048),
+    "library_down_b8": lambda: library_gemm(8, 2048, 8192),
+    "library_qkv_b8": lambda: library_gemm(8, 3072, 2048),
+    "library_gate_up_b64": lambda: library_gemm(64, 16384, 2048),
+    "library_gate_up_2048": lambda: library_gemm(2048, 16384, 2048),
+    "library_down_2048": lambda: library_gemm(2048, 2048, 8192),
+    "add_rmsnorm_b8": lambda: rmsnorm(8, 2048),
+    "add_rmsnorm_2048": lambda: rmsnorm(2048, 2048),
+}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--kernel", default="all", help="one of: all, " + ", ".join(CASES))
+    args = parser.parse_args()
+    names = list(CASES) if args.kernel == "all" else [args.kernel]
+    for name in names:
+        result = CASES[name]()
+        print(json.dumps({"case": name, **{k: (round(v, 2) if isinstance(v, float) else v) for k, v in result.items()}}),
+              flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -391,7 +391,7 @@ def _interleave(gate, up):
     return torch.stack([gate.reshape(-1, 8, *rest), up.reshape(-1, 8, *rest)], dim=1).reshape(2 * gate.shape[0], *rest).contiguous()
 
 
-@pytest.mark.parametrize("M", [1, 8, 33])
+@pytest.mark.parametrize("M", [1, 5, 8])
 @pytest.mark.parametrize("inter,K,act", [(8192, 2048, "silu"), (112, 120, "gelu_pytorch_tanh"), (176, 64, "relu")])
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_gated_linear_is_product_activation_and_multiply_in_one(M, inter, K, act, with_bias):
