@@ -21,183 +21,9 @@
 // Optional epilogue for a gated feed-forward: with `gated_act >= 0` the rows of w
 // are interleaved in groups of eight (eight gate rows, then their eight up rows),
 // and the block writes act(gate) * up, N/2 columns wide.
-#include "common.cuh"
+#include "gemm_skinny.cuh"
 
 namespace li {
-
-constexpr int kSkinnyWarps = 4;
-constexpr int kBlocksPerWarp = 8;                                  // 32-wide k blocks per warp and pass
-constexpr int kSlicePass = kSkinnyWarps * kBlocksPerWarp * 32;      // 1024 k per pass
-constexpr int kMaxSlices = 16;
-
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-
-__device__ __forceinline__ void mma_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
-                                          unsigned b0, unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ float gated(float gate, float up, int act) {
-  float a;
-  switch (act) {
-    case 0: a = gate / (1.0f + expf(-gate)); break;
-    case 1: a = 0.5f * gate * (1.0f + erff(gate * 0.70710678118654752440f)); break;
-    case 2: a = 0.5f * gate * (1.0f + tanhf(0.79788456080286535588f * (gate + 0.044715f * gate * gate * gate))); break;
-    default: a = fmaxf(gate, 0.f);
-  }
-  return __bfloat162float(__float2bfloat16_rn(a)) * up;   // the activation is rounded before the multiply
-}
-
-struct SkinnyParams {
-  const bf16* x;
-  const bf16* w;
-  const bf16* bias;
-  bf16* out;
-  int M, N, K;
-  int slice_k;        // k per slice, a multiple of 32
-  int num_slices;
-  int gated_act;      // -1: plain product
-  float* scratch;     // [tiles][num_slices][16][NT*8] partial tiles, when num_slices > 1
-  unsigned* counters; // [tiles], zero between launches
-};
-
-template <int NT>   // NT tiles of 8 rows of x
-__global__ void __launch_bounds__(kSkinnyWarps * 32)
-gemm_skinny_kernel(const SkinnyParams p) {
-  constexpr int kCols = NT * 8;
-  __shared__ float partial[kSkinnyWarps][16][kCols + 1];
-  __shared__ bool is_last;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int tile = blockIdx.x, slice = blockIdx.y;
-  const int row0 = tile * 16;
-  const int K = p.K, M = p.M, N = p.N;
-  // Rows past N read the last row again; their results are not stored.
-  const bf16* w_lo = p.w + (size_t)min(row0 + g, N - 1) * K;
-  const bf16* w_hi = p.w + (size_t)min(row0 + g + 8, N - 1) * K;
-  const bf16* xr[NT];
-#pragma unroll
-  for (int j = 0; j < NT; ++j) xr[j] = p.x + (size_t)min(j * 8 + g, M - 1) * K;
-
-  float acc[NT][4];
-#pragma unroll
-  for (int j = 0; j < NT; ++j)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-
-  const int k_begin = slice * p.slice_k, k_end = min(K, k_begin + p.slice_k);
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  bool waited = false;
-  for (int pass = k_begin; pass < k_end; pass += kSlicePass) {
-    uint4 wl[kBlocksPerWarp], wh[kBlocksPerWarp];
-#pragma unroll
-    for (int u = 0; u < kBlocksPerWarp; ++u) {
-      const int k = pass + (u * kSkinnyWarps + warp) * 32 + 8 * t;
-      const bool in = k < k_end;
-      wl[u] = in ? ldg_stream(w_lo + k) : zero;
-      wh[u] = in ? ldg_stream(w_hi + k) : zero;
-    }
-    // The weights above depend on no earlier kernel and are already on their way; x does.
-    if (!waited) {
-      grid_dependency_wait();
-      waited = true;
-    }
-#pragma unroll
-    for (int u = 0; u < kBlocksPerWarp; ++u) {
-      const int k = pass + (u * kSkinnyWarps + warp) * 32 + 8 * t;
-      const bool in = k < k_end;
-#pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        const uint4 xv = (in && j * 8 + g < M) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
-        mma_16816(acc[j], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv.x, xv.y);
-        mma_16816(acc[j], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv.z, xv.w);
-      }
-    }
-  }
-
-  if (!waited) grid_dependency_wait();
-  grid_launch_dependents();
-  // acc[j]: c0,c1 = (w row g, x rows j*8 + 2t, +1); c2,c3 = (w row g+8, same x rows).
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    partial[warp][g][j * 8 + 2 * t] = acc[j][0];
-    partial[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
-    partial[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
-    partial[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
-  }
-  __syncthreads();
-
-  // Sum of the four warps, kept in partial[0].
-  for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
-    const int r = e % 16, m = e / 16;
-    float sum = 0.f;
-#pragma unroll
-    for (int wv = 0; wv < kSkinnyWarps; ++wv) sum += partial[wv][r][m];
-    partial[0][r][m] = sum;   // each element is read and written by this thread only
-  }
-
-  if (p.num_slices > 1) {
-    float* mine = p.scratch + ((size_t)tile * p.num_slices + slice) * (16 * kCols);
-    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) mine[e] = partial[0][e % 16][e / 16];
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const unsigned arrived = atomicAdd(&p.counters[tile], 1u);
-      is_last = arrived == (unsigned)p.num_slices - 1;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    const float* all = p.scratch + (size_t)tile * p.num_slices * (16 * kCols);
-    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
-      // Every slice's value is requested before the first is added: one trip to L2, not one per slice.
-      float v[kMaxSlices];
-#pragma unroll
-      for (int s = 0; s < kMaxSlices; ++s)
-        if (s < p.num_slices) v[s] = __ldcg(all + (size_t)s * (16 * kCols) + e);
-      float sum = 0.f;
-#pragma unroll
-      for (int s = 0; s < kMaxSlices; ++s)
-        if (s < p.num_slices) sum += v[s];
-      partial[0][e % 16][e / 16] = sum;
-    }
-    if (threadIdx.x == 0) p.counters[tile] = 0;   // ready for the next launch
-  }
-  __syncthreads();
-
-  if (p.gated_act < 0) {
-    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
-      const int r = e % 16, m = e / 16;     // consecutive threads write consecutive output columns
-      const int n = row0 + r;
-      if (m >= M || n >= N) continue;
-      float sum = partial[0][r][m];
-      if (p.bias) sum += __bfloat162float(p.bias[n]);
-      p.out[(size_t)m * N + n] = __float2bfloat16_rn(sum);
-    }
-  } else {
-    const int half = N / 2;                 // rows [0, 8) of the tile are gate rows, [8, 16) their up rows
-    for (int e = threadIdx.x; e < 8 * kCols; e += kSkinnyWarps * 32) {
-      const int r = e % 8, m = e / 8;
-      const int n = tile * 8 + r;
-      if (m >= M || n >= half) continue;
-      float gate = partial[0][r][m], up = partial[0][r + 8][m];
-      if (p.bias) {
-        gate += __bfloat162float(p.bias[row0 + r]);
-        up += __bfloat162float(p.bias[row0 + r + 8]);
-      }
-      // The products are rounded to bfloat16 before the activation, as a separate kernel would see them.
-      gate = __bfloat162float(__float2bfloat16_rn(gate));
-      up = __bfloat162float(__float2bfloat16_rn(up));
-      p.out[(size_t)m * half + n] = __float2bfloat16_rn(gated(gate, up, p.gated_act));
-    }
-  }
-}
 
 template <int NT>
 int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
@@ -211,19 +37,7 @@ using namespace li;
 
 // How the kernel would cut k for these sizes: (slices, k per slice).  Slices are at least 512 wide and are
 // used only while there are too few 16-row tiles to occupy the GPU.
-LI_EXPORT int li_gemm_skinny_slices(int N, int K, int* slice_k) {
-  const int tiles = (N + 15) / 16;
-  int slices = 1024 / tiles;
-  const int most = K / 512;
-  if (slices > most) slices = most;
-  if (slices > kMaxSlices) slices = kMaxSlices;
-  if (slices < 1) slices = 1;
-  int per = (K + slices - 1) / slices;
-  per = (per + 31) / 32 * 32;
-  slices = (K + per - 1) / per;
-  if (slice_k) *slice_k = per;
-  return slices;
-}
+LI_EXPORT int li_gemm_skinny_slices(int N, int K, int* slice_k) { return skinny_slices(N, K, slice_k); }
 
 // bfloat16 only; 1 <= M <= 64; K a multiple of 8 and 16-byte aligned rows.  scratch (float) and counters
 // (unsigned, all zero) are needed when li_gemm_skinny_slices(N, K) > 1: scratch_floats must be at least
