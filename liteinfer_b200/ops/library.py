@@ -35,7 +35,8 @@ NVCC_FLAGS = [
 ]
 
 # Source file (without .cu) of every library.
-SOURCES = ("elementwise", "rope_cache", "attention_generic", "attention_mma", "gemm_simt", "gemm_skinny", "sampling")
+SOURCES = ("elementwise", "rope_cache", "attention_generic", "attention_mma", "gemm_simt", "gemm_skinny", "gemm_skinny_static",
+           "sampling")
 
 
 class KernelLibraryError(RuntimeError):
