@@ -111,14 +111,20 @@ class EngineCore:
         return int(min(affordable, reachable))
 
     # ------------------------------------------------------------- requests
-    def _pages_free_for(self, seq: Sequence, admitted_tokens: int) -> bool:
-        """Admission gate: are the pages of this whole prompt (beside what this step already admitted) free?"""
+    def _pages_free_for(self, seq: Sequence, admitted: list[Sequence]) -> bool:
+        """Admission gate: can the cache hold this request to its very end, beside every request that is
+        running or was admitted earlier in this step, each grown to its own end?  With this rule a step
+        of admitted requests never runs out of pages; requests wait for room instead."""
         cache = self.runner.cache
         page = cache.page_size
-        need = _cdiv(len(seq) + 1, page) + _cdiv(admitted_tokens, page)
-        # Requests that are decoding take a page now and then; leave them one each.
-        reserve = sum(1 for s in self.scheduler.running if s.is_prompt_computed)
-        return all(need + reserve <= g.allocator.num_free for g in cache.groups)
+
+        def pages_at_end(s: Sequence) -> int:
+            end = min(len(s.prompt_token_ids) + s.sampling_params.max_tokens, self.config.max_model_len)
+            return _cdiv(end, page)
+
+        live = [s for s in self.scheduler.running if not s.is_finished]
+        need = sum(pages_at_end(s) for s in [seq, *admitted, *live])
+        return all(need <= g.allocator.num_pages for g in cache.groups)
 
     @property
     def num_waiting(self) -> int:

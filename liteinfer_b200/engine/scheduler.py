@@ -11,9 +11,10 @@ is part-way through its prompt and nothing is admitted behind it.
 One decision is added where the reference leaves it to failure
 (liteinfer/engine/async_llm_engine.py:73-85,244-248 sheds requests after the pool
 refused a step): when a `page_gate` is given, a waiting request is admitted only
-if the pages for its whole prompt are free at that moment, so newcomers wait
-instead of being aborted.  Running out of pages during decoding is still
-possible; the engine then sheds by the reference's tiers.
+if the cache can hold it to its end beside everything already running, so
+newcomers wait instead of being aborted.  Without a gate, or for a request that
+can never fit, running out of pages is still possible; the engine then sheds by
+the reference's tiers.
 """
 
 from __future__ import annotations
@@ -38,8 +39,9 @@ class SchedulerOutput:
 
 class Scheduler:
     def __init__(self, config: EngineConfig,
-                 page_gate: Callable[[Sequence, int], bool] | None = None) -> None:
-        """`page_gate(seq, tokens_already_granted_to_newcomers)` says whether the cache can take `seq` now."""
+                 page_gate: Callable[[Sequence, list[Sequence]], bool] | None = None) -> None:
+        """`page_gate(seq, admitted)` says whether the cache can take `seq` now, beside the requests
+        `admitted` earlier in this same step (which hold no pages yet)."""
         self.config = config
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
@@ -59,10 +61,10 @@ class Scheduler:
             if not seq.is_finished:
                 budget -= self._grant(out, seq, budget)
 
-        admitted_tokens = 0
+        admitted: list[Sequence] = []
         while budget > 0 and self.waiting and len(self.running) < self.config.max_num_seqs:
             seq = self.waiting[0]
-            if self.page_gate is not None and not self.page_gate(seq, admitted_tokens):
+            if self.page_gate is not None and not self.page_gate(seq, admitted):
                 # Wait for pages rather than fail — unless nothing runs at all, in which case
                 # waiting would never end and the request is let through to fail on its own.
                 if self.running:
@@ -70,7 +72,7 @@ class Scheduler:
             self.waiting.popleft()
             seq.status = SequenceStatus.RUNNING
             self.running.append(seq)
-            admitted_tokens += len(seq)
+            admitted.append(seq)
             budget -= self._grant(out, seq, budget)
         return out
 

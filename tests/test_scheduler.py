@@ -88,7 +88,7 @@ def test_seats_limit_admission():
 
 def test_page_gate_makes_newcomers_wait_instead_of_fail():
     free = {"pages": 3}
-    gate = lambda seq, admitted: -(-(len(seq) + admitted) // 4) <= free["pages"]
+    gate = lambda seq, admitted: sum(-(-len(s) // 4) for s in [seq, *admitted]) <= free["pages"]
     sched = Scheduler(EngineConfig(model="m", max_num_seqs=4), page_gate=gate)
     sched.add(_seq("a", 10)); sched.add(_seq("b", 10))
     out = _run_step(sched)
