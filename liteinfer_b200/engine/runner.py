@@ -198,6 +198,8 @@ class ModelRunner:
         """Replay steps that hold single decoded tokens only from CUDA graphs."""
         if self.device.type != "cuda":
             raise ValueError("CUDA graphs need a CUDA device")
+        if not self.model.graph_safe:
+            return          # a part works on the host inside forward: every step launches kernel by kernel
         self._graph_limits = (max_num_seqs, max_model_len)
         self.graph_pool = torch.cuda.graph_pool_handle()
 

@@ -82,6 +82,12 @@ class Model:
         for prefix, part in self._named_parts():
             part.bind({local: tensors[prefix + local] for local in part.tensor_specs()})
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a step of this model may be captured into a CUDA graph: every part launches kernels only.
+        A part that reads device values on the host in `forward` sets `graph_safe = False`."""
+        return all(getattr(part, "graph_safe", True) for _, part in self._named_parts())
+
     def weight_bytes(self) -> int:
         seen: dict[int, int] = {}
         for _, part in self._named_parts():

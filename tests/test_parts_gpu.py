@@ -94,6 +94,8 @@ def test_rotary_part_frequencies_are_the_plain_ones():
 class EmaMixer:
     """y_t = (s_t) W, s_t = decay * s_{t-1} + x_t: a recurrence whose state lives in the request's state slot."""
 
+    graph_safe = False      # forward reads the slots on the host, so steps are not captured into CUDA graphs
+
     def __init__(self, hidden_size: int, decay: float, dtype, device):
         self.hidden_size, self.decay, self.dtype, self.device = hidden_size, decay, dtype, device
         self.weight = None
