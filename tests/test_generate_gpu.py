@@ -35,27 +35,27 @@ def test_greedy_generation_float32_equals_plain(model_dirs, name):
 
 
 @pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
-def test_greedy_generation_bfloat16_follows_plain_where_the_margin_allows(model_dirs, name):
-    """In bfloat16 one rounding can flip an arg-max between near-equal logits, so tokens are compared only
-    while the plain run's own margin (top-1 minus top-2) is well above bfloat16's drift."""
+def test_greedy_generation_bfloat16_picks_a_top_token_of_the_plain_run(model_dirs, name):
+    """In bfloat16 one rounding can flip an arg-max between near-equal logits (random weights give flat
+    logits), so the check is on logits, along the engine's own tokens: what the engine picked is, in the
+    plain 32-bit run, the maximum or within bfloat16's drift of it, at every step."""
     from liteinfer_b200 import LLM, SamplingParams
 
     config, _, page = tiny_configs.ALL[name]
     prompt = tiny_configs.prompt(config["vocab_size"], 30, 5)
     raw, weights = plain_llama.read_model(model_dirs[name])
+    exact = plain_llama.forward(raw, weights, prompt, device="cuda")
+    drift = float((plain_llama.forward(raw, weights, prompt, torch.bfloat16, "cuda") - exact).abs().max())
     with LLM(str(model_dirs[name]), dtype="bfloat16", block_size=page, max_num_seqs=2, max_model_len=128) as llm:
         got = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))[0].token_ids
-    tokens = list(prompt)
+    assert len(got) == 12
+    tokens, agree = list(prompt), 0
     for step, token in enumerate(got):
         logits = plain_llama.forward(raw, weights, tokens, device="cuda")[-1]
-        top = torch.topk(logits, 2).values
-        if float(top[0] - top[1]) < 0.05:
-            break
-        assert token == int(torch.argmax(logits)), f"step {step}"
+        assert float(logits.max() - logits[token]) <= 4 * drift, f"step {step}: token {token} is not near the top"
+        agree += int(token == int(torch.argmax(logits)))
         tokens.append(token)
-    else:
-        step = len(got)
-    assert step >= 3
+    assert agree >= 8
 
 
 def test_long_decoding_and_first_tokens(model_dirs, tmp_path):
