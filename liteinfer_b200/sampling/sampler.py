@@ -7,8 +7,8 @@ batch of only greedy rows runs the arg-max kernel, any other batch the
 sampling kernel, which treats a row with temperature 0 or top_k 1 as arg-max.
 
 Random numbers come from the host: every request owns a `random.Random` stream
-(seeded by `SamplingParams.seed`, or by the engine's seed and a key the caller
-gives), and each sampled token consumes one uniform number from it.  What a
+(seeded by `SamplingParams.seed` alone, or for unseeded requests by the engine's
+seed and a key the caller gives), and each sampled token consumes one uniform number from it.  What a
 request draws therefore does not depend on which other requests share its
 batch.
 """
@@ -33,7 +33,8 @@ class Sampler:
         stream = self._streams.get(stream_key)
         if stream is None:
             if params.seed is not None:
-                stream = random.Random(params.seed if key is None else f"{params.seed}/{key}")
+                # Every request with this seed draws the same numbers: the same prompt gives the same tokens.
+                stream = random.Random(params.seed)
             else:
                 stream = random.Random(f"{self.seed}/{stream_key}")
             self._streams[stream_key] = stream
