@@ -1,0 +1,421 @@
+// out[M, N] = x[M, K] @ w[N, K]^T (+ bias) in bfloat16 on the fifth-generation tensor cores:
+// the matrix product of prefill, where M is in the hundreds or thousands.
+//
+// One persistent block per SM walks 128 x BN output tiles.  Inside a block the work is split
+// by warp: warp 0 moves tiles of x and w from global to shared memory with TMA
+// (cp.async.bulk.tensor, 128-byte swizzle) through a ring of stages guarded by mbarriers; one
+// thread of warp 1 issues tcgen05.mma (M 128, N BN, K 16 per instruction, operands straight
+// from shared memory through matrix descriptors) accumulating in tensor memory, and commits
+// each stage back to the loader; warps 2-5 drain a finished accumulator from tensor memory
+// with tcgen05.ld, round it to bfloat16 and store it, while the next tile's products already
+// run into the second accumulator (2 x BN of the 512 TMEM columns).
+//
+// Optional epilogue for a gated feed-forward (`gated_act >= 0`): the rows of w are interleaved in
+// eights (eight gate rows, then their eight up rows); the block then writes act(gate) * up,
+// N/2 columns wide, with the same rounding points as the separate kernels (products rounded to
+// bfloat16, activation rounded, then the multiply).
+//
+// Every wait on an mbarrier is bounded: a wait that runs out records where it gave up in
+// `error_flag` and the block winds down (tensor memory is freed on every path), so a fault in
+// the choreography shows up as an error code, not as a hang.
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace li {
+
+constexpr int kTileM = 128;
+constexpr int kTileK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;          // loader, issuer, four epilogue warps
+constexpr unsigned kWaitLimit = 1u << 22;  // polls of one mbarrier wait before it gives up
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// Returns false when the wait ran out; `where` identifies the wait in the error flag.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* error_flag, int where) {
+  for (unsigned it = 0; it < kWaitLimit; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  if (error_flag) atomicCAS(error_flag, 0, where);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// start address, leading offset 1 (unused with swizzle), 1024 bytes between groups of eight rows,
+// descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ unsigned long long umma_desc(unsigned addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr >> 4) & 0x3fff);
+  d |= (unsigned long long)1 << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
+                                          bool accumulate) {
+  const unsigned acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ float gated_value(float gate, float up, int act) {
+  gate = __bfloat162float(__float2bfloat16_rn(gate));
+  up = __bfloat162float(__float2bfloat16_rn(up));
+  float a;
+  switch (act) {
+    case 0: a = gate / (1.0f + expf(-gate)); break;
+    case 1: a = 0.5f * gate * (1.0f + erff(gate * 0.70710678118654752440f)); break;
+    case 2: a = 0.5f * gate * (1.0f + tanhf(0.79788456080286535588f * (gate + 0.044715f * gate * gate * gate))); break;
+    default: a = fmaxf(gate, 0.f);
+  }
+  return __bfloat162float(__float2bfloat16_rn(a)) * up;
+}
+
+// Tiles are walked in bands of eight tile rows, column by column inside a band, so that the blocks running at
+// the same time share a few tiles of x and a few of w (which then come from L2, not from HBM).
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int kBand = 8;
+  const int per_band = kBand * tiles_n;
+  const int band = tile / per_band, in_band = tile - band * per_band;
+  const int rows = min(kBand, tiles_m - band * kBand);
+  tn = in_band / rows;
+  tm = band * kBand + in_band % rows;
+}
+
+struct GemmParams {
+  bf16* out;
+  const bf16* bias;
+  int M, N, K;
+  int gated_act;
+  int* error_flag;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  // Tiles must start on 1024-byte boundaries for the 128-byte swizzle.
+  const unsigned base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  constexpr unsigned kBytesA = kTileM * kTileK * 2, kBytesB = BN * kTileK * 2, kStageBytes = kBytesA + kBytesB;
+  const unsigned bars = base + STAGES * kStageBytes;       // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  const unsigned tmem_slot = bars + 8u * (2 * STAGES + 4);
+  __shared__ unsigned tmem_base_shared;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + kTileK - 1) / kTileK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), 4);     // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // the issuing warp owns tensor memory: 2 accumulators of BN columns, all 512 columns asked for
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  if (threadIdx.x == 0) {
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(tmem_slot));
+    tmem_base_shared = v;
+  }
+  __syncthreads();
+  const unsigned tmem_base = tmem_base_shared;
+  grid_dependency_wait();   // x comes from the kernel before (a no-op under an ordinary launch)
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0) {
+      int stage = 0;
+      unsigned phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, p.error_flag, 1)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), kStageBytes);
+          const unsigned a = base + stage * kStageBytes;
+          tma_load_2d(a, &map_x, full_bar(stage), kb * kTileK, tm * kTileM);
+          tma_load_2d(a + kBytesA, &map_w, full_bar(stage), kb * kTileK, tn * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ issuer
+    if (lane == 0) {
+      // Instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, N = BN, M = 128.
+      constexpr unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
+                                 ((unsigned)(kTileM >> 4) << 24);
+      int stage = 0;
+      unsigned phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const unsigned use = (unsigned)(local >> 1);
+        if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, p.error_flag, 2)) { ok = false; break; }
+        tcgen05_fence_after();
+        const unsigned acc = tmem_base + (unsigned)(buf * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.error_flag, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const unsigned a = base + stage * kStageBytes, b = a + kBytesA;
+#pragma unroll
+          for (int k = 0; k < kTileK / kUmmaK; ++k)
+            umma_bf16(acc, umma_desc(a + k * kUmmaK * 2), umma_desc(b + k * kUmmaK * 2), idesc, kb > 0 || k > 0);
+          umma_commit(empty_bar(stage));          // the stage is free once these products have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(acc_full_bar(buf));   // the accumulator is complete once all products are done
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4) ...
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int buf = local & 1;
+      const unsigned use = (unsigned)(local >> 1);
+      if (!mbar_wait(acc_full_bar(buf), use & 1, p.error_flag, 4)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int m = tm * kTileM + quarter * 32 + lane;
+      const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        unsigned r[32];
+        __syncwarp();                       // the load below is a warp-wide instruction
+        tmem_load32(taddr + c * 32, r);
+        tmem_load_wait();
+        const int n0 = tn * BN + c * 32;
+        if (m >= p.M || n0 >= p.N) continue;
+        if (p.gated_act < 0) {
+          bf16* dst = p.out + (size_t)m * p.N + n0;
+          if (n0 + 32 <= p.N && (p.N % 8) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pack;
+              unsigned* w = reinterpret_cast<unsigned*>(&pack);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float lo = __uint_as_float(r[v * 8 + 2 * j]), hi = __uint_as_float(r[v * 8 + 2 * j + 1]);
+                if (p.bias) {
+                  lo += __bfloat162float(p.bias[n0 + v * 8 + 2 * j]);
+                  hi += __bfloat162float(p.bias[n0 + v * 8 + 2 * j + 1]);
+                }
+                __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                w[j] = *reinterpret_cast<unsigned*>(&h);
+              }
+              *reinterpret_cast<uint4*>(dst + v * 8) = pack;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (n0 + j < p.N) {
+                float v = __uint_as_float(r[j]);
+                if (p.bias) v += __bfloat162float(p.bias[n0 + j]);
+                dst[j] = __float2bfloat16_rn(v);
+              }
+            }
+          }
+        } else {
+          // 32 columns = two groups of (eight gate, eight up) -> 16 outputs at column n0 / 2.
+          const int half = p.N / 2;
+          bf16* dst = p.out + (size_t)m * half + n0 / 2;
+#pragma unroll
+          for (int grp = 0; grp < 2; ++grp) {
+            if (n0 + grp * 16 >= p.N) break;
+            uint4 pack;
+            unsigned* w = reinterpret_cast<unsigned*>(&pack);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float v[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int col = grp * 16 + 2 * j + e;
+                float gate = __uint_as_float(r[col]), up = __uint_as_float(r[col + 8]);
+                if (p.bias) {
+                  gate += __bfloat162float(p.bias[n0 + col]);
+                  up += __bfloat162float(p.bias[n0 + col + 8]);
+                }
+                v[e] = gated_value(gate, up, p.gated_act);
+              }
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[0], v[1]);
+              w[j] = *reinterpret_cast<unsigned*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + grp * 8) = pack;
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown (every path comes here)
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)entry;
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix as a 2-D tensor map with boxes of 64 x box_rows and 128-byte swizzle;
+// elements outside the matrix read as zero.
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+  // Encoding is pure host arithmetic on (pointer, sizes): the same matrix gives the same map, so maps are kept.
+  static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
+  const auto key = std::make_tuple(ptr, rows, K, box_rows);
+  const auto found = cache.find(key);
+  if (found != cache.end()) {
+    *map = found->second;
+    return true;
+  }
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *map);
+  return true;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmParams& p, int sms, cudaStream_t s) {
+  constexpr size_t smem = (size_t)STAGES * (kTileM + BN) * kTileK * 2 + 8 * (2 * STAGES + 4) + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_tcgen05_kernel<BN, STAGES><<<grid, kGemmThreads, smem, s>>>(mx, mw, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace li
+
+using namespace li;
+
+// bfloat16; K a multiple of 8; x and w 16-byte aligned.  gated_act: -1 plain; 0..3 act(gate) * up on rows of w
+// interleaved in eights (N a multiple of 16; out is [M, N/2]).  error_flag (device int, zero): set to the number
+// of the wait that gave up if the kernel's choreography ever stalls (1 loader, 2 accumulator free, 3 stage full,
+// 4 accumulator full); the output is then not to be trusted.
+LI_EXPORT int li_gemm_tcgen05(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                              int gated_act, int* error_flag, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (K < 8 || (K % 8) || gated_act > 3 || (gated_act >= 0 && (N % 16))) return LI_ERR_UNSUPPORTED;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(out)) return LI_ERR_ALIGNMENT;
+  static int sms = 0;
+  if (!sms) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (sms <= 0) sms = 148;
+  }
+  // Tile width: whichever of 256 and 128 needs less time in whole waves of blocks (ties go to the wide tile,
+  // which reads less per product).
+  const int tiles_m = (M + kTileM - 1) / kTileM;
+  const long cost_wide = (long)((tiles_m * ((N + 255) / 256) + sms - 1) / sms) * 256;
+  const long cost_narrow = (long)((tiles_m * ((N + 127) / 128) + sms - 1) / sms) * 128;
+  const bool wide = N > 128 && 2 * cost_wide <= 3 * cost_narrow;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, kTileM) || !make_map(&mw, w, N, K, wide ? 256 : 128)) return LI_ERR_UNSUPPORTED;
+  GemmParams p{(bf16*)out, (const bf16*)bias, M, N, K, gated_act, error_flag};
+  return wide ? launch_gemm<256, 4>(mx, mw, p, sms, stream) : launch_gemm<128, 6>(mx, mw, p, sms, stream);
+}

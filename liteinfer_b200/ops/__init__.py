@@ -9,7 +9,9 @@ from liteinfer_b200.ops.kernels import (  # noqa: F401
     argmax,
     embedding,
     decode_splits_for,
+    gemm_error_flag,
     gemm_simt,
+    gemm_tcgen05,
     gated_linear,
     gated_linear_supported,
     gemm_skinny,

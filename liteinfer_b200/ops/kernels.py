@@ -48,6 +48,8 @@ _SIGNATURES = {
     "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_void_p, c_size_t, c_void_p, c_int, c_void_p]),
     "li_gemm_skinny_slices": ("gemm_skinny", [c_int, c_int, c_void_p]),
+    "li_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                         c_void_p]),
     "li_gemm_simt": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p]),
@@ -122,6 +124,7 @@ class _Scratch:
         self.argmax_value = torch.empty(self.ARGMAX_ROWS * 32, dtype=torch.float32, device=device)
         self.argmax_index = torch.empty(self.ARGMAX_ROWS * 32, dtype=torch.int32, device=device)
         self.argmax_counters = torch.zeros(self.ARGMAX_ROWS, dtype=torch.int32, device=device)
+        self.gemm_error = torch.zeros(1, dtype=torch.int32, device=device)
 
 
 _scratch: dict[torch.device, _Scratch] = {}
@@ -258,6 +261,33 @@ def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: 
     return _skinny(x, weight, out, bias, -1)
 
 
+def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
+                 gated_activation: str | None = None) -> torch.Tensor:
+    """The tcgen05 / TMA / tensor-memory product for bfloat16: out = x @ weight^T (+ bias), or with
+    `gated_activation` act(gate) * up on a weight whose rows are interleaved in eights (out is [M, N/2]).
+
+    `gemm_error_flag(device)` tells afterwards whether a wait inside the kernel ever gave up."""
+    _on_gpu(x, weight, out, bias)
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and x.dtype == weight.dtype == out.dtype == torch.bfloat16
+    assert out.shape == ((M, N) if gated_activation is None else (M, N // 2))
+    act = -1 if gated_activation is None else ACTIVATIONS[gated_activation]
+    _check(_fn("li_gemm_tcgen05")(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, act,
+                                  scratch_for(x.device).gemm_error.data_ptr(), _stream()), "gemm_tcgen05")
+    return out
+
+
+def gemm_error_flag(device: torch.device) -> int:
+    """0, or the number of the wait that gave up in a tcgen05 product since the flag was last cleared
+    (synchronises the device)."""
+    flag = scratch_for(torch.device(device)).gemm_error
+    value = int(flag.item())
+    if value:
+        flag.zero_()
+    return value
+
+
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """The FFMA product for either dtype (32-bit accumulation, fixed summation order)."""
     _on_gpu(x, weight, out, bias)
@@ -274,22 +304,30 @@ def gemm_skinny_slices(N: int, K: int) -> int:
     return int(_fn("li_gemm_skinny_slices")(N, K, None))
 
 
+# Rows of x from which the gated product runs on the tcgen05 kernel (one 128-row tile at least).
+TCGEN05_MIN_ROWS = 128
+
+
 def gated_linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether product, activation and multiply can be one kernel for this x: at most 8 rows (the
+    weight-streaming kernel) or at least 128 (the tcgen05 kernel)."""
     M, K = x.shape
-    return (x.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and K >= 8
-            and weight.shape[0] % 16 == 0)
+    return (x.dtype == torch.bfloat16 and K % 8 == 0 and K >= 8 and weight.shape[0] % 16 == 0
+            and (0 < M <= SKINNY_MAX_ROWS or M >= TCGEN05_MIN_ROWS))
 
 
 def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, activation: str,
                  bias: torch.Tensor | None = None) -> torch.Tensor:
     """out[M, N/2] = act(gate) * up, where `weight` [N, K] holds gate and up rows interleaved in eights
     (rows 16b..16b+7 are gate rows 8b..8b+7, rows 16b+8..16b+15 their up rows): product, activation and
-    multiply in one kernel.  bfloat16, at most 64 rows of x."""
+    multiply in one kernel (bfloat16)."""
     _on_gpu(x, weight, out, bias)
     M, K = x.shape
     N = weight.shape[0]
     assert weight.shape[1] == K and out.shape == (M, N // 2) and gated_linear_supported(x, weight)
-    return _skinny(x, weight, out, bias, ACTIVATIONS[activation])
+    if M <= SKINNY_MAX_ROWS:
+        return _skinny(x, weight, out, bias, ACTIVATIONS[activation])
+    return gemm_tcgen05(x, weight, out, bias, activation)
 
 
 def act_mul_interleaved(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> torch.Tensor:

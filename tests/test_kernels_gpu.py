@@ -436,3 +436,38 @@ def test_skinny_slices_leave_their_counters_at_zero():
     torch.cuda.synchronize()
     assert int(scratch_for(x.device).gemm_counters.abs().sum()) == 0
     assert int(scratch_for(x.device).attention_counters.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (2048, 2048, 2048), (300, 1000, 96), (77, 136, 40), (129, 3072, 2048),
+                                   (1024, 16384, 512), (256, 2048, 8192)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gemm_tcgen05(M, N, K, with_bias):
+    """The tcgen05 / TMA / tensor-memory product against a float64 product, at sizes that leave ragged tiles in
+    every direction; no wait inside the kernel may have given up."""
+    from liteinfer_b200 import ops
+
+    x, w = _randn(M, K, dtype=torch.bfloat16), _randn(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    b = _randn(N, dtype=torch.bfloat16, seed=2) if with_bias else None
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tcgen05(x, w, out, b)
+    want = x.double() @ w.double().t() + (b.double() if with_bias else 0)
+    assert ops.gemm_error_flag("cuda:0") == 0
+    torch.testing.assert_close(out.double(), want, rtol=2 ** -7, atol=2 ** -6)
+
+
+@pytest.mark.parametrize("M,inter,K,act", [(2048, 8192, 2048, "silu"), (130, 176, 64, "gelu_pytorch_tanh"),
+                                           (500, 112, 120, "relu")])
+def test_gemm_tcgen05_gated_epilogue(M, inter, K, act):
+    """act(gate) * up in the product's epilogue equals the library product followed by the activation kernel,
+    bit for bit without a bias (the same sums rounded at the same places)."""
+    from liteinfer_b200 import ops
+
+    dt = torch.bfloat16
+    x = _randn(M, K, dtype=dt)
+    w = _interleave(_randn(inter, K, dtype=dt, seed=1, scale=0.05), _randn(inter, K, dtype=dt, seed=2, scale=0.05))
+    got = ops.gated_linear(x, w, torch.empty(M, inter, dtype=dt, device="cuda"), act)
+    gu = ops.linear(x, w, torch.empty(M, 2 * inter, dtype=dt, device="cuda"))
+    two = ops.act_mul_interleaved(gu, torch.empty(M, inter, dtype=dt, device="cuda"), act)
+    assert ops.gemm_error_flag("cuda:0") == 0
+    # the library may add its products in another order: a rounding of the bfloat16 product apart at most
+    torch.testing.assert_close(got.float(), two.float(), rtol=2 ** -6, atol=2 ** -6)
