@@ -125,11 +125,10 @@ __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParam
 }
 
 // kDecode: every launched sequence brings one token and the group has at most 16 heads.
-template <int D, bool kDecode>
+template <int D, bool kDecode, int kStages>   // kStages: K/V tiles in flight per block
 __global__ void __launch_bounds__(kWarps * 32)
 attention_mma_kernel(const AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  constexpr int kStages = 2;   // K/V tiles in flight per block
   constexpr int kQRows = kDecode ? 16 : kBlockM;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);           // [kQRows][D]
   bf16* kbuf = qs + kQRows * D;                           // kStages x [64][D]
@@ -461,21 +460,20 @@ attention_mma_kernel(const AttnParams p) {
   if (threadIdx.x == 0) p.counters[counter_index] = 0;   // ready for the next launch
 }
 
-template <int D, bool kDecode>
+template <int D, bool kDecode, int kStages>
 int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, cudaStream_t stream) {
   const int groups = p.heads / p.kv_heads;
   const int tq = (kDecode ? 16 : kBlockM) / groups;
-  constexpr int kStages = 2;
   const size_t smem = (size_t)((kDecode ? 16 : kBlockM) + 2 * kStages * kBlockN) * D * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D, kDecode>,
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D, kDecode, kStages>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const dim3 grid(((max_q_len + tq - 1) / tq) * p.num_splits, p.kv_heads, num_seqs);
-  return (int)launch_pdl(attention_mma_kernel<D, kDecode>, grid, dim3(kWarps * 32), smem, stream, p);
+  return (int)launch_pdl(attention_mma_kernel<D, kDecode, kStages>, grid, dim3(kWarps * 32), smem, stream, p);
 }
 
 }  // namespace li
@@ -519,9 +517,19 @@ LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out,
     for (int s = 0; s < 31; ++s)
       if ((1 << s) == page_size) p.page_shift = s;
   const bool decode = max_q_len == 1 && groups <= 16;
+  if (!decode)
+    return head_dim == 64 ? launch_attention<64, false, 2>(p, num_seqs, max_q_len, stream)
+                          : launch_attention<128, false, 2>(p, num_seqs, max_q_len, stream);
+  // Few blocks (a narrow batch): each keeps more tiles in flight.  Many blocks: more of them per SM instead.
+  static int deep_override = -1;
+  if (deep_override < 0) {
+    const char* e = getenv("LITEINFER_DECODE_STAGES");
+    deep_override = e ? atoi(e) : 0;
+  }
+  const bool deep = deep_override ? deep_override >= 3 : (long)num_seqs * kv_heads * num_splits <= 3 * 148;
   if (head_dim == 64)
-    return decode ? launch_attention<64, true>(p, num_seqs, max_q_len, stream)
-                  : launch_attention<64, false>(p, num_seqs, max_q_len, stream);
-  return decode ? launch_attention<128, true>(p, num_seqs, max_q_len, stream)
-                : launch_attention<128, false>(p, num_seqs, max_q_len, stream);
+    return deep ? launch_attention<64, true, 4>(p, num_seqs, max_q_len, stream)
+                : launch_attention<64, true, 2>(p, num_seqs, max_q_len, stream);
+  return deep ? launch_attention<128, true, 3>(p, num_seqs, max_q_len, stream)
+              : launch_attention<128, true, 2>(p, num_seqs, max_q_len, stream);
 }

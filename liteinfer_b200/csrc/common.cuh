@@ -102,13 +102,34 @@ template <typename T> __device__ __forceinline__ void store16(T* p, const Vec16<
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" :::); }
 
-inline bool pdl_enabled() {
-  static int enabled = -1;
-  if (enabled < 0) {
+// LITEINFER_PDL: 0 = every kernel launched the ordinary way; 1 = every kernel may start early; 2 (default) =
+// only the kernels that have something to prefetch before their wait (the weight-streaming products).
+inline int pdl_mode() {
+  static int mode = -1;
+  if (mode < 0) {
     const char* e = getenv("LITEINFER_PDL");
-    enabled = (e && e[0] == '1') ? 1 : 0;   // off unless LITEINFER_PDL=1: measured slower on B200 with CUDA graphs
+    mode = e ? atoi(e) : 2;
   }
-  return enabled == 1;
+  return mode;
+}
+inline bool pdl_enabled() { return pdl_mode() == 1; }
+
+// Launches `kernel`, with programmatic stream serialization when `early` (it may then start before the kernel
+// ahead of it has finished, and must call grid_dependency_wait() before it reads that kernel's results).
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_maybe_early(bool early, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = early ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
 }
 
 // Launches `kernel`, with programmatic stream serialization when LITEINFER_PDL=1.
