@@ -102,13 +102,14 @@ template <typename T> __device__ __forceinline__ void store16(T* p, const Vec16<
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" :::); }
 
-// LITEINFER_PDL: 0 = every kernel launched the ordinary way; 1 = every kernel may start early; 2 (default) =
-// only the kernels that have something to prefetch before their wait (the weight-streaming products).
+// LITEINFER_PDL: 0 = every kernel launched the ordinary way; 1 (default) = every kernel of the decode path may
+// start early; 2 = only the kernels that have something to prefetch before their wait (the weight-streaming
+// products).
 inline int pdl_mode() {
   static int mode = -1;
   if (mode < 0) {
     const char* e = getenv("LITEINFER_PDL");
-    mode = e ? atoi(e) : 2;
+    mode = e ? atoi(e) : 1;
   }
   return mode;
 }
