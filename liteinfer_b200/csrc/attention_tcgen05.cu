@@ -1,0 +1,411 @@
+// Paged attention for prompts and portions of prompts on the fifth-generation tensor cores
+// (bfloat16, head size 64, pages of 16, 32 or 64 tokens).
+//
+// Rule as in attention_generic.cu (liteinfer/models/attention.py:24-27,69-84).  A block owns 128
+// rows for one KV head, a row being (query token, head of the group), and walks the visible keys
+// in tiles of 64:
+//
+//   loader  (warp 0)    TMA: each page of a tile's keys and values is one box of the pool's tensor map,
+//                       landing in 128-byte-swizzled shared memory, three tiles ahead at most.
+//   issuer  (warp 1)    tcgen05.mma: S = Q K^T (128 x 64, K 64) into one of two score buffers in tensor
+//                       memory, then O += P V (128 x 64, K 64 keys) into the output accumulator;
+//                       S of the next tile is issued before P V of this one, so the tensor cores work
+//                       while the softmax of this tile is computed.
+//   softmax (warps 2-5) one thread per row: tcgen05.ld brings the row's 64 scores into registers, so
+//                       maximum and sum need no exchange between threads; the probabilities go to
+//                       shared memory as bfloat16 in the layout tcgen05.mma reads; the accumulator in
+//                       tensor memory is rescaled (ld, multiply, st) only when a row's maximum moved.
+//
+// Scores, maximum, sum and accumulator are 32-bit; probabilities are rounded to bfloat16 for P V
+// (liteinfer/models/paged_kernels.py:282-284).  Keys outside the visible range are masked to -inf and
+// their value rows are zeroed in shared memory, so an unwritten slot of a page cannot leak.
+// Every mbarrier wait is bounded (see tcgen05.cuh); a wait that runs out sets `error_flag`.
+#include <map>
+#include <tuple>
+
+#include "tcgen05.cuh"
+
+namespace li {
+
+constexpr int kRows = 128;       // rows (query token x head in group) per block
+constexpr int kKeys = 64;        // keys per tile
+constexpr int kHeadDim = 64;
+constexpr int kKvStages = 3;
+constexpr int kAttnThreads = 192;
+constexpr float kLog2eF = 1.4426950408889634f;
+
+struct TcAttnParams {
+  const bf16* q;
+  int q_row_stride;
+  bf16* out;
+  int out_row_stride;
+  const int* block_table;
+  int table_stride;
+  const int* query_start_loc;
+  const int* context_lens;
+  const int* seq_index;
+  int heads, kv_heads, page_size, page_shift, num_pages;
+  float scale_log2;
+  int window;
+  int* error_flag;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 2)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                         const TcAttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  constexpr unsigned kTileBytes = kKeys * kHeadDim * 2;             // 8 KB: one K or V tile
+  constexpr unsigned kRowTileBytes = kRows * kHeadDim * 2;          // 16 KB: Q, or one P buffer
+  const unsigned q_smem = base;
+  const unsigned p_smem = q_smem + kRowTileBytes;                   // 2 buffers
+  const unsigned k_smem = p_smem + 2 * kRowTileBytes;               // kKvStages
+  const unsigned v_smem = k_smem + kKvStages * kTileBytes;          // kKvStages
+  const unsigned bars = v_smem + kKvStages * kTileBytes;
+  auto k_full = [&](int s) { return bars + 8u * s; };
+  auto v_full = [&](int s) { return bars + 8u * (kKvStages + s); };
+  auto kv_empty = [&](int s) { return bars + 8u * (2 * kKvStages + s); };
+  auto s_full = [&](int b) { return bars + 8u * (3 * kKvStages + b); };
+  auto s_free = [&](int b) { return bars + 8u * (3 * kKvStages + 2 + b); };
+  auto p_full = [&](int b) { return bars + 8u * (3 * kKvStages + 4 + b); };
+  auto pv_done = [&](int b) { return bars + 8u * (3 * kKvStages + 6 + b); };
+  const unsigned tmem_slot = bars + 8u * (3 * kKvStages + 8);
+  __shared__ unsigned tmem_base_shared;
+  unsigned char* generic_base = smem_raw + (base - smem_addr(smem_raw));   // the same place as a generic pointer
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
+  const int kvh = blockIdx.y;
+  const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
+  const int groups = p.heads / p.kv_heads;
+  const int tq = kRows / groups;
+  // The last query tiles see the most keys: they are handed out first, so that the long blocks do not end up alone.
+  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tq;
+  if (q0 >= q_len) return;
+  const int ctx = p.context_lens[seq];
+  const int tile_q = min(tq, q_len - q0);
+  const int rows_used = tile_q * groups;
+  const int* table = p.block_table + (size_t)seq * p.table_stride;
+  const int first_qpos = ctx - q_len + q0, last_qpos = first_qpos + tile_q - 1;
+  const int hi = last_qpos + 1;
+  const int lo = (p.window > 0 && first_qpos - p.window + 1 > 0) ? first_qpos - p.window + 1 : 0;
+  const int tile_lo = lo / kKeys, tile_hi = (hi + kKeys - 1) / kKeys;
+  const int ntiles = tile_hi - tile_lo;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_full(b), 1);
+      mbar_init(s_free(b), 4);
+      mbar_init(p_full(b), 4);
+      mbar_init(pv_done(b), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // scores 2 x 64 columns, output 64 columns: 256 columns asked for (a power of two)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // Q: each softmax thread copies its row (128 bytes) into the swizzled tile; rows of padding are zero.
+  if (warp >= 2) {
+    const int row = (warp & 3) * 32 + lane;
+    uint4 v[8];
+    if (row < rows_used) {
+      const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + qi) * p.q_row_stride + (size_t)head * kHeadDim);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[c] = src[c];
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[c] = make_uint4(0, 0, 0, 0);
+    }
+    unsigned char* dst = generic_base + (q_smem - base) + row * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = v[c];
+    fence_async_shared();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  if (threadIdx.x == 0) {
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(tmem_slot));
+    tmem_base_shared = v;
+  }
+  __syncthreads();
+  const unsigned tmem_base = tmem_base_shared;
+  const unsigned tmem_s[2] = {tmem_base, tmem_base + 64u};
+  const unsigned tmem_o = tmem_base + 128u;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0) {
+      const int boxes = kKeys / p.page_size;
+      const unsigned box_bytes = (unsigned)p.page_size * kHeadDim * 2;
+      for (int t = 0; t < ntiles; ++t) {
+        const int stage = t % kKvStages;
+        const unsigned phase = (unsigned)(t / kKvStages) & 1;
+        if (!mbar_wait(kv_empty(stage), phase ^ 1, p.error_flag, 11)) break;
+        const int key0 = (tile_lo + t) * kKeys;
+        int rows[4];
+        int valid = 0;
+        for (int b = 0; b < boxes; ++b) {
+          const int kpos = key0 + b * p.page_size;
+          int page = -1;
+          if (kpos < hi && kpos + p.page_size > lo) page = table[kpos >> p.page_shift];
+          rows[b] = (page >= 0 && page < p.num_pages) ? (page * p.kv_heads + kvh) * p.page_size : -1;
+          valid += rows[b] >= 0;
+        }
+        mbar_expect_tx(k_full(stage), valid * box_bytes);
+        mbar_expect_tx(v_full(stage), valid * box_bytes);
+        for (int b = 0; b < boxes; ++b) {
+          if (rows[b] < 0) continue;
+          tma_load_2d(k_smem + stage * kTileBytes + b * box_bytes, &map_k, k_full(stage), 0, rows[b]);
+          tma_load_2d(v_smem + stage * kTileBytes + b * box_bytes, &map_v, v_full(stage), 0, rows[b]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ issuer
+    if (lane == 0) {
+      // f32 accumulate, bf16 x bf16, M 128, N 64; for P V the second operand (values) is N-major.
+      constexpr unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(kKeys >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
+      constexpr unsigned idesc_pv = idesc_qk | (1u << 16);
+      auto issue_qk = [&](int t) -> bool {
+        const int stage = t % kKvStages, buf = t & 1;
+        if (t >= 2 && !mbar_wait(s_free(buf), (unsigned)((t - 2) >> 1) & 1, p.error_flag, 12)) return false;
+        if (!mbar_wait(k_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 13)) return false;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int k = 0; k < kHeadDim / 16; ++k)
+          umma_bf16(tmem_s[buf], umma_desc(q_smem + k * 32), umma_desc(k_smem + stage * kTileBytes + k * 32), idesc_qk, k > 0);
+        umma_commit(s_full(buf));
+        return true;
+      };
+      bool ok = ntiles > 0 && issue_qk(0);
+      for (int t = 0; ok && t < ntiles; ++t) {
+        if (t + 1 < ntiles && !issue_qk(t + 1)) { ok = false; break; }
+        const int stage = t % kKvStages, buf = t & 1;
+        if (!mbar_wait(v_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 14)) { ok = false; break; }
+        if (!mbar_wait(p_full(buf), (unsigned)(t >> 1) & 1, p.error_flag, 15)) { ok = false; break; }
+        tcgen05_fence_after();
+#pragma unroll
+        for (int k = 0; k < kKeys / 16; ++k)
+          umma_bf16(tmem_o, umma_desc(p_smem + buf * kRowTileBytes + k * 32),
+                    umma_desc(v_smem + stage * kTileBytes + k * 16 * 128), idesc_pv, t > 0 || k > 0);
+        umma_commit(kv_empty(stage));
+        umma_commit(pv_done(buf));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const unsigned lane_field = (unsigned)(quarter * 32) << 16;
+    const int qpos = row < rows_used ? first_qpos + row / groups : -1;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int t = 0; ok && t < ntiles; ++t) {
+      const int buf = t & 1, stage = t % kKvStages;
+      const int key0 = (tile_lo + t) * kKeys;
+      if (!mbar_wait(s_full(buf), (unsigned)(t >> 1) & 1, p.error_flag, 16)) { ok = false; break; }
+      tcgen05_fence_after();
+      unsigned sa[32], sb[32];
+      __syncwarp();
+      tmem_load32(tmem_s[buf] + lane_field, sa);
+      tmem_load32(tmem_s[buf] + lane_field + 32, sb);
+      tmem_load_wait();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free(buf));
+
+      const bool all_visible = key0 + kKeys - 1 <= first_qpos && (p.window <= 0 || key0 > last_qpos - p.window);
+      float mx = m;
+      if (all_visible && qpos >= 0) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int ka = key0 + j, kb = key0 + 32 + j;
+          const bool va = ka <= qpos && (p.window <= 0 || ka > qpos - p.window);
+          const bool vb = kb <= qpos && (p.window <= 0 || kb > qpos - p.window);
+          if (!va) sa[j] = __float_as_uint(-INFINITY);
+          if (!vb) sb[j] = __float_as_uint(-INFINITY);
+          mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
+        }
+      }
+      // mx is in units of raw scores; exp2 arguments are (s - mx) * scale_log2.
+      const float m_use = mx == -INFINITY ? 0.f : mx;
+      const float alpha = ex2((m - m_use) * p.scale_log2);      // m = -inf gives 0
+      const float neg = -m_use * p.scale_log2;
+      // P for this tile overwrites the buffer that P V of tile t-2 read, and the accumulator may be rescaled only
+      // once P V of tile t-1 has landed: both hold once pv_done of tile t-1 has fired.
+      if (t >= 1 && !mbar_wait(pv_done((t - 1) & 1), (unsigned)((t - 1) >> 1) & 1, p.error_flag, 17)) { ok = false; break; }
+      tcgen05_fence_after();
+      if (t >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        unsigned o[32];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          tmem_load32(tmem_o + lane_field + half * 32, o);
+          tmem_load_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_store32(tmem_o + lane_field + half * 32, o);
+        }
+        tmem_store_wait();
+      }
+      m = mx;
+      float sum = 0.f;
+      unsigned char* prow = generic_base + (p_smem - base) + buf * kRowTileBytes + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {       // chunk of 8 keys = 16 bytes of bfloat16
+        unsigned w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = c * 8 + 2 * e;
+          const float x0 = __uint_as_float(j < 32 ? sa[j] : sb[j - 32]);
+          const float x1 = __uint_as_float(j + 1 < 32 ? sa[j + 1] : sb[j + 1 - 32]);
+          const float e0 = ex2(fmaf(x0, p.scale_log2, neg)), e1 = ex2(fmaf(x1, p.scale_log2, neg));
+          sum += e0 + e1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+          w[e] = *reinterpret_cast<unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l = l * alpha + sum;
+      // Value rows of keys outside [lo, hi) may hold anything (an unwritten slot): zero them before P V reads them.
+      if (key0 < lo || key0 + kKeys > hi) {
+        if (!mbar_wait(v_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 18)) { ok = false; break; }
+        unsigned char* vt = generic_base + (v_smem - base) + stage * kTileBytes;
+        for (int e = threadIdx.x - 64; e < kKeys * 8; e += 128) {
+          const int key = e >> 3;
+          const int kpos = key0 + key;
+          if (kpos < lo || kpos >= hi) *reinterpret_cast<uint4*>(vt + key * 128 + ((e & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      fence_async_shared();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(buf));
+    }
+    // Output: wait for the last P V, read the row, divide by the row's sum, store.
+    if (ok && ntiles > 0 && mbar_wait(pv_done((ntiles - 1) & 1), (unsigned)((ntiles - 1) >> 1) & 1, p.error_flag, 19)) {
+      tcgen05_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+      bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * kHeadDim;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        unsigned o[32];
+        __syncwarp();
+        tmem_load32(tmem_o + lane_field + half * 32, o);
+        tmem_load_wait();
+        if (row < rows_used) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            unsigned w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[v * 8 + 2 * e]) * inv,
+                                                       __uint_as_float(o[v * 8 + 2 * e + 1]) * inv);
+              w[e] = *reinterpret_cast<unsigned*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + half * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  }
+}
+
+// The pool [pages, kv_heads, page_size, 64] as a 2-D map of rows of 64, one page of one head per box.
+static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int page_size) {
+  static std::map<std::tuple<const void*, long, int>, CUtensorMap> cache;
+  const auto key = std::make_tuple(pool, rows, page_size);
+  const auto found = cache.find(key);
+  if (found != cache.end()) {
+    *map = found->second;
+    return true;
+  }
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)kHeadDim * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kHeadDim, (cuuint32_t)page_size};
+  const cuuint32_t elem[2] = {1, 1};
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *map);
+  return true;
+}
+
+}  // namespace li
+
+using namespace li;
+
+// Whether li_paged_attention_tcgen05 takes these sizes.
+LI_EXPORT int li_paged_attention_tcgen05_supports(int heads, int kv_heads, int head_dim, int page_size) {
+  if (kv_heads < 1 || heads % kv_heads || head_dim != kHeadDim) return 0;
+  const int groups = heads / kv_heads;
+  if (groups > kRows || (kRows % groups)) return 0;
+  return page_size == 16 || page_size == 32 || page_size == 64;
+}
+
+// bfloat16; head_dim 64; page_size 16, 32 or 64; groups dividing 128.  Sequences may bring any number of queries
+// (the kernel is meant for those that bring many).  error_flag (device int, zero): set if a wait inside gave up.
+LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                         const void* k_pool, const void* v_pool, const int* block_table,
+                                         int table_stride, const int* query_start_loc, const int* context_lens,
+                                         const int* seq_index, int num_seqs, int max_q_len, int heads, int kv_heads,
+                                         int head_dim, int page_size, int num_pages, float scale, int window,
+                                         int* error_flag, cudaStream_t stream) {
+  if (num_seqs == 0 || max_q_len == 0) return 0;
+  if (!li_paged_attention_tcgen05_supports(heads, kv_heads, head_dim, page_size)) return LI_ERR_UNSUPPORTED;
+  if (kv_heads > 65535 || num_seqs > 65535) return LI_ERR_UNSUPPORTED;
+  if ((q_row_stride % 8) || (out_row_stride % 8) || !aligned16(q) || !aligned16(out) || !aligned16(k_pool) ||
+      !aligned16(v_pool))
+    return LI_ERR_ALIGNMENT;
+  CUtensorMap mk, mv;
+  const long rows = (long)num_pages * kv_heads * page_size;
+  if (!make_pool_map(&mk, k_pool, rows, page_size) || !make_pool_map(&mv, v_pool, rows, page_size))
+    return LI_ERR_UNSUPPORTED;
+  int shift = 0;
+  while ((1 << shift) < page_size) ++shift;
+  TcAttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, block_table, table_stride,
+                 query_start_loc, context_lens, seq_index, heads, kv_heads, page_size, shift, num_pages,
+                 scale * kLog2eF, window, error_flag};
+  constexpr size_t smem = 3 * (size_t)kRows * kHeadDim * 2 + 2 * kKvStages * (size_t)kKeys * kHeadDim * 2 +
+                          8 * (3 * kKvStages + 8) + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int groups = heads / kv_heads;
+  const int tq = kRows / groups;
+  const dim3 grid((max_q_len + tq - 1) / tq, kv_heads, num_seqs);
+  attention_tcgen05_kernel<<<grid, kAttnThreads, smem, stream>>>(mk, mv, p);
+  return (int)cudaGetLastError();
+}

@@ -45,6 +45,10 @@ _SIGNATURES = {
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
         c_void_p]),
     "li_paged_attention_mma_counters": ("attention_mma", [c_int, c_int, c_int, c_int]),
+    "li_paged_attention_tcgen05": ("attention_tcgen05", [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
+    "li_paged_attention_tcgen05_supports": ("attention_tcgen05", [c_int, c_int, c_int, c_int]),
     "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_void_p, c_size_t, c_void_p, c_int, c_void_p]),
     "li_gemm_skinny_slices": ("gemm_skinny", [c_int, c_int, c_void_p]),
@@ -414,6 +418,26 @@ def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query
     return out
 
 
+def paged_attention_tcgen05(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
+                            seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0) -> torch.Tensor:
+    """The tcgen05 / TMA / tensor-memory attention kernel for prompts and portions (bfloat16, head size 64,
+    pages of 16, 32 or 64 tokens, groups dividing 128).  `gemm_error_flag(device)` tells afterwards whether a
+    wait inside the kernel ever gave up."""
+    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
+    pages, kvh, page_size, hd = k_pool.shape
+    _check(_fn("li_paged_attention_tcgen05")(
+        q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
+        _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
+        int(window), scratch_for(q.device).gemm_error.data_ptr(), _stream()), "paged_attention_tcgen05")
+    return out
+
+
+def tcgen05_attention_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and bool(
+        _fn("li_paged_attention_tcgen05_supports")(heads, kv_heads, head_dim, page_size))
+
+
 def mma_attention_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim in (64, 128) and heads // kv_heads <= 64
 
@@ -443,8 +467,10 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     if plan is None:
         return paged_attention_mma(*common, None, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window)
     if plan.num_prefill:
-        paged_attention_mma(*common, plan.prefill_seqs, plan.num_prefill, plan.max_prefill_query_len, heads,
-                            kv_heads, head_dim, scale, window)
+        many = (paged_attention_tcgen05 if tcgen05_attention_supports(q.dtype, heads, kv_heads, head_dim, page_size)
+                else paged_attention_mma)
+        many(*common, plan.prefill_seqs, plan.num_prefill, plan.max_prefill_query_len, heads, kv_heads, head_dim,
+             scale, window)
     if plan.num_decode:
         bound = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window)
         splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound)

@@ -471,3 +471,36 @@ def test_gemm_tcgen05_gated_epilogue(M, inter, K, act):
     assert ops.gemm_error_flag("cuda:0") == 0
     # the library may add its products in another order: a rounding of the bfloat16 product apart at most
     torch.testing.assert_close(got.float(), two.float(), rtol=2 ** -6, atol=2 ** -6)
+
+
+@pytest.mark.parametrize("heads,kv_heads,page_size", [(4, 1, 16), (32, 8, 16), (8, 8, 32), (16, 2, 64), (128, 1, 16)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_tcgen05_attention_against_the_plain_kernel(heads, kv_heads, page_size, window):
+    """The tcgen05 / TMA / tensor-memory attention kernel: portions, whole prompts and single tokens over shuffled
+    pages, NaN in every slot no request owns, contexts that straddle the 64-key tiles; no wait may give up."""
+    from liteinfer_b200 import ops
+
+    d = 64
+    q_lens, ctx_lens = [1, 130, 1, 7, 64, 2, 257], [700, 190, 1, 7, 64, 129, 300]
+    case = _paged_case(torch.bfloat16, heads, kv_heads, d, page_size, q_lens, ctx_lens)
+    qkv, k_pool, v_pool = case["qkv"], case["k_pool"], case["v_pool"]
+    ops.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_pool, v_pool, None, heads, kv_heads, d, 0)
+    rest = (k_pool, v_pool, case["table"], case["qsl"], case["ctx"])
+    tail = (case["B"], max(q_lens), heads, kv_heads, d, d ** -0.5, window)
+    want = ref.paged_attention(qkv, qkv.shape[1], torch.empty(case["T"], heads * d, dtype=torch.bfloat16, device="cuda"),
+                               *rest, *tail)
+    out = torch.full((case["T"], heads * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.tcgen05_attention_supports(torch.bfloat16, heads, kv_heads, d, page_size)
+    ops.paged_attention_tcgen05(qkv, qkv.shape[1], out, *rest, None, *tail)
+    assert ops.gemm_error_flag("cuda:0") == 0
+    assert torch.isfinite(out.float()).all()
+    torch.testing.assert_close(out.float(), want.float(), rtol=2 ** -6, atol=2 ** -6)
+
+
+def test_tcgen05_attention_refuses_what_it_cannot_do():
+    from liteinfer_b200 import ops
+
+    assert not ops.tcgen05_attention_supports(torch.bfloat16, 6, 2, 64, 16)      # groups of 3 do not divide 128
+    assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 128, 16)     # head size 128: the mma.sync kernel
+    assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 64, 8)       # pages of 8
+    assert not ops.tcgen05_attention_supports(torch.float32, 4, 2, 64, 16)
