@@ -53,6 +53,16 @@ def skinny(M: int, N: int, K: int) -> dict:
             "slices": ops.gemm_skinny_slices(N, K)}
 
 
+def tcgen05_gemm(M: int, N: int, K: int, gated: bool = False) -> dict:
+    copies = max(2, (300 << 20) // (N * K * 2) + 1)
+    w = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N // 2 if gated else N, device="cuda", dtype=torch.bfloat16)
+    us = _time(lambda i: ops.gemm_tcgen05(x, w[i], out, None, "silu" if gated else None), copies)
+    return {"kernel": "gemm_tcgen05" + ("+silu*up" if gated else ""), "M": M, "N": N, "K": K, "us": us,
+            "TFLOPs": 2.0 * M * N * K / us / 1e6, "wait_that_gave_up": ops.gemm_error_flag("cuda:0")}
+
+
 def library_gemm(M: int, N: int, K: int) -> dict:
     copies = max(2, (300 << 20) // (N * K * 2) + 1)
     w = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
@@ -110,6 +120,8 @@ CASES = {
     "decode_attention_b1": lambda: attention(1, 1, 4096),
     "decode_attention_b64": lambda: attention(64, 1, 4096),
     "prefill_attention_2048": lambda: attention(1, 2048, 2048),
+    "prefill_attention_4x2048_ctx4096": lambda: attention(4, 2048, 4096),
+    "prefill_attention_2048_head128": lambda: attention(1, 2048, 2048, heads=32, kv_heads=8, head_dim=128),
     "skinny_qkv_b8": lambda: skinny(8, 3072, 2048),
     "skinny_o_b8": lambda: skinny(8, 2048, 2048),
     "skinny_gate_up_b8": lambda: skinny(8, 16384, 2048),
@@ -123,6 +135,11 @@ CASES = {
     "library_down_b8": lambda: library_gemm(8, 2048, 8192),
     "library_qkv_b8": lambda: library_gemm(8, 3072, 2048),
     "library_gate_up_b64": lambda: library_gemm(64, 16384, 2048),
+    "tcgen05_gate_up_2048": lambda: tcgen05_gemm(2048, 16384, 2048),
+    "tcgen05_gate_up_silu_2048": lambda: tcgen05_gemm(2048, 16384, 2048, gated=True),
+    "tcgen05_down_2048": lambda: tcgen05_gemm(2048, 2048, 8192),
+    "tcgen05_qkv_2048": lambda: tcgen05_gemm(2048, 3072, 2048),
+    "library_qkv_2048": lambda: library_gemm(2048, 3072, 2048),
     "library_gate_up_2048": lambda: library_gemm(2048, 16384, 2048),
     "library_down_2048": lambda: library_gemm(2048, 2048, 8192),
     "add_rmsnorm_b8": lambda: rmsnorm(8, 2048),
