@@ -473,7 +473,7 @@ int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, cudaStrea
     configured = true;
   }
   const dim3 grid(((max_q_len + tq - 1) / tq) * p.num_splits, p.kv_heads, num_seqs);
-  return (int)launch_pdl(attention_mma_kernel<D, kDecode, kStages>, grid, dim3(kWarps * 32), smem, stream, p);
+  return (int)launch_pdl((long)num_seqs * max_q_len, attention_mma_kernel<D, kDecode, kStages>, grid, dim3(kWarps * 32), smem, stream, p);
 }
 
 }  // namespace li

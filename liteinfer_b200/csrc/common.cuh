@@ -102,9 +102,10 @@ template <typename T> __device__ __forceinline__ void store16(T* p, const Vec16<
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" :::); }
 
-// LITEINFER_PDL: 0 = every kernel launched the ordinary way; 1 (default) = every kernel of the decode path may
-// start early; 2 = only the kernels that have something to prefetch before their wait (the weight-streaming
-// products).
+// LITEINFER_PDL: 0 = every kernel launched the ordinary way; 1 (default) = the kernels of a narrow decode step
+// (at most kEarlyLaunchRows rows: the steps whose products stream their weights through gemm_skinny) may start
+// early; 2 = of those only the weight-streaming products.  Wider steps mix in library kernels, and early
+// launches beside them measured slower (batch 64: 3.65 ms against 3.46 ms per step).
 inline int pdl_mode() {
   static int mode = -1;
   if (mode < 0) {
@@ -113,7 +114,8 @@ inline int pdl_mode() {
   }
   return mode;
 }
-inline bool pdl_enabled() { return pdl_mode() == 1; }
+constexpr int kEarlyLaunchRows = 8;
+inline bool pdl_enabled(long rows) { return pdl_mode() == 1 && rows <= kEarlyLaunchRows; }
 
 // Launches `kernel`, with programmatic stream serialization when `early` (it may then start before the kernel
 // ahead of it has finished, and must call grid_dependency_wait() before it reads that kernel's results).
@@ -133,10 +135,10 @@ inline cudaError_t launch_maybe_early(bool early, void (*kernel)(KernelArgs...),
   return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
 }
 
-// Launches `kernel`, with programmatic stream serialization when LITEINFER_PDL=1.
+// Launches `kernel` of a step that is `rows` rows wide, early when the mode and the width allow it.
 template <typename... KernelArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              Args... args) {
+inline cudaError_t launch_pdl(long rows, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -146,7 +148,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 blo
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = pdl_enabled() ? 1 : 0;
+  config.numAttrs = pdl_enabled(rows) ? 1 : 0;
   return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
 }
 

@@ -235,7 +235,7 @@ template <typename T>
 int launch_embedding(const int* ids, const void* table, void* out, int tokens, int width, int vocab,
                      int* error_flag, cudaStream_t s) {
   if (tokens == 0) return 0;
-  return (int)launch_pdl(embedding_kernel<T>, dim3(tokens), dim3(128), 0, s, ids, (const T*)table, (T*)out, width,
+  return (int)launch_pdl(tokens, embedding_kernel<T>, dim3(tokens), dim3(128), 0, s, ids, (const T*)table, (T*)out, width,
                          vocab, error_flag);
 }
 
@@ -250,11 +250,11 @@ int launch_rmsnorm(void* x, const void* delta, const void* weight, void* out, co
   T* xp = (T*)x;
   const T *dp = (const T*)delta, *wp = (const T*)weight;
   T* op = (T*)out;
-  if (need <= 1) return (int)launch_pdl(rmsnorm_reg_kernel<T, 1>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
-  if (need <= 2) return (int)launch_pdl(rmsnorm_reg_kernel<T, 2>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
-  if (need <= 4) return (int)launch_pdl(rmsnorm_reg_kernel<T, 4>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
+  if (need <= 1) return (int)launch_pdl(out_rows, rmsnorm_reg_kernel<T, 1>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
+  if (need <= 2) return (int)launch_pdl(out_rows, rmsnorm_reg_kernel<T, 2>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
+  if (need <= 4) return (int)launch_pdl(out_rows, rmsnorm_reg_kernel<T, 4>, dim3(out_rows), dim3(256), 0, s, xp, dp, wp, op, rows, width, eps, write_residual);
   const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  return (int)launch_pdl(rmsnorm_kernel<T>, dim3(out_rows), dim3(block), 0, s, xp, dp, wp, op, rows, width, eps,
+  return (int)launch_pdl(out_rows, rmsnorm_kernel<T>, dim3(out_rows), dim3(block), 0, s, xp, dp, wp, op, rows, width, eps,
                          write_residual);
 }
 

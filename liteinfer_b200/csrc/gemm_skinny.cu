@@ -28,7 +28,7 @@ namespace li {
 template <int NT>
 int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
   const dim3 grid((p.N + 15) / 16, p.num_slices);
-  return (int)launch_maybe_early(pdl_mode() >= 1, gemm_skinny_kernel<NT>, grid, dim3(kSkinnyWarps * 32), 0, s, p);
+  return (int)launch_maybe_early(pdl_mode() >= 1 && p.M <= kEarlyLaunchRows, gemm_skinny_kernel<NT>, grid, dim3(kSkinnyWarps * 32), 0, s, p);
 }
 
 }  // namespace li

@@ -92,10 +92,10 @@ LI_EXPORT int li_rope_kv_write(int dtype, void* qkv, const int* positions, const
   if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
   const int block = 256;
   if (dtype == kFloat32)
-    return (int)launch_pdl(rope_kv_write_kernel<float>, dim3(tokens), dim3(block), smem, stream, (float*)qkv,
+    return (int)launch_pdl(tokens, rope_kv_write_kernel<float>, dim3(tokens), dim3(block), smem, stream, (float*)qkv,
                            positions, seq_of_token, block_table, table_stride, (float*)k_pool, (float*)v_pool,
                            inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size, num_pages);
-  return (int)launch_pdl(rope_kv_write_kernel<bf16>, dim3(tokens), dim3(block), smem, stream, (bf16*)qkv, positions,
+  return (int)launch_pdl(tokens, rope_kv_write_kernel<bf16>, dim3(tokens), dim3(block), smem, stream, (bf16*)qkv, positions,
                          seq_of_token, block_table, table_stride, (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads,
                          kv_heads, head_dim, rotary_dim, page_size, num_pages);
 }

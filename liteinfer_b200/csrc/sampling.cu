@@ -331,9 +331,9 @@ LI_EXPORT int li_argmax(int dtype, const void* logits, int rows, int vocab, int*
     const int chunk = ((vocab + chunks - 1) / chunks + 7) / 8 * 8;
     const dim3 grid(rows, (vocab + chunk - 1) / chunk);
     if (dtype == kFloat32)
-      return (int)launch_pdl(argmax_split_kernel<float>, grid, dim3(kArgmaxThreads), 0, stream,
+      return (int)launch_pdl(rows, argmax_split_kernel<float>, grid, dim3(kArgmaxThreads), 0, stream,
                              (const float*)logits, vocab, chunk, part_value, part_index, counters, out);
-    return (int)launch_pdl(argmax_split_kernel<bf16>, grid, dim3(kArgmaxThreads), 0, stream, (const bf16*)logits,
+    return (int)launch_pdl(rows, argmax_split_kernel<bf16>, grid, dim3(kArgmaxThreads), 0, stream, (const bf16*)logits,
                            vocab, chunk, part_value, part_index, counters, out);
   }
   if (dtype == kFloat32)

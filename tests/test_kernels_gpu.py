@@ -465,7 +465,7 @@ def test_gemm_tcgen05_gated_epilogue(M, inter, K, act):
     dt = torch.bfloat16
     x = _randn(M, K, dtype=dt)
     w = _interleave(_randn(inter, K, dtype=dt, seed=1, scale=0.05), _randn(inter, K, dtype=dt, seed=2, scale=0.05))
-    got = ops.gated_linear(x, w, torch.empty(M, inter, dtype=dt, device="cuda"), act)
+    got = ops.gemm_tcgen05(x, w, torch.empty(M, inter, dtype=dt, device="cuda"), None, act)
     gu = ops.linear(x, w, torch.empty(M, 2 * inter, dtype=dt, device="cuda"))
     two = ops.act_mul_interleaved(gu, torch.empty(M, inter, dtype=dt, device="cuda"), act)
     assert ops.gemm_error_flag("cuda:0") == 0
