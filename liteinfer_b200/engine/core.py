@@ -204,6 +204,8 @@ class EngineCore:
             self.stats.record(StepMetrics(self._step_idx, len(entries), sum(len(e.tokens) for e in entries),
                                           prompt_tokens, len(sampling), time.perf_counter() - start))
         self._step_idx += 1
+        if self._step_idx % 256 == 1:
+            self.runner.check_kernels()
         return result
 
     def _abort(self, seqs: list[Sequence], error: Exception, result: StepResult) -> None:
@@ -213,6 +215,8 @@ class EngineCore:
             result.aborted.append((seq, error))
 
     def close(self) -> None:
+        if self.runner is not None:
+            self.runner.check_kernels()
         self.runner = None
         if self.device.type == "cuda":
             torch.cuda.empty_cache()

@@ -254,6 +254,18 @@ class ModelRunner:
         self.num_steps += 1
         return logits
 
+    def check_kernels(self) -> None:
+        """Raises if a bounded wait inside a tcgen05 kernel ever gave up (the results since the last check are then
+        not to be trusted).  Reads one integer from the device, so callers do it where they synchronise anyway."""
+        if self.device.type != "cuda":
+            return
+        from liteinfer_b200 import ops
+
+        where = ops.gemm_error_flag(self.device)
+        if where:
+            raise RuntimeError(f"a tcgen05 kernel stopped waiting on its pipeline (wait number {where}); "
+                               "its output is unreliable")
+
     def release(self, request_id: str) -> None:
         """The request is finished: what it holds is given back."""
         self.cache.release(request_id)

@@ -80,6 +80,7 @@ def main(argv=None) -> int:
         if args.device.startswith("cuda"):
             torch.cuda.synchronize()
         print(f"done {step}", flush=True)
+    runner.check_kernels()
     return 0
 
 

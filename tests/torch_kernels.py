@@ -165,6 +165,10 @@ def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_sta
     return out
 
 
+def gemm_error_flag(device):
+    return 0
+
+
 def argmax(logits, out):
     out.copy_(torch.argmax(logits.float(), dim=-1).to(torch.int32))
     return out
@@ -206,4 +210,4 @@ def sample(logits, temperature, top_k, top_p, uniform, out):
 
 
 ALL = ("embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
-       "gated_linear", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
+       "gated_linear", "gemm_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
