@@ -76,6 +76,65 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// The same with 16-byte accesses, for bfloat16 with every dimension rotated and halves that are multiples of
+// eight: one work item is eight pairs (j, j + half) of one head, or eight values of v.
+__global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                         const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                         int table_stride, bf16* __restrict__ k_pool, bf16* __restrict__ v_pool,
+                                         const float* __restrict__ inv_freq, int heads, int kv_heads, int head_dim,
+                                         int page_size, int num_pages) {
+  extern __shared__ float cs[];  // cos[half], sin[half]
+  const int t = blockIdx.x;
+  grid_launch_dependents();
+  const int pos = positions[t];
+  const int half = head_dim / 2;
+  float* cosv = cs;
+  float* sinv = cs + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float angle = (float)pos * inv_freq[i];
+    cosv[i] = cosf(angle);
+    sinv[i] = sinf(angle);
+  }
+  const int seq = seq_of_token[t];
+  const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+  grid_dependency_wait();
+  __syncthreads();
+
+  bf16* row = qkv + (size_t)t * (heads + 2 * kv_heads) * head_dim;
+  const bool store = page >= 0 && page < num_pages;
+  const int slot = pos % page_size;
+  const int per_head = half / 8;                       // work items per rotated head
+  const int rotated = (heads + kv_heads) * per_head;   // q heads, then k heads
+  const int copies = kv_heads * (head_dim / 8);        // v
+  for (int w = threadIdx.x; w < rotated + copies; w += blockDim.x) {
+    if (w < rotated) {
+      const int h = w / per_head, j = (w - h * per_head) * 8;
+      bf16* p = row + h * head_dim + j;
+      const Vec16<bf16> a = load16(p), b = load16(p + half);
+      Vec16<bf16> lo, hi;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float c = cosv[j + e], sn = sinv[j + e];
+        lo.set(e, a.get(e) * c - b.get(e) * sn);
+        hi.set(e, b.get(e) * c + a.get(e) * sn);
+      }
+      if (h < heads) {
+        store16(p, lo);
+        store16(p + half, hi);
+      } else if (store) {
+        bf16* dst = k_pool + (((size_t)page * kv_heads + (h - heads)) * page_size + slot) * head_dim + j;
+        store16(dst, lo);
+        store16(dst + half, hi);
+      }
+    } else if (store) {
+      const int c = w - rotated;
+      const int h = c / (head_dim / 8), j = (c % (head_dim / 8)) * 8;
+      const bf16* src = row + (heads + kv_heads + h) * head_dim + j;
+      store16(v_pool + (((size_t)page * kv_heads + h) * page_size + slot) * head_dim + j, load16(src));
+    }
+  }
+}
+
 }  // namespace li
 
 using namespace li;
@@ -91,6 +150,11 @@ LI_EXPORT int li_rope_kv_write(int dtype, void* qkv, const int* positions, const
   const size_t smem = (size_t)rotary_dim * sizeof(float);
   if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
   const int block = 256;
+  if (dtype == kBFloat16 && rotary_dim == head_dim && head_dim % 16 == 0 && aligned16(qkv) && aligned16(k_pool) &&
+      aligned16(v_pool))
+    return (int)launch_pdl(tokens, rope_kv_write_vec_kernel, dim3(tokens), dim3(block), smem, stream, (bf16*)qkv,
+                           positions, seq_of_token, block_table, table_stride, (bf16*)k_pool, (bf16*)v_pool, inv_freq,
+                           heads, kv_heads, head_dim, page_size, num_pages);
   if (dtype == kFloat32)
     return (int)launch_pdl(tokens, rope_kv_write_kernel<float>, dim3(tokens), dim3(block), smem, stream, (float*)qkv,
                            positions, seq_of_token, block_table, table_stride, (float*)k_pool, (float*)v_pool,
