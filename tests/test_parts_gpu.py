@@ -308,3 +308,98 @@ def test_toy_model_generates_through_the_entry_point(toy_model):
              max_num_batched_tokens=5) as llm:
         out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
     assert out[0].token_ids == tokens[12:]
+
+
+def _context_for(cache, entries):
+    """A StepContext for `entries` = [(request id, number of new tokens)], the way the step function builds it."""
+    from liteinfer_b200.engine.runner import StepEntry, _Batch, _context, _fill
+
+    step = [StepEntry(r, [0] * n, ()) for r, n in entries]
+    starts = [cache.length(r) for r, _ in entries]
+    counts = [n for _, n in entries]
+    totals = [s + n for s, n in zip(starts, counts)]
+    cache.reserve([r for r, _ in entries], totals)
+    widths = [max(len(cache.block_table(g, r)) for r, _ in entries) for g in range(len(cache.groups))]
+    n_dec = sum(1 for n in counts if n == 1)
+    batch = _Batch(len(entries), sum(counts), 0, widths, n_dec, len(entries) - n_dec)
+    host = torch.empty(batch.total, dtype=torch.int32)
+    _fill(batch, host.numpy(), step, cache, starts)
+    ctx = _context(batch, host.to(DEV), torch.device(DEV), counts, totals, None,
+                   max((t for t, n in zip(totals, counts) if n == 1), default=0))
+    for (r, _), total in zip(entries, totals):
+        cache.commit(r, total)
+    return ctx
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(4, 2, 16, 8), (8, 2, 64, 16), (6, 6, 48, 4)])
+def test_attention_part_alone(dtype, heads, kv_heads, head_dim, page):
+    """The attention mixer by itself (projections, rotary, cache write, attention over pages, output projection):
+    a sequence fed whole, and the same sequence fed in portions beside another request, against the plain block."""
+    from liteinfer_b200.cache.manager import CacheManager
+    from liteinfer_b200.parts.attention import Attention
+    from liteinfer_b200.parts.spec import PartSpec, ScheduleEntry
+
+    hidden = 96
+    config = {"num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim,
+              "hidden_size": hidden, "rope_theta": 10000.0}
+    part = Attention(hidden_size=hidden, heads=heads, kv_heads=kv_heads, head_dim=head_dim, dtype=dtype,
+                     device=torch.device(DEV), position=PartSpec("rotary", {"head_dim": head_dim, "theta": 10000.0}))
+    tensors = {n: _randn(*s.shape, seed=i, scale=0.08, dtype=dtype) for i, (n, s) in enumerate(part.tensor_specs().items())}
+    part.bind(dict(tensors))
+    x = _randn(70, hidden, seed=40, dtype=dtype)
+    other = _randn(9, hidden, seed=41, dtype=dtype)
+    cos, sin = plain_llama.rope_tables(plain_llama.rope_inverse_frequencies(config), torch.arange(70, device=DEV), torch.float32)
+    w32 = {"p." + n: t.float() for n, t in tensors.items()}
+    want = plain_llama.attention_block(x.float(), w32, "p.", config, cos, sin)
+
+    cache = CacheManager([part.cache_needs()], (ScheduleEntry(0),), page, 40, 4, dtype, DEV)
+    view = cache.layer_caches()[0]
+    whole = part.forward(x, _context_for(cache, [("a", 70)]), view)
+    torch.testing.assert_close(whole.float(), want, **_tol(dtype))
+    cache.release("a")
+    rows, at = [], 0
+    for n, m in ((33, 4), (1, 1), (2, 3), (34, 1)):      # request a in portions; request b beside it, also growing
+        ctx = _context_for(cache, [("b", m), ("a", n)])
+        out = part.forward(torch.cat([other[:m], x[at:at + n]]), ctx, view)
+        rows.append(out[m:])
+        at += n
+    torch.testing.assert_close(torch.cat(rows).float(), want, **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prenorm_block_alone(dtype):
+    """The block arrangement with real parts against the plain decoder layer; the residual stream travels as
+    (hidden, pending delta)."""
+    from liteinfer_b200.cache.manager import CacheManager
+    from liteinfer_b200.parts.model import Layer
+    from liteinfer_b200.parts.spec import LayerSpec, PartSpec, ScheduleEntry
+
+    config = dict(tiny_configs.TINY_B)
+    h, heads, kvh, d = config["hidden_size"], config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    norm = PartSpec("rmsnorm", {"size": h, "eps": config["rms_norm_eps"]})
+    scaling = config["rope_scaling"]
+    spec = LayerSpec("prenorm_residual", {
+        "mixer_norm": norm,
+        "mixer": PartSpec("attention", {"hidden_size": h, "heads": heads, "kv_heads": kvh, "head_dim": d,
+                                        "position": PartSpec("rotary", {"head_dim": d, "theta": config["rope_theta"], **scaling})}),
+        "feed_forward_norm": norm,
+        "feed_forward": PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": config["intermediate_size"],
+                                               "activation": "silu"}),
+    }, {"mixer_norm": "model.layers.0.input_layernorm.", "mixer": "model.layers.0.self_attn.",
+        "feed_forward_norm": "model.layers.0.post_attention_layernorm.", "feed_forward": "model.layers.0.mlp."})
+    layer = Layer(spec, dtype, torch.device(DEV))
+    weights = {}
+    for role, part in layer.parts.items():
+        local = {n: (1 + 0.1 * _randn(*s.shape, seed=len(weights) + i)).to(dtype) if s.init == "ones_normal"
+                 else _randn(*s.shape, seed=len(weights) + i, scale=0.08, dtype=dtype)
+                 for i, (n, s) in enumerate(part.tensor_specs().items())}
+        part.bind(dict(local))
+        weights.update({spec.prefixes[role] + n: t.float() for n, t in local.items()})
+    x = _randn(40, h, seed=90, dtype=dtype)
+    delta = _randn(40, h, seed=91, dtype=dtype)
+    cos, sin = plain_llama.rope_tables(plain_llama.rope_inverse_frequencies(config), torch.arange(40, device=DEV), torch.float32)
+    want = plain_llama.decoder_layer((x + delta).float(), weights, 0, config, cos, sin)
+    cache = CacheManager([layer.cache_needs()], (ScheduleEntry(0),), 8, 16, 2, dtype, DEV)
+    hidden, pending = layer.block.forward(x.clone(), delta, _context_for(cache, [("a", 40)]), cache.layer_caches()[0])
+    torch.testing.assert_close((hidden.float() + pending.float()), want, **_tol(dtype))
