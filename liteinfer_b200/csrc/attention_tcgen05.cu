@@ -14,7 +14,9 @@
 //   softmax (warps 2-5) one thread per row: tcgen05.ld brings the row's 64 scores into registers, so
 //                       maximum and sum need no exchange between threads; the probabilities go to
 //                       shared memory as bfloat16 in the layout tcgen05.mma reads; the accumulator in
-//                       tensor memory is rescaled (ld, multiply, st) only when a row's maximum moved.
+//                       tensor memory is rescaled (ld, multiply, st) only when a row's maximum has outgrown
+//                       the reference of its exponentials by 2^8, so the softmax of one tile does not wait
+//                       for P V of the tile before it.
 //
 // Scores, maximum, sum and accumulator are 32-bit; probabilities are rounded to bfloat16 for P V
 // (liteinfer/models/paged_kernels.py:282-284).  Keys outside the visible range are masked to -inf and
@@ -33,6 +35,7 @@ constexpr int kHeadDim = 64;
 constexpr int kKvStages = 3;
 constexpr int kAttnThreads = 192;
 constexpr float kLog2eF = 1.4426950408889634f;
+constexpr float kLazyLog2 = 8.f;   // how far (in powers of two) a row's maximum may outgrow the reference of its exponentials
 
 struct TcAttnParams {
   const bf16* q;
@@ -54,6 +57,28 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Three-input maximum and two-wide 32-bit arithmetic: fewer instructions for the softmax threads, whose
+// instruction stream is what a tile's time is made of.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
 }
 
 __global__ void __launch_bounds__(kAttnThreads, 2)
@@ -232,8 +257,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       const bool all_visible = key0 + kKeys - 1 <= first_qpos && (p.window <= 0 || key0 > last_qpos - p.window);
       float mx = m;
       if (all_visible && qpos >= 0) {
+        float part[4] = {m, m, m, m};      // four chains, so that the maxima do not wait for one another
 #pragma unroll
-        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
+        for (int j = 0; j < 32; ++j) part[j & 3] = max3(part[j & 3], __uint_as_float(sa[j]), __uint_as_float(sb[j]));
+        mx = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -245,15 +272,44 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
         }
       }
-      // mx is in units of raw scores; exp2 arguments are (s - mx) * scale_log2.
-      const float m_use = mx == -INFINITY ? 0.f : mx;
-      const float alpha = ex2((m - m_use) * p.scale_log2);      // m = -inf gives 0
-      const float neg = -m_use * p.scale_log2;
-      // P for this tile overwrites the buffer that P V of tile t-2 read, and the accumulator may be rescaled only
-      // once P V of tile t-1 has landed: both hold once pv_done of tile t-1 has fired.
-      if (t >= 1 && !mbar_wait(pv_done((t - 1) & 1), (unsigned)((t - 1) >> 1) & 1, p.error_flag, 17)) { ok = false; break; }
-      tcgen05_fence_after();
-      if (t >= 1 && __any_sync(0xffffffffu, alpha != 1.f)) {
+      // Exponentials are taken against m, which follows the row's maximum lazily: it moves only when the maximum
+      // has outgrown it by more than 2^kLazyLog2, so that the accumulator is rarely rescaled.  Numerator and
+      // denominator share m, so the result is the same up to rounding; values stay below 2^kLazyLog2.
+      float m_new = m, alpha = 1.f;
+      if ((mx - m) * p.scale_log2 > kLazyLog2) {     // also when m is still -inf and a score is not
+        m_new = mx;
+        alpha = ex2((m - mx) * p.scale_log2);
+      }
+      const bool rescale = alpha != 1.f && m != -INFINITY;   // a row that has seen no key yet holds zeros
+      const float neg = m_new == -INFINITY ? 0.f : -m_new * p.scale_log2;
+      // P of this tile overwrites the buffer that P V of tile t-2 read.
+      if (t >= 2 && !mbar_wait(pv_done(buf), (unsigned)((t - 2) >> 1) & 1, p.error_flag, 17)) { ok = false; break; }
+      float2 sums[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg, neg);
+      unsigned char* prow = generic_base + (p_smem - base) + buf * kRowTileBytes + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {       // chunk of 8 keys = 16 bytes of bfloat16
+        unsigned w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = c * 8 + 2 * e;
+          const float2 x = make_float2(__uint_as_float(j < 32 ? sa[j] : sb[j - 32]),
+                                       __uint_as_float(j + 1 < 32 ? sa[j + 1] : sb[j + 1 - 32]));
+          const float2 y = fma2(x, scale2, neg2);
+          const float2 ev = make_float2(ex2(y.x), ex2(y.y));
+          sums[e] = add2(sums[e], ev);
+          __nv_bfloat162 h = __floats2bfloat162_rn(ev.x, ev.y);
+          w[e] = *reinterpret_cast<unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      const float2 total = add2(add2(sums[0], sums[1]), add2(sums[2], sums[3]));
+      const float sum = total.x + total.y;
+      // The accumulator may be rescaled only between P V of tile t-1 and P V of this tile; the latter waits for
+      // this warp's arrival below.  The softmax of this tile has not waited for P V of the last one otherwise.
+      if (t >= 1 && __any_sync(0xffffffffu, rescale)) {
+        if (!mbar_wait(pv_done((t - 1) & 1), (unsigned)((t - 1) >> 1) & 1, p.error_flag, 20)) { ok = false; break; }
+        tcgen05_fence_after();
         unsigned o[32];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -265,24 +321,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         }
         tmem_store_wait();
       }
-      m = mx;
-      float sum = 0.f;
-      unsigned char* prow = generic_base + (p_smem - base) + buf * kRowTileBytes + row * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {       // chunk of 8 keys = 16 bytes of bfloat16
-        unsigned w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = c * 8 + 2 * e;
-          const float x0 = __uint_as_float(j < 32 ? sa[j] : sb[j - 32]);
-          const float x1 = __uint_as_float(j + 1 < 32 ? sa[j + 1] : sb[j + 1 - 32]);
-          const float e0 = ex2(fmaf(x0, p.scale_log2, neg)), e1 = ex2(fmaf(x1, p.scale_log2, neg));
-          sum += e0 + e1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-          w[e] = *reinterpret_cast<unsigned*>(&h);
-        }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+      m = m_new;
       l = l * alpha + sum;
       // Value rows of keys outside [lo, hi) may hold anything (an unwritten slot): zero them before P V reads them.
       if (key0 < lo || key0 + kKeys > hi) {
