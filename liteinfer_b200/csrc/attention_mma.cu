@@ -56,6 +56,12 @@ struct AttnParams {
   float* partial_out;     // [tokens * heads * splits, D] when num_splits > 1
   float* partial_lse;     // [tokens * heads * splits]
   unsigned* counters;     // [grid.z * kv_heads * query tiles], zero between launches, when num_splits > 1
+  // Decode with the rotary encoding and the cache write fused in (see li_paged_attention_mma): q, k_new and
+  // v_new are the unrotated projections of each sequence's newest token, all with q_row_stride.
+  const float* rope_inv_freq;   // [D / 2], or null: q is already rotated and the newest key is in its page
+  const bf16* k_new;
+  const bf16* v_new;
+  int store_new;                // 0: this layer reads pages that another layer writes
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -134,8 +140,10 @@ attention_mma_kernel(const AttnParams p) {
   bf16* kbuf = qs + kQRows * D;                           // kStages x [64][D]
   bf16* vbuf = kbuf + kStages * kBlockN * D;              // kStages x [64][D]
   __shared__ bool is_last;
-  grid_dependency_wait();   // q and the newest keys and values come from the kernels before
+  __shared__ float rope_cos[kDecode ? D / 2 : 1], rope_sin[kDecode ? D / 2 : 1];
+  __shared__ __align__(16) bf16 newest[kDecode ? 2 * D : 8];   // the rotated key and the value of the newest token
 
+  // Tables and lengths are inputs of the step; what an earlier kernel wrote is read after the wait below.
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
   const int kvh = blockIdx.y;
   const int split = blockIdx.x % p.num_splits, qtile = blockIdx.x / p.num_splits;
@@ -163,13 +171,72 @@ attention_mma_kernel(const AttnParams p) {
   const int per_split = (ntiles + p.num_splits - 1) / p.num_splits;
   const int my_lo = tile_lo + split * per_split, my_hi = min(tile_hi, my_lo + per_split);
 
-  // ---- Q tile -> shared (zero rows beyond rows_used), then A fragments in registers.
-  for (int c = threadIdx.x; c < kQRows * kChunks; c += kWarps * 32) {
-    const int row = c / kChunks, chunk = c % kChunks;
-    const bool valid = row < rows_used;
-    const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-    const bf16* src = p.q + (valid ? (size_t)(q_begin + qi) * p.q_row_stride + (size_t)head * D + chunk * 8 : 0);
-    cp_async16(tile_ptr<D>(qs, row, chunk), src, valid);
+  const bool fused = kDecode && p.rope_inv_freq != nullptr;
+  const int newest_pos = ctx - 1;
+  // With the rotary encoding fused in, the block whose keys include the newest position rotates that key,
+  // stores it and the value into their page, and uses them from shared memory.
+  const bool owns_newest = fused && p.store_new && newest_pos / kBlockN >= my_lo && newest_pos / kBlockN < my_hi;
+  if (kDecode && fused) {
+    for (int i = threadIdx.x; i < D / 2; i += kWarps * 32) {
+      const float angle = __fmul_rn((float)newest_pos, p.rope_inv_freq[i]);
+      rope_cos[i] = cosf(angle);
+      rope_sin[i] = sinf(angle);
+    }
+  }
+  grid_dependency_wait();   // q and the newest keys and values come from the kernels before
+  if (kDecode && fused) {
+    __syncthreads();
+    constexpr int kItems = D / 16;                   // work items of eight pairs (j, j + D/2) per head
+    const size_t token = (size_t)(q_begin + q0) * p.q_row_stride;
+    for (int w = threadIdx.x; w < kQRows * kItems; w += kWarps * 32) {
+      const int row = w / kItems, j = (w % kItems) * 8;
+      Vec16<bf16> lo, hi;
+      if (row < rows_used) {
+        const bf16* src = p.q + token + (size_t)(kvh * groups + row) * D + j;
+        rotate_eight(load16(src), load16(src + D / 2), rope_cos + j, rope_sin + j, lo, hi);
+      } else {
+        lo.raw = hi.raw = make_uint4(0, 0, 0, 0);
+      }
+      store16(tile_ptr<D>(qs, row, j / 8), lo);
+      store16(tile_ptr<D>(qs, row, (j + D / 2) / 8), hi);
+    }
+    if (owns_newest) {
+      const int page = table[p.page_shift >= 0 ? newest_pos >> p.page_shift : newest_pos / p.page_size];
+      const int slot = newest_pos - (p.page_shift >= 0 ? (newest_pos >> p.page_shift) << p.page_shift
+                                                       : newest_pos / p.page_size * p.page_size);
+      const bool store = page >= 0 && page < p.num_pages;
+      const size_t dst = (((size_t)(store ? page : 0) * p.kv_heads + kvh) * p.page_size + slot) * D;
+      bf16* k_pool = const_cast<bf16*>(p.k_pool);
+      bf16* v_pool = const_cast<bf16*>(p.v_pool);
+      for (int w = threadIdx.x; w < kItems + D / 8; w += kWarps * 32) {
+        if (w < kItems) {
+          const int j = w * 8;
+          const bf16* src = p.k_new + token + (size_t)kvh * D + j;
+          Vec16<bf16> lo, hi;
+          rotate_eight(load16(src), load16(src + D / 2), rope_cos + j, rope_sin + j, lo, hi);
+          store16(newest + j, lo);
+          store16(newest + j + D / 2, hi);
+          if (store) {
+            store16(k_pool + dst + j, lo);
+            store16(k_pool + dst + j + D / 2, hi);
+          }
+        } else {
+          const int j = (w - kItems) * 8;
+          const Vec16<bf16> v = load16(p.v_new + token + (size_t)kvh * D + j);
+          store16(newest + D + j, v);
+          if (store) store16(v_pool + dst + j, v);
+        }
+      }
+    }
+  } else {
+    // ---- Q tile -> shared (zero rows beyond rows_used), then A fragments in registers.
+    for (int c = threadIdx.x; c < kQRows * kChunks; c += kWarps * 32) {
+      const int row = c / kChunks, chunk = c % kChunks;
+      const bool valid = row < rows_used;
+      const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+      const bf16* src = p.q + (valid ? (size_t)(q_begin + qi) * p.q_row_stride + (size_t)head * D + chunk * 8 : 0);
+      cp_async16(tile_ptr<D>(qs, row, chunk), src, valid);
+    }
   }
   cp_async_commit();
   // The first kStages-1 tiles are requested at once; a group is committed per tile even when it is empty.
@@ -214,6 +281,16 @@ attention_mma_kernel(const AttnParams p) {
     cp_async_commit();
     cp_async_wait<kStages - 1>();   // all but the newest kStages-1 groups are complete: this tile is here
     __syncthreads();
+    if (kDecode && owns_newest && tile == newest_pos / kBlockN) {
+      // The page's copy of the newest token may be older than the store above: take it from shared memory.
+      const int key = newest_pos - tile * kBlockN;
+      if (threadIdx.x < 2 * kChunks) {
+        const int c = threadIdx.x % kChunks;
+        bf16* dst = tile_ptr<D>(threadIdx.x < kChunks ? ks : vs, key, c);
+        store16(dst, load16(newest + (threadIdx.x < kChunks ? 0 : D) + c * 8));
+      }
+      __syncthreads();
+    }
 
     // S = Q K^T for 16 rows x (16 keys per group).
     float s[kGroupsPerWarp * 2][4];
@@ -494,12 +571,19 @@ LI_EXPORT int li_paged_attention_mma_counters(int num_seqs, int max_q_len, int h
 // num_splits > 1 needs scratch: partial_out [tokens*heads*splits, head_dim] and partial_lse
 // [tokens*heads*splits] (float32, tokens = rows of q), and `counters`
 // (li_paged_attention_mma_counters(...) unsigned values, zero; the kernel leaves them zero).
+// rope_inv_freq (optional, [head_dim / 2] float32; only with max_q_len 1 and groups of at most 16): the rotary
+// encoding and the cache write are done here instead of by li_rope_kv_write.  q, k_new and v_new then point at
+// the unrotated projections of the tokens (same row stride); every sequence brings exactly one token, at position
+// context_len - 1.  q is rotated on its way into shared memory (the buffer keeps the unrotated values); the key
+// is rotated and, with store_new, written to its page together with the value.  Without store_new the pages
+// already hold the newest token.
 LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out, int out_row_stride,
                                      const void* k_pool, const void* v_pool, const int* block_table,
                                      int table_stride, const int* query_start_loc, const int* context_lens,
                                      const int* seq_index, int num_seqs, int max_q_len, int heads, int kv_heads,
                                      int head_dim, int page_size, int num_pages, float scale, int window,
                                      int num_splits, float* partial_out, float* partial_lse, unsigned* counters,
+                                     const float* rope_inv_freq, const void* k_new, const void* v_new, int store_new,
                                      cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (kv_heads < 1 || heads % kv_heads) return LI_ERR_UNSUPPORTED;
@@ -512,11 +596,13 @@ LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out,
     return LI_ERR_ALIGNMENT;
   AttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                block_table, table_stride, query_start_loc, context_lens, seq_index, heads, kv_heads, page_size,
-               num_pages, -1, scale * kLog2e, window, num_splits, partial_out, partial_lse, counters};
+               num_pages, -1, scale * kLog2e, window, num_splits, partial_out, partial_lse, counters,
+               rope_inv_freq, (const bf16*)k_new, (const bf16*)v_new, store_new};
   if ((page_size & (page_size - 1)) == 0)
     for (int s = 0; s < 31; ++s)
       if ((1 << s) == page_size) p.page_shift = s;
   const bool decode = max_q_len == 1 && groups <= 16;
+  if (rope_inv_freq && (!decode || !k_new || !v_new || !aligned16(k_new) || !aligned16(v_new))) return LI_ERR_UNSUPPORTED;
   if (!decode)
     return head_dim == 64 ? launch_attention<64, false, 2>(p, num_seqs, max_q_len, stream)
                           : launch_attention<128, false, 2>(p, num_seqs, max_q_len, stream);

@@ -93,6 +93,27 @@ template <typename T> __device__ __forceinline__ void store16(T* p, const Vec16<
   *reinterpret_cast<decltype(v.raw)*>(p) = v.raw;
 }
 
+// ---- rotary pairs ---------------------------------------------------------------------------------
+// (a, b) = dimensions (j, j + half) of a head, rotated by the angle whose cosine and sine are c and s.  Every
+// product and sum is rounded on its own, whichever kernel the rotation is part of, so that all of them agree
+// to the bit (and with a plain a*c - b*s written in any tensor library).
+__device__ __forceinline__ float rotate_lo(float a, float b, float c, float s) {
+  return __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+}
+__device__ __forceinline__ float rotate_hi(float a, float b, float c, float s) {
+  return __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+}
+// Eight pairs at once: a and b hold dimensions j..j+7 and j+half..j+half+7; cosv and sinv point at entry j.
+__device__ __forceinline__ void rotate_eight(const Vec16<bf16>& a, const Vec16<bf16>& b, const float* cosv,
+                                             const float* sinv, Vec16<bf16>& lo, Vec16<bf16>& hi) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float x = a.get(e), y = b.get(e), c = cosv[e], s = sinv[e];
+    lo.set(e, rotate_lo(x, y, c, s));
+    hi.set(e, rotate_hi(x, y, c, s));
+  }
+}
+
 // ---- programmatic dependent launch -------------------------------------------------------------
 // Every kernel of this library is launched so that it may start while the kernel before it in the
 // stream is still running.  What a kernel does before `grid_dependency_wait()` must not read what

@@ -31,7 +31,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   float* cosv = cs;
   float* sinv = cs + half;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float angle = (float)pos * inv_freq[i];
+    const float angle = __fmul_rn((float)pos, inv_freq[i]);
     cosv[i] = cosf(angle);
     sinv[i] = sinf(angle);
   }
@@ -50,8 +50,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     const int h = w / per_head, i = w - h * per_head;
     T* p = row + h * head_dim;
     const float a = to_float(p[i]), b = to_float(p[i + half]);
-    p[i] = from_float<T>(a * cosv[i] - b * sinv[i]);
-    p[i + half] = from_float<T>(b * cosv[i] + a * sinv[i]);
+    p[i] = from_float<T>(rotate_lo(a, b, cosv[i], sinv[i]));
+    p[i + half] = from_float<T>(rotate_hi(a, b, cosv[i], sinv[i]));
   }
   (void)pass;
 
@@ -65,9 +65,9 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     const size_t dst = (((size_t)page * kv_heads + h) * page_size + slot) * head_dim + j;
     float kv;
     if (j < half) {
-      kv = to_float(krow[w]) * cosv[j] - to_float(krow[w + half]) * sinv[j];
+      kv = rotate_lo(to_float(krow[w]), to_float(krow[w + half]), cosv[j], sinv[j]);
     } else if (j < rotary_dim) {
-      kv = to_float(krow[w]) * cosv[j - half] + to_float(krow[w - half]) * sinv[j - half];
+      kv = rotate_hi(to_float(krow[w - half]), to_float(krow[w]), cosv[j - half], sinv[j - half]);
     } else {
       kv = to_float(krow[w]);
     }
@@ -91,7 +91,7 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
   float* cosv = cs;
   float* sinv = cs + half;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float angle = (float)pos * inv_freq[i];
+    const float angle = __fmul_rn((float)pos, inv_freq[i]);
     cosv[i] = cosf(angle);
     sinv[i] = sinf(angle);
   }
@@ -112,12 +112,7 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
       bf16* p = row + h * head_dim + j;
       const Vec16<bf16> a = load16(p), b = load16(p + half);
       Vec16<bf16> lo, hi;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float c = cosv[j + e], sn = sinv[j + e];
-        lo.set(e, a.get(e) * c - b.get(e) * sn);
-        hi.set(e, b.get(e) * c + a.get(e) * sn);
-      }
+      rotate_eight(a, b, cosv + j, sinv + j, lo, hi);
       if (h < heads) {
         store16(p, lo);
         store16(p + half, hi);

@@ -14,6 +14,8 @@ import ctypes
 import os
 from ctypes import c_float, c_int, c_size_t, c_void_p
 
+from dataclasses import dataclass
+
 import torch
 
 from liteinfer_b200.ops.library import KernelLibraryError, load
@@ -44,7 +46,7 @@ _SIGNATURES = {
     "li_paged_attention_mma": ("attention_mma", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
-        c_void_p]),
+        c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "li_paged_attention_mma_counters": ("attention_mma", [c_int, c_int, c_int, c_int]),
     "li_paged_attention_tcgen05": ("attention_tcgen05", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -398,9 +400,11 @@ def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, q
 
 def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
                         seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0,
-                        num_splits=1) -> torch.Tensor:
+                        num_splits=1, newest=None) -> torch.Tensor:
     """The tensor-core kernel (bfloat16, head size 64 or 128); `num_splits` > 1 splits every sequence's keys
-    over that many blocks, the last of which merges the partial results."""
+    over that many blocks, the last of which merges the partial results.  `newest` (NewestToken, single-token
+    sequences only): q is unrotated and the newest key and value are not in their pages yet; the kernel
+    rotates q and the key and stores key and value itself."""
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
     pages, kvh, page_size, hd = k_pool.shape
     partial_out = partial_lse = counters = None
@@ -416,9 +420,28 @@ def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query
         q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
         _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
-        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters), _stream()),
+        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters),
+        _ptr(newest.inv_freq if newest else None), _ptr(newest.k if newest else None),
+        _ptr(newest.v if newest else None), int(newest.store) if newest else 0, _stream()),
         "paged_attention_mma")
     return out
+
+
+@dataclass
+class NewestToken:
+    """The unrotated key and value projections of each sequence's newest token (views with the row stride of
+    q) and the rotary frequencies, for the decode kernel that rotates and stores them itself."""
+    inv_freq: torch.Tensor     # [head_dim / 2] float32
+    k: torch.Tensor
+    v: torch.Tensor
+    store: bool = True         # False: the pages are another layer's and already hold the token
+
+
+def fused_decode_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, rotary_dim: int, plan) -> bool:
+    """Whether a step's attention can run as one launch that also rotates q and k and writes the cache: every
+    sequence brings one token, all of the head is rotated, and the tensor-core decode kernel takes the sizes."""
+    return (plan is not None and plan.num_prefill == 0 and plan.num_decode > 0 and rotary_dim == head_dim
+            and mma_attention_supports(dtype, heads, kv_heads, head_dim) and heads // kv_heads <= 16)
 
 
 def paged_attention_tcgen05(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
@@ -449,7 +472,7 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
                     v_pool: torch.Tensor, block_table: torch.Tensor, query_start_loc: torch.Tensor,
                     context_lens: torch.Tensor, num_seqs: int, max_q_len: int, heads: int, kv_heads: int,
                     head_dim: int, scale: float, window: int = 0, plan=None,
-                    decode_splits: int | None = None) -> torch.Tensor:
+                    decode_splits: int | None = None, newest: "NewestToken | None" = None) -> torch.Tensor:
     """Attention of each sequence's newest queries over its pages (any mix of portions and single tokens).
 
     q: the tensor holding the queries, head h of token t at q[t, h*head_dim:...]
@@ -458,11 +481,14 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     on tensor cores; with a `plan` (AttentionPlan) the sequences that bring one
     token go through a launch that splits their keys over several blocks, the
     others through an unsplit one.  Everything else runs the plain SIMT kernel.
+    `newest`: only where `fused_decode_supports` said yes; see `paged_attention_mma`.
     """
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
     _int32(block_table, "block_table"); _int32(query_start_loc, "query_start_loc"); _int32(context_lens, "context_lens")
     pages, kvh, page_size, hd = k_pool.shape
     assert (kvh, hd) == (kv_heads, head_dim) and q.dtype == out.dtype == k_pool.dtype == v_pool.dtype
+    if newest is not None and not fused_decode_supports(q.dtype, heads, kv_heads, head_dim, head_dim, plan):
+        raise ValueError("the decode kernel with the rotary encoding fused in does not take this step")
     if not mma_attention_supports(q.dtype, heads, kv_heads, head_dim):
         return paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc,
                                        context_lens, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window)
@@ -478,7 +504,7 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
         bound = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window)
         splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound)
         paged_attention_mma(*common, plan.decode_seqs, plan.num_decode, 1, heads, kv_heads, head_dim, scale,
-                            window, splits)
+                            window, splits, newest)
     return out
 
 

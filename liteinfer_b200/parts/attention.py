@@ -85,6 +85,19 @@ class Attention:
         ops.linear(x, self.qkv_weight, qkv, self.qkv_bias)
         table = ctx.block_tables[kv.group]
         rotary = self.position.rotary()
+        attended = torch.empty((tokens, q_width), dtype=x.dtype, device=x.device)
+        if rotary is not None and ops.fused_decode_supports(x.dtype, self.heads, self.kv_heads, self.head_dim,
+                                                            rotary.rotary_dim, ctx.plan):
+            # Every sequence brings one token: one launch rotates q and k, stores k and v and attends.
+            kv_width = self.kv_heads * self.head_dim
+            newest = ops.NewestToken(rotary.inv_freq, qkv[:, q_width:], qkv[:, q_width + kv_width:],
+                                     store=not cache.read_only)
+            ops.paged_attention(qkv, qkv.shape[1], attended, kv.k_pool, kv.v_pool, table, ctx.query_start_loc,
+                                ctx.context_lens, ctx.num_seqs, ctx.max_query_len, self.heads, self.kv_heads,
+                                self.head_dim, self.scale, self.window or 0, plan=ctx.plan,
+                                decode_splits=ctx.decode_splits, newest=newest)
+            out = torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device)
+            return ops.linear(attended, self.o_weight, out, self.o_bias)
         if rotary is None:
             kv_width = self.kv_heads * self.head_dim
             self.position.apply(qkv[:, :q_width].unflatten(1, (self.heads, self.head_dim)),
@@ -92,7 +105,6 @@ class Attention:
         ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, kv.k_pool, kv.v_pool,
                           rotary.inv_freq if rotary else None, self.heads, self.kv_heads, self.head_dim,
                           rotary.rotary_dim if rotary else 0, store=not cache.read_only)
-        attended = torch.empty((tokens, q_width), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, qkv.shape[1], attended, kv.k_pool, kv.v_pool, table, ctx.query_start_loc,
                             ctx.context_lens, ctx.num_seqs, ctx.max_query_len, self.heads, self.kv_heads,
                             self.head_dim, self.scale, self.window or 0, plan=ctx.plan,

@@ -356,6 +356,49 @@ def test_tensor_core_attention_against_the_plain_kernel(heads, kv_heads, head_di
     torch.testing.assert_close(got.float(), want.float(), rtol=2 ** -6, atol=2 ** -6)
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [(32, 8, 64, 16), (8, 8, 64, 8), (16, 1, 128, 16),
+                                                               (6, 2, 128, 5), (5, 1, 64, 32)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("splits", [1, 3, 32])
+def test_decode_attention_with_rotary_and_cache_write_fused(heads, kv_heads, head_dim, page_size, window, splits):
+    """One launch that rotates q and the newest key, stores key and value and attends, against the two
+    launches it replaces: the same output and the same pages, to the bit; contexts end at, just before and
+    just after the edges of pages and of 64-key tiles."""
+    from liteinfer_b200 import ops
+
+    ctx_lens = [700, 1, 64, 65, 63, 129, 320, 16, 17]
+    q_lens = [1] * len(ctx_lens)
+    case = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page_size, q_lens, ctx_lens, seed=3)
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, head_dim, 2).float() / head_dim))).cuda()
+    plan = _plan_for(q_lens, ctx_lens)
+    rest = (case["table"], case["qsl"], case["ctx"], case["B"], 1, heads, kv_heads, head_dim, head_dim ** -0.5, window)
+    q_width, kv_width = heads * head_dim, kv_heads * head_dim
+
+    qkv, k_two, v_two = case["qkv"].clone(), case["k_pool"].clone(), case["v_pool"].clone()
+    ops.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_two, v_two, inv_freq, heads, kv_heads,
+                      head_dim, head_dim)
+    want = ops.paged_attention(qkv, qkv.shape[1], torch.empty(case["T"], q_width, dtype=torch.bfloat16, device="cuda"),
+                               k_two, v_two, *rest, plan=plan, decode_splits=splits)
+
+    qkv, k_one, v_one = case["qkv"].clone(), case["k_pool"].clone(), case["v_pool"].clone()
+    assert ops.fused_decode_supports(torch.bfloat16, heads, kv_heads, head_dim, head_dim, plan)
+    newest = ops.NewestToken(inv_freq, qkv[:, q_width:], qkv[:, q_width + kv_width:])
+    got = ops.paged_attention(qkv, qkv.shape[1], torch.empty(case["T"], q_width, dtype=torch.bfloat16, device="cuda"),
+                              k_one, v_one, *rest, plan=plan, decode_splits=splits, newest=newest)
+    assert torch.equal(got, want)
+    for one, two in ((k_one, k_two), (v_one, v_two)):
+        assert torch.equal(torch.isnan(one.float()), torch.isnan(two.float()))
+        assert torch.equal(torch.nan_to_num(one.float()), torch.nan_to_num(two.float()))
+
+    # A layer that reads another layer's pages: the newest token is there already and nothing is written.
+    frozen_k, frozen_v = k_two.clone(), v_two.clone()
+    newest = ops.NewestToken(inv_freq, qkv[:, q_width:], qkv[:, q_width + kv_width:], store=False)
+    again = ops.paged_attention(qkv, qkv.shape[1], torch.empty_like(got), frozen_k, frozen_v, *rest, plan=plan,
+                                decode_splits=splits, newest=newest)
+    assert torch.equal(again, want)
+    assert torch.equal(torch.nan_to_num(frozen_k.float()), torch.nan_to_num(k_two.float()))
+
+
 def test_tensor_core_attention_finds_one_far_key_under_splits():
     from liteinfer_b200 import ops
 

@@ -209,5 +209,9 @@ def sample(logits, temperature, top_k, top_p, uniform, out):
     return out
 
 
-ALL = ("embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
+def fused_decode_supports(*args) -> bool:
+    return False      # the stand-ins rotate and store in `rope_kv_write`, never inside the attention
+
+
+ALL = ("fused_decode_supports", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
        "gated_linear", "gemm_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
