@@ -132,7 +132,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParam
 
 // kDecode: every launched sequence brings one token and the group has at most 16 heads.
 template <int D, bool kDecode, int kStages>   // kStages: K/V tiles in flight per block
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32)   // forcing a sixth block per SM (80 registers) measured slower in a step
 attention_mma_kernel(const AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int kQRows = kDecode ? 16 : kBlockM;
@@ -182,8 +182,16 @@ attention_mma_kernel(const AttnParams p) {
       rope_cos[i] = cosf(angle);
       rope_sin[i] = sinf(angle);
     }
+    // The pages hold nothing that the kernel before this one wrote (the newest token is stored here, not
+    // there), so the first K/V tiles are requested before that kernel is waited for.
+#pragma unroll
+    for (int st = 0; st < kStages - 1; ++st) {
+      if (my_lo + st < my_hi)
+        load_kv_tile<D>(kbuf + st * kBlockN * D, vbuf + st * kBlockN * D, p, table, kvh, (my_lo + st) * kBlockN, lo, hi);
+      cp_async_commit();
+    }
   }
-  grid_dependency_wait();   // q and the newest keys and values come from the kernels before
+  grid_dependency_wait();   // q, and without the fused rotation the newest keys and values, come from the kernels before
   if (kDecode && fused) {
     __syncthreads();
     constexpr int kItems = D / 16;                   // work items of eight pairs (j, j + D/2) per head
@@ -238,15 +246,17 @@ attention_mma_kernel(const AttnParams p) {
       cp_async16(tile_ptr<D>(qs, row, chunk), src, valid);
     }
   }
-  cp_async_commit();
-  // The first kStages-1 tiles are requested at once; a group is committed per tile even when it is empty.
-#pragma unroll
-  for (int st = 0; st < kStages - 1; ++st) {
-    if (my_lo + st < my_hi)
-      load_kv_tile<D>(kbuf + st * kBlockN * D, vbuf + st * kBlockN * D, p, table, kvh, (my_lo + st) * kBlockN, lo, hi);
+  if (!fused) {
     cp_async_commit();
+    // The first kStages-1 tiles are requested at once; a group is committed per tile even when it is empty.
+#pragma unroll
+    for (int st = 0; st < kStages - 1; ++st) {
+      if (my_lo + st < my_hi)
+        load_kv_tile<D>(kbuf + st * kBlockN * D, vbuf + st * kBlockN * D, p, table, kvh, (my_lo + st) * kBlockN, lo, hi);
+      cp_async_commit();
+    }
+    cp_async_wait<kStages - 1>();   // the Q tile has landed
   }
-  cp_async_wait<kStages - 1>();   // the Q tile has landed
   __syncthreads();
 
   unsigned qf[D / 16][4];
@@ -563,6 +573,25 @@ LI_EXPORT int li_paged_attention_mma_counters(int num_seqs, int max_q_len, int h
   const bool decode = max_q_len == 1 && groups <= 16;
   const int tq = (decode ? 16 : kBlockM) / groups;
   return num_seqs * kv_heads * ((max_q_len + tq - 1) / tq);
+}
+
+// How many blocks of the decode launch (the variant with two K/V tiles per block) the device holds at once:
+// a launch of up to this many blocks runs as one wave.  0 if the head size has no kernel or the query fails.
+LI_EXPORT int li_paged_attention_mma_decode_capacity(int head_dim) {
+  if (head_dim != 64 && head_dim != 128) return 0;
+  int device = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+  const size_t smem = (size_t)(16 + 2 * 2 * kBlockN) * head_dim * sizeof(bf16);
+  cudaError_t e;
+  if (head_dim == 64) {
+    cudaFuncSetAttribute(attention_mma_kernel<64, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<64, true, 2>, kWarps * 32, smem);
+  } else {
+    cudaFuncSetAttribute(attention_mma_kernel<128, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<128, true, 2>, kWarps * 32, smem);
+  }
+  return e == cudaSuccess ? per_sm * sms : 0;
 }
 
 // Tensor-core paged attention (bfloat16; head_dim 64 or 128; groups of at most 64 heads).

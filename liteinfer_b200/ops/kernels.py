@@ -48,6 +48,7 @@ _SIGNATURES = {
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "li_paged_attention_mma_counters": ("attention_mma", [c_int, c_int, c_int, c_int]),
+    "li_paged_attention_mma_decode_capacity": ("attention_mma", [c_int]),
     "li_paged_attention_tcgen05": ("attention_tcgen05", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
@@ -375,14 +376,28 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
            "rope_kv_write")
 
 
-def decode_splits_for(num_decode: int, kv_heads: int, max_context_len: int) -> int:
-    """Blocks that share one sequence's keys in a decode launch: enough to fill the GPU when the
-    batch is narrow, never fewer than two key tiles each, at most 32
-    (liteinfer/engine/model_runner.py:250-272 and paged_kernels.py:645-693 choose likewise)."""
+_decode_capacity: dict[int, int] = {}
+
+
+def decode_capacity(head_dim: int) -> int:
+    """Blocks of the decode attention launch that the device holds at once (asked of the occupancy calculator
+    once per head size); without a device, what a B200 holds."""
+    if head_dim not in _decode_capacity:
+        blocks = 0
+        if torch.cuda.is_available():
+            blocks = int(_fn("li_paged_attention_mma_decode_capacity")(head_dim))
+        _decode_capacity[head_dim] = blocks or (5 if head_dim <= 64 else 2) * NUM_SMS
+    return _decode_capacity[head_dim]
+
+
+def decode_splits_for(num_decode: int, kv_heads: int, max_context_len: int, head_dim: int = 64) -> int:
+    """Blocks that share one sequence's keys in a decode launch: as many as still run as one wave when the
+    batch is narrow (a launch a little over one wave takes as long as two), never fewer than two key tiles
+    each, at most 32 (liteinfer/engine/model_runner.py:250-272 and paged_kernels.py:645-693 choose likewise)."""
     tiles = -(-max_context_len // 64)
     if tiles < 4:
         return 1
-    return max(1, min(6 * NUM_SMS // max(1, num_decode * kv_heads), tiles // 2, 32))
+    return max(1, min(decode_capacity(head_dim) // max(1, num_decode * kv_heads), tiles // 2, 32))
 
 
 def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
@@ -502,7 +517,7 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
              scale, window)
     if plan.num_decode:
         bound = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window)
-        splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound)
+        splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound, head_dim)
         paged_attention_mma(*common, plan.decode_seqs, plan.num_decode, 1, heads, kv_heads, head_dim, scale,
                             window, splits, newest)
     return out
