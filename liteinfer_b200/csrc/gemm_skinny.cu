@@ -9,14 +9,15 @@
 // for both operands, which a sum over k does not notice), all loads of a block
 // in flight at once, no shared-memory staging; x comes through L1/L2.
 //
-// Work unit: one block = 16 rows of w x one slice of k.  The four warps of a
-// block take interleaved 32-wide k blocks and add their partial sums through
-// shared memory in a fixed order.  When k is cut into several slices (few rows
-// of w, long k: the down and output projections) every block writes its 16 x M
-// partial tile to scratch memory and bumps the tile's counter; the block that
-// arrives last adds the slices in slice order, writes the result and resets the
-// counter.  Nothing waits on anything, and the order of every sum is fixed, so a
-// row's result depends neither on the batch nor on which block came last.
+// Work unit: one block = 16 rows of w x one slice of k.  The warps of a block
+// (4, or 8 or 16 where the weight has few rows: the output and down projections)
+// take interleaved 32-wide k blocks and add their partial sums through shared
+// memory in a fixed order.  When k is also cut into several slices every block
+// writes its 16 x M partial tile to scratch memory and bumps the tile's counter;
+// the block that arrives last adds the slices in slice order, writes the result
+// and resets the counter.  Nothing waits on anything, and the order of every sum
+// is fixed, so a row's result depends neither on the batch nor on which block
+// came last.
 //
 // Optional epilogue for a gated feed-forward: with `gated_act >= 0` the rows of w
 // are interleaved in groups of eight (eight gate rows, then their eight up rows),
@@ -25,22 +26,23 @@
 
 namespace li {
 
-template <int NT>
+template <int NT, int kWarps = kSkinnyWarps>
 int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
   const dim3 grid((p.N + 15) / 16, p.num_slices);
-  return (int)launch_maybe_early(pdl_mode() >= 1 && p.M <= kEarlyLaunchRows, gemm_skinny_kernel<NT>, grid, dim3(kSkinnyWarps * 32), 0, s, p);
+  return (int)launch_maybe_early(pdl_mode() >= 1 && p.M <= kEarlyLaunchRows, gemm_skinny_kernel<NT, kWarps>, grid, dim3(kWarps * 32), 0, s, p);
 }
 
 }  // namespace li
 
 using namespace li;
 
-// How the kernel would cut k for these sizes: (slices, k per slice).  Slices are at least 512 wide and are
-// used only while there are too few 16-row tiles to occupy the GPU.
-LI_EXPORT int li_gemm_skinny_slices(int N, int K, int* slice_k) { return skinny_slices(N, K, slice_k); }
+// How the kernel would run these sizes: returns the slices of k; *warps (optional) the warps per block,
+// *slice_k (optional) the k per slice.
+// The plan depends on the weight's shape only, so that a row of x meets the same order of sums in any batch.
+LI_EXPORT int li_gemm_skinny_plan(int N, int K, int* warps, int* slice_k) { return skinny_plan(N, K, warps, slice_k); }
 
 // bfloat16 only; 1 <= M <= 64; K a multiple of 8 and 16-byte aligned rows.  scratch (float) and counters
-// (unsigned, all zero) are needed when li_gemm_skinny_slices(N, K) > 1: scratch_floats must be at least
+// (unsigned, all zero) are needed when li_gemm_skinny_plan(N, K) > 1: scratch_floats must be at least
 // tiles * slices * 16 * 8 * ceil(M/8) and num_counters at least tiles, with tiles = ceil(N/16).
 // gated_act: -1 plain; 0 silu, 1 gelu, 2 gelu-tanh, 3 relu on rows interleaved in eights (N a multiple of 16);
 // out is then [M, N/2].
@@ -53,7 +55,8 @@ LI_EXPORT int li_gemm_skinny(const void* x, const void* w, const void* bias, voi
   if (!aligned16(x) || !aligned16(w)) return LI_ERR_ALIGNMENT;
   SkinnyParams p{(const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)out, M, N, K, 0, 1, gated_act,
                  scratch, counters};
-  p.num_slices = li_gemm_skinny_slices(N, K, &p.slice_k);
+  int warps = kSkinnyWarps;
+  p.num_slices = li_gemm_skinny_plan(N, K, &warps, &p.slice_k);
   const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
   const int tiles = (N + 15) / 16;
   if (p.num_slices > 1) {
@@ -64,10 +67,18 @@ LI_EXPORT int li_gemm_skinny(const void* x, const void* w, const void* bias, voi
       p.slice_k = (K + 31) / 32 * 32;
     }
   }
-  switch (nt) {
-    case 1: return launch_skinny<1>(p, stream);
-    case 2: return launch_skinny<2>(p, stream);
-    case 4: return launch_skinny<4>(p, stream);
-    default: return launch_skinny<8>(p, stream);
+  switch (nt * 100 + warps) {
+    case 104: return launch_skinny<1, 4>(p, stream);
+    case 108: return launch_skinny<1, 8>(p, stream);
+    case 116: return launch_skinny<1, 16>(p, stream);
+    case 204: return launch_skinny<2, 4>(p, stream);
+    case 208: return launch_skinny<2, 8>(p, stream);
+    case 216: return launch_skinny<2, 16>(p, stream);
+    case 404: return launch_skinny<4, 4>(p, stream);
+    case 408: return launch_skinny<4, 8>(p, stream);
+    case 416: return launch_skinny<4, 16>(p, stream);
+    case 804: return launch_skinny<8, 4>(p, stream);
+    case 808: return launch_skinny<8, 8>(p, stream);
+    default: return launch_skinny<8, 16>(p, stream);
   }
 }

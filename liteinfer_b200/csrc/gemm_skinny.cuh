@@ -5,9 +5,8 @@
 
 namespace li {
 
-constexpr int kSkinnyWarps = 4;
+constexpr int kSkinnyWarps = 4;                                   // warps of the narrow block; wide blocks have 8 or 16
 constexpr int kBlocksPerWarp = 8;                                  // 32-wide k blocks per warp and pass
-constexpr int kSlicePass = kSkinnyWarps * kBlocksPerWarp * 32;      // 1024 k per pass
 constexpr int kMaxSlices = 16;
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -48,11 +47,12 @@ struct SkinnyParams {
   unsigned* counters; // [tiles], zero between launches
 };
 
-template <int NT>   // NT tiles of 8 rows of x
-__global__ void __launch_bounds__(kSkinnyWarps * 32)
+template <int NT, int kWarps = kSkinnyWarps>   // NT tiles of 8 rows of x; kWarps warps share a slice's k blocks
+__global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(const SkinnyParams p) {
   constexpr int kCols = NT * 8;
-  __shared__ float partial[kSkinnyWarps][16][kCols + 1];
+  constexpr int kSlicePass = kWarps * kBlocksPerWarp * 32;   // k per pass of the block
+  __shared__ float partial[4][16][kCols + 1];   // four warps' tiles at a time; [0] ends up holding the block's sum
   __shared__ bool is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int tile = blockIdx.x, slice = blockIdx.y;
@@ -78,7 +78,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
     uint4 wl[kBlocksPerWarp], wh[kBlocksPerWarp];
 #pragma unroll
     for (int u = 0; u < kBlocksPerWarp; ++u) {
-      const int k = pass + (u * kSkinnyWarps + warp) * 32 + 8 * t;
+      const int k = pass + (u * kWarps + warp) * 32 + 8 * t;
       const bool in = k < k_end;
       wl[u] = in ? ldg_stream(w_lo + k) : zero;
       wh[u] = in ? ldg_stream(w_hi + k) : zero;
@@ -90,7 +90,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
     }
 #pragma unroll
     for (int u = 0; u < kBlocksPerWarp; ++u) {
-      const int k = pass + (u * kSkinnyWarps + warp) * 32 + 8 * t;
+      const int k = pass + (u * kWarps + warp) * 32 + 8 * t;
       const bool in = k < k_end;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
@@ -104,27 +104,45 @@ gemm_skinny_kernel(const SkinnyParams p) {
   if (!waited) grid_dependency_wait();
   grid_launch_dependents();
   // acc[j]: c0,c1 = (w row g, x rows j*8 + 2t, +1); c2,c3 = (w row g+8, same x rows).
+  // The warps' tiles are added in warp order, four warps per round through shared memory; every element of
+  // the tile belongs to one thread, which keeps its running sum in a register.
+  constexpr int kThreads = kWarps * 32;
+  constexpr int kOwned = (16 * kCols + kThreads - 1) / kThreads;
+  float running[kOwned];
 #pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    partial[warp][g][j * 8 + 2 * t] = acc[j][0];
-    partial[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
-    partial[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
-    partial[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+  for (int i = 0; i < kOwned; ++i) running[i] = 0.f;
+#pragma unroll
+  for (int round = 0; round < kWarps / 4; ++round) {
+    if (warp / 4 == round) {
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        partial[warp % 4][g][j * 8 + 2 * t] = acc[j][0];
+        partial[warp % 4][g][j * 8 + 2 * t + 1] = acc[j][1];
+        partial[warp % 4][g + 8][j * 8 + 2 * t] = acc[j][2];
+        partial[warp % 4][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kOwned; ++i) {
+      const int e = threadIdx.x + i * kThreads;
+      if (e < 16 * kCols) {
+        const int r = e % 16, m = e / 16;
+#pragma unroll
+        for (int wv = 0; wv < 4; ++wv) running[i] += partial[wv][r][m];
+      }
+    }
+    __syncthreads();
   }
-  __syncthreads();
-
-  // Sum of the four warps, kept in partial[0].
-  for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
-    const int r = e % 16, m = e / 16;
-    float sum = 0.f;
 #pragma unroll
-    for (int wv = 0; wv < kSkinnyWarps; ++wv) sum += partial[wv][r][m];
-    partial[0][r][m] = sum;   // each element is read and written by this thread only
+  for (int i = 0; i < kOwned; ++i) {
+    const int e = threadIdx.x + i * kThreads;
+    if (e < 16 * kCols) partial[0][e % 16][e / 16] = running[i];   // read below by this thread only, or after a barrier
   }
 
   if (p.num_slices > 1) {
     float* mine = p.scratch + ((size_t)tile * p.num_slices + slice) * (16 * kCols);
-    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) mine[e] = partial[0][e % 16][e / 16];
+    for (int e = threadIdx.x; e < 16 * kCols; e += kWarps * 32) mine[e] = partial[0][e % 16][e / 16];
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -135,7 +153,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
     if (!is_last) return;
     __threadfence();
     const float* all = p.scratch + (size_t)tile * p.num_slices * (16 * kCols);
-    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
+    for (int e = threadIdx.x; e < 16 * kCols; e += kWarps * 32) {
       // Every slice's value is requested before the first is added: one trip to L2, not one per slice.
       float v[kMaxSlices];
 #pragma unroll
@@ -152,7 +170,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
   __syncthreads();
 
   if (p.gated_act < 0) {
-    for (int e = threadIdx.x; e < 16 * kCols; e += kSkinnyWarps * 32) {
+    for (int e = threadIdx.x; e < 16 * kCols; e += kWarps * 32) {
       const int r = e % 16, m = e / 16;     // consecutive threads write consecutive output columns
       const int n = row0 + r;
       if (m >= M || n >= N) continue;
@@ -162,7 +180,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
     }
   } else {
     const int half = N / 2;                 // rows [0, 8) of the tile are gate rows, [8, 16) their up rows
-    for (int e = threadIdx.x; e < 8 * kCols; e += kSkinnyWarps * 32) {
+    for (int e = threadIdx.x; e < 8 * kCols; e += kWarps * 32) {
       const int r = e % 8, m = e / 8;
       const int n = tile * 8 + r;
       if (m >= M || n >= half) continue;
@@ -179,8 +197,8 @@ gemm_skinny_kernel(const SkinnyParams p) {
   }
 }
 
-// How the kernel cuts k for a weight of [N, K]: (slices, k per slice).  Slices are at least 512 wide and are
-// used only while there are too few 16-row tiles to occupy the GPU.
+// How narrow blocks (four warps) cut k for a weight of [N, K]: (slices, k per slice).  Slices are at least 512
+// wide and are used only while there are too few 16-row tiles to occupy the GPU.
 inline int skinny_slices(int N, int K, int* slice_k) {
   const int tiles = (N + 15) / 16;
   int slices = 1024 / tiles;
@@ -191,6 +209,27 @@ inline int skinny_slices(int N, int K, int* slice_k) {
   int per = (K + slices - 1) / slices;
   per = (per + 31) / 32 * 32;
   slices = (K + per - 1) / per;
+  if (slice_k) *slice_k = per;
+  return slices;
+}
+
+// The plan for at most eight rows of x: warps per block (4, 8 or 16) and slices of k.  A weight with few
+// 16-row tiles is better served by wider blocks, whose warps add up through shared memory, than by slices,
+// which add up through scratch memory and a counter.  Measured on B200 at 8 rows: 3072 x 2048 with 8 warps
+// uncut 4.3 us (4 warps in 4 slices: 7.4 us); 2048 x 2048 likewise 3.7 us (5.5 us); 2048 x 8192 with 16
+// warps uncut 9.2 us (4 warps in 8 slices: 12.1 us); 16384 x 2048 stays at 4 warps uncut (15.2 us).
+// The aim is some 2,400 warps in all with at least one full pass (256 k) each; k is cut only if wide blocks
+// still leave the GPU half empty and the slices stay long.
+inline int skinny_plan(int N, int K, int* warps_out, int* slice_k) {
+  const int tiles = (N + 15) / 16;
+  int warps = 4;
+  while (warps < 16 && tiles * warps < 2400 && K / (2 * warps) >= 256) warps *= 2;
+  int slices = 1;
+  while (slices < kMaxSlices && tiles * warps * (slices + 1) <= 1200 && K / (slices + 1) >= warps * 512) ++slices;
+  int per = (K + slices - 1) / slices;
+  per = (per + 31) / 32 * 32;
+  slices = (K + per - 1) / per;
+  if (warps_out) *warps_out = warps;
   if (slice_k) *slice_k = per;
   return slices;
 }

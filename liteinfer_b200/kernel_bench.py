@@ -50,7 +50,7 @@ def skinny(M: int, N: int, K: int) -> dict:
     us = _time(lambda i: ops.gemm_skinny(x, w[i], out), copies)
     nbytes = N * K * 2 + M * K * 2 + M * N * 2
     return {"kernel": "gemm_skinny", "M": M, "N": N, "K": K, "us": us, "GBps": nbytes / us / 1e3,
-            "slices": ops.gemm_skinny_slices(N, K)}
+            "warps": ops.gemm_skinny_plan(N, K)[0], "slices": ops.gemm_skinny_plan(N, K)[1]}
 
 
 def tcgen05_gemm(M: int, N: int, K: int, gated: bool = False) -> dict:

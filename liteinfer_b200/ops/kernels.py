@@ -55,7 +55,7 @@ _SIGNATURES = {
     "li_paged_attention_tcgen05_supports": ("attention_tcgen05", [c_int, c_int, c_int, c_int]),
     "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_void_p, c_size_t, c_void_p, c_int, c_void_p]),
-    "li_gemm_skinny_slices": ("gemm_skinny", [c_int, c_int, c_void_p]),
+    "li_gemm_skinny_plan": ("gemm_skinny", [c_int, c_int, c_void_p, c_void_p]),
     "li_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                          c_void_p]),
     "li_gemm_simt": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
@@ -307,9 +307,16 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: to
     return out
 
 
+def gemm_skinny_plan(N: int, K: int) -> tuple[int, int]:
+    """(warps per block, slices of k) with which the weight-streaming kernel runs a weight [N, K]."""
+    warps = ctypes.c_int(0)
+    slices = int(_fn("li_gemm_skinny_plan")(N, K, ctypes.byref(warps), None))
+    return warps.value, slices
+
+
 def gemm_skinny_slices(N: int, K: int) -> int:
     """Into how many slices the weight-streaming kernel cuts k for a weight of [N, K]."""
-    return int(_fn("li_gemm_skinny_slices")(N, K, None))
+    return gemm_skinny_plan(N, K)[1]
 
 
 # Rows of x from which the gated product runs on the tcgen05 kernel with the activation in its epilogue.

@@ -279,7 +279,7 @@ def test_sample_distribution():
 
 
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 33, 64])
-@pytest.mark.parametrize("N,K", [(3072, 2048), (2048, 8192), (1000, 96), (17, 40), (128256 // 8, 2048)])
+@pytest.mark.parametrize("N,K", [(3072, 2048), (2048, 8192), (1000, 96), (17, 40), (128256 // 8, 2048), (48, 16384)])
 def test_gemm_skinny(M, N, K):
     from liteinfer_b200 import ops
 
@@ -472,9 +472,12 @@ def test_skinny_slices_leave_their_counters_at_zero():
     from liteinfer_b200 import ops
     from liteinfer_b200.ops.kernels import scratch_for
 
-    assert ops.gemm_skinny_slices(2048, 8192) == 8 and ops.gemm_skinny_slices(16384, 2048) == 1
-    x, w = _randn(8, 8192, dtype=torch.bfloat16), _randn(2048, 8192, dtype=torch.bfloat16, seed=1, scale=0.02)
-    outs = [ops.gemm_skinny(x, w, torch.empty(8, 2048, dtype=torch.bfloat16, device="cuda")) for _ in range(3)]
+    # Few rows of w: wide blocks; very few and a long k: slices of k as well.
+    assert ops.gemm_skinny_plan(16384, 2048) == (4, 1) and ops.gemm_skinny_plan(3072, 2048) == (8, 1)
+    assert ops.gemm_skinny_plan(2048, 8192) == (16, 1) and ops.gemm_skinny_plan(64, 32768) == (16, 4)
+    x, w = _randn(8, 32768, dtype=torch.bfloat16), _randn(64, 32768, dtype=torch.bfloat16, seed=1, scale=0.02)
+    outs = [ops.gemm_skinny(x, w, torch.empty(8, 64, dtype=torch.bfloat16, device="cuda")) for _ in range(3)]
+    torch.testing.assert_close(outs[0].double(), x.double() @ w.double().t(), rtol=2 ** -7, atol=2 ** -6)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     torch.cuda.synchronize()
     assert int(scratch_for(x.device).gemm_counters.abs().sum()) == 0
