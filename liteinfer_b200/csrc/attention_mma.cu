@@ -563,6 +563,25 @@ int launch_attention(const AttnParams& p, int num_seqs, int max_q_len, cudaStrea
   return (int)launch_pdl((long)num_seqs * max_q_len, attention_mma_kernel<D, kDecode, kStages>, grid, dim3(kWarps * 32), smem, stream, p);
 }
 
+// Blocks of the decode kernel with kStages K/V tiles per block that the current device holds at once
+// (asked of the occupancy calculator the first time); 0 if the query fails.
+template <int D, int kStages>
+int decode_capacity() {
+  static int capacity = -1;
+  if (capacity >= 0) return capacity;
+  int device = 0, sms = 0, per_sm = 0;
+  const size_t smem = (size_t)(16 + 2 * kStages * kBlockN) * D * sizeof(bf16);
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+      cudaFuncSetAttribute(attention_mma_kernel<D, true, kStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess ||
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<D, true, kStages>, kWarps * 32,
+                                                    smem) != cudaSuccess)
+    return 0;
+  capacity = per_sm * sms;
+  return capacity;
+}
+
 }  // namespace li
 
 using namespace li;
@@ -578,20 +597,7 @@ LI_EXPORT int li_paged_attention_mma_counters(int num_seqs, int max_q_len, int h
 // How many blocks of the decode launch (the variant with two K/V tiles per block) the device holds at once:
 // a launch of up to this many blocks runs as one wave.  0 if the head size has no kernel or the query fails.
 LI_EXPORT int li_paged_attention_mma_decode_capacity(int head_dim) {
-  if (head_dim != 64 && head_dim != 128) return 0;
-  int device = 0, sms = 0, per_sm = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return 0;
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-  const size_t smem = (size_t)(16 + 2 * 2 * kBlockN) * head_dim * sizeof(bf16);
-  cudaError_t e;
-  if (head_dim == 64) {
-    cudaFuncSetAttribute(attention_mma_kernel<64, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<64, true, 2>, kWarps * 32, smem);
-  } else {
-    cudaFuncSetAttribute(attention_mma_kernel<128, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_mma_kernel<128, true, 2>, kWarps * 32, smem);
-  }
-  return e == cudaSuccess ? per_sm * sms : 0;
+  return head_dim == 64 ? decode_capacity<64, 2>() : (head_dim == 128 ? decode_capacity<128, 2>() : 0);
 }
 
 // Tensor-core paged attention (bfloat16; head_dim 64 or 128; groups of at most 64 heads).
@@ -635,16 +641,23 @@ LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out,
   if (!decode)
     return head_dim == 64 ? launch_attention<64, false, 2>(p, num_seqs, max_q_len, stream)
                           : launch_attention<128, false, 2>(p, num_seqs, max_q_len, stream);
-  // Few blocks (a narrow batch): each keeps more tiles in flight.  Many blocks: more of them per SM instead.
-  static int deep_override = -1;
-  if (deep_override < 0) {
+  // As many K/V tiles in flight per block as still lets all blocks of the launch run at once: few blocks (a
+  // narrow batch) go deep, many blocks get more of themselves per SM instead.
+  static int stages_override = -1;
+  if (stages_override < 0) {
     const char* e = getenv("LITEINFER_DECODE_STAGES");
-    deep_override = e ? atoi(e) : 0;
+    stages_override = e ? atoi(e) : 0;
   }
-  const bool deep = deep_override ? deep_override >= 3 : (long)num_seqs * kv_heads * num_splits <= 3 * 148;
-  if (head_dim == 64)
-    return deep ? launch_attention<64, true, 4>(p, num_seqs, max_q_len, stream)
-                : launch_attention<64, true, 2>(p, num_seqs, max_q_len, stream);
-  return deep ? launch_attention<128, true, 3>(p, num_seqs, max_q_len, stream)
-              : launch_attention<128, true, 2>(p, num_seqs, max_q_len, stream);
+  const long blocks = (long)num_seqs * kv_heads * num_splits;
+  if (head_dim == 64) {
+    int stages = blocks <= decode_capacity<64, 4>() ? 4 : (blocks <= decode_capacity<64, 3>() ? 3 : 2);
+    if (stages_override) stages = stages_override;
+    if (stages >= 4) return launch_attention<64, true, 4>(p, num_seqs, max_q_len, stream);
+    if (stages == 3) return launch_attention<64, true, 3>(p, num_seqs, max_q_len, stream);
+    return launch_attention<64, true, 2>(p, num_seqs, max_q_len, stream);
+  }
+  int stages = blocks <= decode_capacity<128, 3>() ? 3 : 2;
+  if (stages_override) stages = stages_override;
+  return stages >= 3 ? launch_attention<128, true, 3>(p, num_seqs, max_q_len, stream)
+                     : launch_attention<128, true, 2>(p, num_seqs, max_q_len, stream);
 }

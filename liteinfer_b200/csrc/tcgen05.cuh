@@ -70,6 +70,49 @@ __device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a,
 __device__ __forceinline__ void umma_commit(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+
+// ---- two CTAs of a cluster working as one (cta_group::2) ---------------------------------------------
+// The pair shares every tcgen05.mma: M is 256, each CTA holds 128 rows of A, half the rows of B and its 128
+// rows of the accumulator.  CTA 0 of the pair (the leader) issues the products; barriers that both must see
+// are signalled in both CTAs at once (multicast commit), barriers that only the leader waits on are reached
+// from the other CTA through the shared::cluster window, where clearing bit 24 of a shared-memory address
+// names the same place in the leader.
+constexpr unsigned kPeerBitMask = 0xFEFFFFFFu;
+
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A tile load whose completion is counted on the leader's barrier (no multicast: each CTA loads its own tile).
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, unsigned bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar & kPeerBitMask), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
+                                               bool accumulate) {
+  const unsigned acc = accumulate ? 1u : 0u, zero = 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(acc), "r"(zero) : "memory");
+}
+// Arrives, once the pair's products so far are done, on the barrier at this place in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(unsigned bar) {
+  const unsigned short both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(both) : "memory");
+}
+// Arrives on the leader's barrier from either CTA of the pair.
+__device__ __forceinline__ void mbar_arrive_leader(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerBitMask) : "memory");
+}
+
 __device__ __forceinline__ void tmem_load32(unsigned taddr, unsigned (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "

@@ -489,7 +489,8 @@ def test_skinny_slices_leave_their_counters_at_zero():
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_gemm_tcgen05(M, N, K, with_bias):
     """The tcgen05 / TMA / tensor-memory product against a float64 product, at sizes that leave ragged tiles in
-    every direction; no wait inside the kernel may have given up."""
+    every direction, for the kernel of single CTAs (fewer than 256 rows or columns) and the one of CTA pairs; no
+    wait inside the kernel may have given up."""
     from liteinfer_b200 import ops
 
     x, w = _randn(M, K, dtype=torch.bfloat16), _randn(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
@@ -502,7 +503,7 @@ def test_gemm_tcgen05(M, N, K, with_bias):
 
 
 @pytest.mark.parametrize("M,inter,K,act", [(2048, 8192, 2048, "silu"), (130, 176, 64, "gelu_pytorch_tanh"),
-                                           (500, 112, 120, "relu")])
+                                           (500, 112, 120, "relu"), (300, 504, 96, "silu"), (257, 128, 4096, "gelu")])
 def test_gemm_tcgen05_gated_epilogue(M, inter, K, act):
     """act(gate) * up in the product's epilogue equals the library product followed by the activation kernel,
     bit for bit without a bias (the same sums rounded at the same places)."""
