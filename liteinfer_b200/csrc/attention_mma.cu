@@ -27,81 +27,9 @@
 // the products are mma.sync m16n8k16 (bf16 in, f32 out).  Keys outside the
 // visible range are zero-filled in shared memory and masked to -inf, so an
 // unwritten page cannot leak.
-#include "common.cuh"
+#include "attention_mma.cuh"
 
 namespace li {
-
-constexpr int kBlockM = 64;   // rows (query token x head in group) per block
-constexpr int kBlockN = 64;   // keys per tile
-constexpr int kWarps = 4;
-constexpr float kLog2e = 1.4426950408889634f;
-
-struct AttnParams {
-  const bf16* q;
-  int q_row_stride;
-  bf16* out;
-  int out_row_stride;
-  const bf16* k_pool;
-  const bf16* v_pool;
-  const int* block_table;
-  int table_stride;
-  const int* query_start_loc;
-  const int* context_lens;
-  const int* seq_index;   // optional: batch row of each launched sequence
-  int heads, kv_heads, page_size, num_pages;
-  int page_shift;         // log2(page_size) when it is a power of two, else -1
-  float scale_log2;       // scale * log2(e)
-  int window;
-  int num_splits;
-  float* partial_out;     // [tokens * heads * splits, D] when num_splits > 1
-  float* partial_lse;     // [tokens * heads * splits]
-  unsigned* counters;     // [grid.z * kv_heads * query tiles], zero between launches, when num_splits > 1
-  // Decode with the rotary encoding and the cache write fused in (see li_paged_attention_mma): q, k_new and
-  // v_new are the unrotated projections of each sequence's newest token, all with q_row_stride.
-  const float* rope_inv_freq;   // [D / 2], or null: q is already rotated and the newest key is in its page
-  const bf16* k_new;
-  const bf16* v_new;
-  int store_new;                // 0: this layer reads pages that another layer writes
-};
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-  const int bytes = valid ? 16 : 0;   // src-size 0: the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// 2^x for x <= 0 (and -inf -> 0) in one instruction; the argument is a score minus the running maximum.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
-
-// Tile [rows][D] of bf16 in shared memory; the 16-byte chunk c of row r lives at chunk c ^ (r & 7).
-template <int D> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
-  return base + row * D + ((chunk ^ (row & 7)) << 3);
-}
 
 // One K tile and one V tile of 64 keys -> shared memory.  A thread always copies the same 16-byte chunk
 // of a row and walks the keys in steps of (threads / chunks per row), so the index arithmetic of a tile
@@ -140,8 +68,8 @@ attention_mma_kernel(const AttnParams p) {
   bf16* kbuf = qs + kQRows * D;                           // kStages x [64][D]
   bf16* vbuf = kbuf + kStages * kBlockN * D;              // kStages x [64][D]
   __shared__ bool is_last;
-  __shared__ float rope_cos[kDecode ? D / 2 : 1], rope_sin[kDecode ? D / 2 : 1];
-  __shared__ __align__(16) bf16 newest[kDecode ? 2 * D : 8];   // the rotated key and the value of the newest token
+  __shared__ float rope_cos[D / 2], rope_sin[D / 2];
+  __shared__ __align__(16) bf16 newest[2 * D];   // the rotated key and the value of the newest token
 
   // Tables and lengths are inputs of the step; what an earlier kernel wrote is read after the wait below.
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
@@ -426,29 +354,7 @@ attention_mma_kernel(const AttnParams p) {
       }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < rows_used * D; e += kWarps * 32) {
-      const int row = e / D, d = e % D;
-      float mx = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, ms[w * 16 + row]);
-      float denom = 0.f, acc = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        const float mw = ms[w * 16 + row];
-        const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - mx);
-        denom += wgt * ls[w * 16 + row];
-        acc += wgt * os[((size_t)w * 16 + row) * D + d];
-      }
-      const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-      const float value = denom > 0.f ? acc / denom : 0.f;
-      if (p.num_splits == 1) {
-        p.out[(size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d] = __float2bfloat16_rn(value);
-      } else {
-        const size_t slot = ((size_t)(q_begin + qi) * p.heads + head) * p.num_splits + split;
-        p.partial_out[slot * D + d] = value;
-        if (d == 0) p.partial_lse[slot] = denom > 0.f ? mx + log2f(denom) : -INFINITY;
-      }
-    }
+    combine_warps<D>(p, os, ms, ls, rows_used, groups, q_begin, q0, kvh, split);
   } else {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -474,77 +380,7 @@ attention_mma_kernel(const AttnParams p) {
   }
   if (p.num_splits == 1) return;
 
-  // ---- the block that arrives last merges the splits of this (sequence, KV head, query tile).
-  __threadfence();
-  __syncthreads();
-  const unsigned counter_index = ((unsigned)blockIdx.z * gridDim.y + blockIdx.y) * (gridDim.x / p.num_splits) + qtile;
-  if (threadIdx.x == 0) {
-    const unsigned arrived = atomicAdd(&p.counters[counter_index], 1u);
-    is_last = arrived == (unsigned)p.num_splits - 1;
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  // All loads of a phase are issued before any is used: the merge costs a few trips to L2, not one per split.
-  constexpr int kMaxSplits = 32;
-  float* wsm = reinterpret_cast<float*>(smem_raw);              // [64 rows][kMaxSplits + 1] weights
-  const int S = p.num_splits;
-  __syncthreads();
-  for (int e0 = 0; e0 < rows_used * S; e0 += kWarps * 32 * 4) {
-    float v[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int e = e0 + j * kWarps * 32 + threadIdx.x;
-      if (e < rows_used * S) {
-        const int row = e / S, sidx = e - row * S;
-        const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-        v[j] = __ldcg(p.partial_lse + ((size_t)(q_begin + qi) * p.heads + head) * S + sidx);
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int e = e0 + j * kWarps * 32 + threadIdx.x;
-      if (e < rows_used * S) wsm[(e / S) * (kMaxSplits + 1) + (e % S)] = v[j];
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x < rows_used) {
-    float* w = wsm + threadIdx.x * (kMaxSplits + 1);
-    float mx = -INFINITY;
-    for (int sidx = 0; sidx < S; ++sidx) mx = fmaxf(mx, w[sidx]);
-    float denom = 0.f;
-    for (int sidx = 0; sidx < S; ++sidx) {
-      const float e = w[sidx] == -INFINITY ? 0.f : exp2f(w[sidx] - mx);
-      w[sidx] = e;
-      denom += e;
-    }
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    for (int sidx = 0; sidx < S; ++sidx) w[sidx] *= inv;
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < rows_used * (D / 4); e += kWarps * 32) {
-    const int row = e / (D / 4), d4 = e % (D / 4);
-    const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-    const float4* src = reinterpret_cast<const float4*>(
-        p.partial_out + ((size_t)(q_begin + qi) * p.heads + head) * S * D) + d4;
-    const float* w = wsm + row * (kMaxSplits + 1);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < S; s0 += 8) {
-      float4 v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (s0 + j < S) v[j] = __ldcg(src + (size_t)(s0 + j) * (D / 4));
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (s0 + j < S) {
-          const float wj = w[s0 + j];
-          acc.x += wj * v[j].x; acc.y += wj * v[j].y; acc.z += wj * v[j].z; acc.w += wj * v[j].w;
-        }
-    }
-    bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d4 * 4;
-    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
-  }
-  if (threadIdx.x == 0) p.counters[counter_index] = 0;   // ready for the next launch
+  merge_splits<D>(p, smem_raw, &is_last, rows_used, groups, q_begin, q0, kvh, qtile);
 }
 
 template <int D, bool kDecode, int kStages>

@@ -103,7 +103,8 @@ def attention(batch: int, q_len: int, ctx: int, heads: int = 32, kv_heads: int =
     return {"kernel": "paged_attention", "batch": batch, "q_len": q_len, "ctx": ctx, "heads": heads,
             "kv_heads": kv_heads, "head_dim": head_dim, "us": us, "GBps": kv_bytes / us / 1e3,
             "TFLOPs": flops / us / 1e6,
-            "splits": splits or (ops.decode_splits_for(batch, kv_heads, ctx, head_dim) if q_len == 1 else 1)}
+            "splits": splits or (ops.decode_splits_for(batch, kv_heads, ctx, head_dim, ops.stream_attention_supports(
+                torch.bfloat16, heads, kv_heads, head_dim, 16)) if q_len == 1 else 1)}
 
 
 def rmsnorm(rows: int, width: int) -> dict:

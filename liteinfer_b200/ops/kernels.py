@@ -47,6 +47,12 @@ _SIGNATURES = {
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "li_paged_attention_stream": ("attention_stream", [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "li_paged_attention_stream_supports": ("attention_stream", [c_int, c_int, c_int, c_int]),
+    "li_paged_attention_stream_capacity": ("attention_stream", [c_int]),
     "li_paged_attention_mma_counters": ("attention_mma", [c_int, c_int, c_int, c_int]),
     "li_paged_attention_mma_decode_capacity": ("attention_mma", [c_int]),
     "li_paged_attention_tcgen05": ("attention_tcgen05", [
@@ -383,28 +389,31 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
            "rope_kv_write")
 
 
-_decode_capacity: dict[int, int] = {}
+_decode_capacity: dict[tuple[int, bool], int] = {}
 
 
-def decode_capacity(head_dim: int) -> int:
+def decode_capacity(head_dim: int, streaming: bool = False) -> int:
     """Blocks of the decode attention launch that the device holds at once (asked of the occupancy calculator
-    once per head size); without a device, what a B200 holds."""
-    if head_dim not in _decode_capacity:
+    once per head size and kernel); without a device, what a B200 holds."""
+    key = (head_dim, streaming)
+    if key not in _decode_capacity:
         blocks = 0
         if torch.cuda.is_available():
-            blocks = int(_fn("li_paged_attention_mma_decode_capacity")(head_dim))
-        _decode_capacity[head_dim] = blocks or (5 if head_dim <= 64 else 2) * NUM_SMS
-    return _decode_capacity[head_dim]
+            name = "li_paged_attention_stream_capacity" if streaming else "li_paged_attention_mma_decode_capacity"
+            blocks = int(_fn(name)(head_dim))
+        _decode_capacity[key] = blocks or ((3 if streaming else 5) if head_dim <= 64 else 2) * NUM_SMS
+    return _decode_capacity[key]
 
 
-def decode_splits_for(num_decode: int, kv_heads: int, max_context_len: int, head_dim: int = 64) -> int:
+def decode_splits_for(num_decode: int, kv_heads: int, max_context_len: int, head_dim: int = 64,
+                      streaming: bool = False) -> int:
     """Blocks that share one sequence's keys in a decode launch: as many as still run as one wave when the
     batch is narrow (a launch a little over one wave takes as long as two), never fewer than two key tiles
     each, at most 32 (liteinfer/engine/model_runner.py:250-272 and paged_kernels.py:645-693 choose likewise)."""
     tiles = -(-max_context_len // 64)
     if tiles < 4:
         return 1
-    return max(1, min(decode_capacity(head_dim) // max(1, num_decode * kv_heads), tiles // 2, 32))
+    return max(1, min(decode_capacity(head_dim, streaming) // max(1, num_decode * kv_heads), tiles // 2, 32))
 
 
 def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
@@ -422,11 +431,12 @@ def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, q
 
 def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
                         seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0,
-                        num_splits=1, newest=None) -> torch.Tensor:
+                        num_splits=1, newest=None, streaming=False) -> torch.Tensor:
     """The tensor-core kernel (bfloat16, head size 64 or 128); `num_splits` > 1 splits every sequence's keys
     over that many blocks, the last of which merges the partial results.  `newest` (NewestToken, single-token
     sequences only): q is unrotated and the newest key and value are not in their pages yet; the kernel
-    rotates q and the key and stores key and value itself."""
+    rotates q and the key and stores key and value itself.  `streaming` (single-token sequences, sizes that
+    `stream_attention_supports` allows): the kernel that passes K and V through registers only."""
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
     pages, kvh, page_size, hd = k_pool.shape
     partial_out = partial_lse = counters = None
@@ -438,13 +448,22 @@ def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query
         counters = scratch_for(q.device).attention_counters
         if need > counters.numel():
             counters = torch.zeros(need, dtype=torch.int32, device=q.device)
+    tail = (_ptr(newest.inv_freq if newest else None), _ptr(newest.k if newest else None),
+            _ptr(newest.v if newest else None), int(newest.store) if newest else 0)
+    if streaming:
+        assert max_q_len == 1
+        _check(_fn("li_paged_attention_stream")(
+            q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
+            block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
+            _ptr(seq_index), num_seqs, heads, kv_heads, head_dim, page_size, pages, float(scale), int(window),
+            int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters), *tail,
+            scratch_for(q.device).gemm_error.data_ptr(), _stream()), "paged_attention_stream")
+        return out
     _check(_fn("li_paged_attention_mma")(
         q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
         _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
-        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters),
-        _ptr(newest.inv_freq if newest else None), _ptr(newest.k if newest else None),
-        _ptr(newest.v if newest else None), int(newest.store) if newest else 0, _stream()),
+        int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters), *tail, _stream()),
         "paged_attention_mma")
     return out
 
@@ -486,6 +505,13 @@ def tcgen05_attention_supports(dtype: torch.dtype, heads: int, kv_heads: int, he
         _fn("li_paged_attention_tcgen05_supports")(heads, kv_heads, head_dim, page_size))
 
 
+def stream_attention_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether single-token sequences can go through the kernel that streams K and V through registers.
+    LITEINFER_DECODE_STREAM=0 keeps them on the shared-memory kernel."""
+    return (dtype == torch.bfloat16 and os.environ.get("LITEINFER_DECODE_STREAM", "1") != "0"
+            and bool(_fn("li_paged_attention_stream_supports")(heads, kv_heads, head_dim, page_size)))
+
+
 def mma_attention_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim in (64, 128) and heads // kv_heads <= 64
 
@@ -524,9 +550,10 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
              scale, window)
     if plan.num_decode:
         bound = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window)
-        splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound, head_dim)
+        streaming = stream_attention_supports(q.dtype, heads, kv_heads, head_dim, page_size)
+        splits = decode_splits or decode_splits_for(plan.num_decode, kv_heads, bound, head_dim, streaming)
         paged_attention_mma(*common, plan.decode_seqs, plan.num_decode, 1, heads, kv_heads, head_dim, scale,
-                            window, splits, newest)
+                            window, splits, newest, streaming)
     return out
 
 
