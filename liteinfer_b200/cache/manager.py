@@ -77,6 +77,8 @@ class CacheManager:
         self._slot_of: dict[str, int] = {}
         self._length: dict[str, int] = {}
         self._state_tensors: list[torch.Tensor] = []
+        self._table_version: dict[str, int] = {}            # changes whenever a block table of the request does
+        self._versions = 0
 
         by_need: dict[KVNeed, KVGroup] = {}
         for stop, entry in enumerate(schedule):
@@ -132,6 +134,15 @@ class CacheManager:
     def state_slot(self, request_id: str) -> int:
         return self._slot_of[request_id]
 
+    def table_version(self, request_id: str) -> int:
+        """A number that is new whenever one of the request's block tables (or its state slot) has changed: a
+        caller that kept a copy of the tables may keep it while the number stays."""
+        return self._table_version[request_id]
+
+    def _touch(self, request_id: str) -> None:
+        self._versions += 1
+        self._table_version[request_id] = self._versions
+
     @property
     def live_requests(self) -> list[str]:
         return list(self._length)
@@ -173,10 +184,14 @@ class CacheManager:
                 state[slot].zero_()
             for group in self.groups:
                 group.tables[request_id] = []
+            self._touch(request_id)
         for request_id, total in zip(request_ids, new_totals, strict=True):
             old = self._length[request_id]
             for group in self.groups:
                 blocks = group.missing_blocks(request_id, old, total)
+                if not blocks:
+                    continue
+                self._touch(request_id)
                 pages = group.allocator.allocate(len(blocks))
                 table = group.tables[request_id]
                 for block, page in zip(blocks, pages, strict=True):
@@ -193,9 +208,12 @@ class CacheManager:
             table = group.tables[request_id]
             passed = min(group.first_needed_block(new_total), len(table))
             freed = [table[b] for b in range(passed) if table[b] >= 0]
+            if not freed:
+                continue
             for b in range(passed):
                 table[b] = -1
             group.allocator.free(freed)
+            self._touch(request_id)
 
     def rollback(self, request_ids: list[str]) -> None:
         """A step failed after its reservation: give back the pages beyond what each request holds."""
@@ -211,6 +229,7 @@ class CacheManager:
                 table = group.tables[request_id]
                 group.allocator.free([p for p in table[keep:] if p >= 0])
                 del table[keep:]
+            self._touch(request_id)
 
     def release(self, request_id: str) -> None:
         """The request is over: all its pages and its state slot go back."""
@@ -221,6 +240,7 @@ class CacheManager:
             group.allocator.free([p for p in table if p >= 0])
         self.slots.free([self._slot_of.pop(request_id)])
         del self._length[request_id]
+        del self._table_version[request_id]
 
     # -------------------------------------------------------------- views
     def block_table(self, group: int, request_id: str) -> list[int]:

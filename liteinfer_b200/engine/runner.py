@@ -128,6 +128,40 @@ class _DecodeGraph:
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
         self.launches = 0
+        # The batch is staged in one pinned buffer that keeps its contents from step to step: the rows of a
+        # request (its block tables, its state slot) are rewritten only when the cache manager says they changed,
+        # what is the same for every batch of this width is written once, and a step writes tokens and lengths.
+        self.host = torch.zeros(self.batch.total, dtype=torch.int32, pin_memory=True)
+        self.views = self.batch.views(self.host.numpy())
+        self.copied = torch.cuda.Event()       # recorded behind the copy of `host` to the device
+        self.row_keys: list[tuple[str, int] | None] = [None] * width
+        tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = self.views
+        seq[:] = np.arange(width, dtype=np.int32)
+        qsl[:] = np.arange(width + 1, dtype=np.int32)
+        rows[:] = seq
+        dseq[:] = seq
+        dtok[:] = seq
+        for table in tables:
+            table.fill(-1)
+
+    def stage(self, entries: list[StepEntry], cache: CacheManager, starts: list[int]) -> None:
+        """Writes this step's batch (every entry one token, logits wanted) into the pinned buffer."""
+        self.copied.synchronize()              # the device has read the batch before this one
+        tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = self.views
+        tok[:] = [entry.tokens[0] for entry in entries]
+        pos[:] = starts
+        np.add(pos, 1, out=ctxl)
+        for i, entry in enumerate(entries):
+            key = (entry.request_id, cache.table_version(entry.request_id))
+            if self.row_keys[i] == key:
+                continue
+            self.row_keys[i] = key
+            slots[i] = cache.state_slot(entry.request_id)
+            for g, width in enumerate(self.batch.widths):
+                blocks = cache.block_table(g, entry.request_id)
+                row = tables[g][i * width:(i + 1) * width]
+                row[:len(blocks)] = blocks
+                row[len(blocks):] = -1
 
     def capture(self, runner: ModelRunner) -> None:
         """Called with the buffers holding a real batch: one eager pass on a side stream, then the capture."""
@@ -221,11 +255,9 @@ class ModelRunner:
 
     def _replay(self, graph: _DecodeGraph, entries: list[StepEntry]) -> torch.Tensor:
         starts = [self.cache.length(e.request_id) for e in entries]
-        # A fresh pinned buffer every step: the copy below is asynchronous, and the host may be
-        # filling the next step's batch before the device has read this one.
-        host = torch.empty(graph.batch.total, dtype=torch.int32, pin_memory=True)
-        _fill(graph.batch, host.numpy(), entries, self.cache, starts)
-        graph.device_buffer.copy_(host, non_blocking=True)
+        graph.stage(entries, self.cache, starts)
+        graph.device_buffer.copy_(graph.host, non_blocking=True)
+        graph.copied.record()
         if graph.graph is None:
             graph.capture(self)
         graph.graph.replay()

@@ -170,3 +170,33 @@ def test_random_orders_keep_the_books(seed):
     for r in list(lengths):
         m.release(r)
     assert all(g.allocator.num_held == 0 for g in m.groups) and m.slots.num_held == 0
+
+
+def test_table_version_moves_exactly_when_a_table_does():
+    """A caller may keep a copy of a request's block tables while `table_version` stays the same."""
+    cache = _manager([FULL, WINDOW], page_size=4, num_pages=16)
+
+    def snapshot(r):
+        return [list(cache.block_table(g, r)) for g in range(len(cache.groups))], cache.state_slot(r)
+
+    cache.reserve(["a"], [3]); cache.commit("a", 3)
+    version, seen = cache.table_version("a"), snapshot("a")
+    history = {version}
+    for total in range(4, 30):
+        cache.reserve(["a"], [total])
+        cache.commit("a", total)
+        if cache.table_version("a") == version:
+            assert snapshot("a") == seen
+        else:
+            assert snapshot("a") != seen and cache.table_version("a") not in history
+            version, seen = cache.table_version("a"), snapshot("a")
+            history.add(version)
+    cache.reserve(["a"], [40])                       # new pages ...
+    assert cache.table_version("a") != version
+    version = cache.table_version("a")
+    cache.rollback(["a"])                            # ... given back: the tables moved again
+    assert cache.table_version("a") != version
+    cache.release("a")
+    cache.reserve(["a"], [2])                        # the same name again is a new request
+    assert cache.table_version("a") not in history
+    cache.check_invariants()
