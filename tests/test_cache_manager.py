@@ -200,3 +200,30 @@ def test_table_version_moves_exactly_when_a_table_does():
     cache.reserve(["a"], [2])                        # the same name again is a new request
     assert cache.table_version("a") not in history
     cache.check_invariants()
+
+
+def test_slot_addressing_follows_the_block_tables():
+    """`packed_addresses`, `newest_slots` and `slot_table` name the same places as the block tables the
+    kernels read: a token written through a slot is found through (page, position in page)."""
+    from liteinfer_b200.cache.addressing import newest_slots, packed_addresses, slot_table
+
+    cache = _manager([FULL], page_size=4, num_pages=16, storage=True)
+    cache.reserve(["b"], [5]); cache.commit("b", 5)
+    cache.reserve(["a", "b"], [7, 11])
+    tables = [cache.block_table(0, r) for r in ("a", "b")]
+    packed = packed_addresses(tables, [0, 5], [7, 6], 4)
+    assert packed.query_start_loc.tolist() == [0, 7, 13] and packed.context_lens.tolist() == [7, 11]
+    assert packed.positions[0].tolist() == [*range(7), *range(5, 11)]
+    pool = cache.groups[0].pool[0, 0]                                  # [pages, kv_heads, page_size, head_dim]
+    for token, slot in enumerate(packed.slots[0].tolist()):
+        pool[slot // 4, :, slot % 4] = token + 1                       # "write" every token of the step
+    for i, (start, count) in enumerate(((0, 7), (5, 6))):
+        for position in range(start, start + count):
+            page = tables[i][position // 4]
+            token = int(packed.query_start_loc[i]) + position - start
+            assert float(pool[page, 0, position % 4, 0]) == token + 1
+    table = slot_table(tables, [7, 11], 4)
+    assert table.shape == (2, 11) and table[0, 7:].tolist() == [-1] * 4
+    assert table[1, 5:11].tolist() == packed.slots[0, 7:].tolist()
+    assert newest_slots(tables, [6, 10], 4).tolist() == [[int(table[0, 6]), int(table[1, 10])]]
+    assert len(set(table[table >= 0].tolist())) == 18                  # no slot named twice
