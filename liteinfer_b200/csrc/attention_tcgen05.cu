@@ -1,14 +1,15 @@
 // Paged attention for prompts and portions of prompts on the fifth-generation tensor cores
-// (bfloat16, head size 64, pages of 16, 32 or 64 tokens).
+// (bfloat16, head sizes 64 and 128, pages of 16, 32 or 64 tokens).
 //
 // Rule as in attention_generic.cu (liteinfer/models/attention.py:24-27,69-84).  A block owns 128
 // rows for one KV head, a row being (query token, head of the group), and walks the visible keys
 // in tiles of 64:
 //
-//   loader  (warp 0)    TMA: each page of a tile's keys and values is one box of the pool's tensor map,
-//                       landing in 128-byte-swizzled shared memory, three tiles ahead at most.
-//   issuer  (warp 1)    tcgen05.mma: S = Q K^T (128 x 64, K 64) into one of two score buffers in tensor
-//                       memory, then O += P V (128 x 64, K 64 keys) into the output accumulator;
+//   loader  (warp 0)    TMA: each page of a tile's keys and values is one box of the pool's tensor map per 64
+//                       dimensions, landing in 128-byte-swizzled shared memory, three tiles ahead at most.
+//   issuer  (warp 1)    tcgen05.mma: S = Q K^T (128 x 64, K = head size) into one of two score buffers in
+//                       tensor memory, then O += P V (128 x 64 per 64 dimensions, K 64 keys) into the output
+//                       accumulator;
 //                       S of the next tile is issued before P V of this one, so the tensor cores work
 //                       while the softmax of this tile is computed.
 //   softmax (warps 2-5) one thread per row: tcgen05.ld brings the row's 64 scores into registers, so
@@ -31,7 +32,6 @@ namespace li {
 
 constexpr int kRows = 128;       // rows (query token x head in group) per block
 constexpr int kKeys = 64;        // keys per tile
-constexpr int kHeadDim = 64;
 constexpr int kKvStages = 3;
 constexpr int kAttnThreads = 192;
 constexpr float kLog2eF = 1.4426950408889634f;
@@ -81,15 +81,21 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
   return d;
 }
 
-__global__ void __launch_bounds__(kAttnThreads, 2)
+// Shared memory holds everything in sub-tiles of 64 columns (128 bytes, one swizzle row): Q is D/64 sub-tiles of
+// 128 rows, a K or V stage D/64 sub-tiles of 64 keys, a P buffer one sub-tile of 128 rows x 64 keys.
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, D == 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          const TcAttnParams p) {
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_addr(smem_raw) + 1023u) & ~1023u;
-  constexpr unsigned kTileBytes = kKeys * kHeadDim * 2;             // 8 KB: one K or V tile
-  constexpr unsigned kRowTileBytes = kRows * kHeadDim * 2;          // 16 KB: Q, or one P buffer
+  constexpr int kSub = D / 64;                                      // sub-tiles of 64 dimensions
+  constexpr unsigned kKeySubBytes = kKeys * 64 * 2;                 // 8 KB: 64 keys x 64 dimensions
+  constexpr unsigned kRowSubBytes = kRows * 64 * 2;                 // 16 KB: 128 rows x 64 columns
+  constexpr unsigned kTileBytes = kSub * kKeySubBytes;              // one K or V tile
+  constexpr unsigned kRowTileBytes = kRowSubBytes;                  // one P buffer
   const unsigned q_smem = base;
-  const unsigned p_smem = q_smem + kRowTileBytes;                   // 2 buffers
+  const unsigned p_smem = q_smem + kSub * kRowSubBytes;             // 2 buffers
   const unsigned k_smem = p_smem + 2 * kRowTileBytes;               // kKvStages
   const unsigned v_smem = k_smem + kKvStages * kTileBytes;          // kKvStages
   const unsigned bars = v_smem + kKvStages * kTileBytes;
@@ -137,26 +143,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {   // scores 2 x 64 columns, output 64 columns: 256 columns asked for (a power of two)
+  if (warp == 1) {   // scores 2 x 64 columns, output D columns: 256 columns asked for (a power of two)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // Q: each softmax thread copies its row (128 bytes) into the swizzled tile; rows of padding are zero.
   if (warp >= 2) {
     const int row = (warp & 3) * 32 + lane;
-    uint4 v[8];
-    if (row < rows_used) {
-      const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + qi) * p.q_row_stride + (size_t)head * kHeadDim);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) v[c] = src[c];
-    } else {
+    for (int sub = 0; sub < kSub; ++sub) {
+      uint4 v[8];
+      if (row < rows_used) {
+        const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+        const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + qi) * p.q_row_stride + (size_t)head * D + sub * 64);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) v[c] = make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < 8; ++c) v[c] = src[c];
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v[c] = make_uint4(0, 0, 0, 0);
+      }
+      unsigned char* dst = generic_base + (q_smem - base) + sub * kRowSubBytes + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = v[c];
     }
-    unsigned char* dst = generic_base + (q_smem - base) + row * 128;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = v[c];
     fence_async_shared();
   }
   tcgen05_fence_before();
@@ -176,7 +185,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     // ------------------------------------------------------------------ loader
     if (lane == 0) {
       const int boxes = kKeys / p.page_size;
-      const unsigned box_bytes = (unsigned)p.page_size * kHeadDim * 2;
+      const unsigned box_bytes = (unsigned)p.page_size * 64 * 2;
       for (int t = 0; t < ntiles; ++t) {
         const int stage = t % kKvStages;
         const unsigned phase = (unsigned)(t / kKvStages) & 1;
@@ -191,12 +200,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           rows[b] = (page >= 0 && page < p.num_pages) ? (page * p.kv_heads + kvh) * p.page_size : -1;
           valid += rows[b] >= 0;
         }
-        mbar_expect_tx(k_full(stage), valid * box_bytes);
-        mbar_expect_tx(v_full(stage), valid * box_bytes);
+        mbar_expect_tx(k_full(stage), valid * kSub * box_bytes);
+        mbar_expect_tx(v_full(stage), valid * kSub * box_bytes);
         for (int b = 0; b < boxes; ++b) {
           if (rows[b] < 0) continue;
-          tma_load_2d(k_smem + stage * kTileBytes + b * box_bytes, &map_k, k_full(stage), 0, rows[b]);
-          tma_load_2d(v_smem + stage * kTileBytes + b * box_bytes, &map_v, v_full(stage), 0, rows[b]);
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub) {
+            tma_load_2d(k_smem + stage * kTileBytes + sub * kKeySubBytes + b * box_bytes, &map_k, k_full(stage), sub * 64, rows[b]);
+            tma_load_2d(v_smem + stage * kTileBytes + sub * kKeySubBytes + b * box_bytes, &map_v, v_full(stage), sub * 64, rows[b]);
+          }
         }
       }
     }
@@ -212,8 +224,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         if (!mbar_wait(k_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 13)) return false;
         tcgen05_fence_after();
 #pragma unroll
-        for (int k = 0; k < kHeadDim / 16; ++k)
-          umma_bf16(tmem_s[buf], umma_desc(q_smem + k * 32), umma_desc(k_smem + stage * kTileBytes + k * 32), idesc_qk, k > 0);
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem_s[buf], umma_desc(q_smem + (k / 4) * kRowSubBytes + (k % 4) * 32),
+                    umma_desc(k_smem + stage * kTileBytes + (k / 4) * kKeySubBytes + (k % 4) * 32), idesc_qk, k > 0);
         umma_commit(s_full(buf));
         return true;
       };
@@ -225,9 +238,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         if (!mbar_wait(p_full(buf), (unsigned)(t >> 1) & 1, p.error_flag, 15)) { ok = false; break; }
         tcgen05_fence_after();
 #pragma unroll
-        for (int k = 0; k < kKeys / 16; ++k)
-          umma_bf16(tmem_o, umma_desc(p_smem + buf * kRowTileBytes + k * 32),
-                    umma_desc(v_smem + stage * kTileBytes + k * 16 * 128), idesc_pv, t > 0 || k > 0);
+        for (int sub = 0; sub < kSub; ++sub)
+#pragma unroll
+          for (int k = 0; k < kKeys / 16; ++k)
+            umma_bf16(tmem_o + sub * 64, umma_desc(p_smem + buf * kRowTileBytes + k * 32),
+                      umma_desc(v_smem + stage * kTileBytes + sub * kKeySubBytes + k * 16 * 128), idesc_pv, t > 0 || k > 0);
         umma_commit(kv_empty(stage));
         umma_commit(pv_done(buf));
       }
@@ -312,12 +327,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         tcgen05_fence_after();
         unsigned o[32];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          tmem_load32(tmem_o + lane_field + half * 32, o);
+        for (int part = 0; part < D / 32; ++part) {
+          tmem_load32(tmem_o + lane_field + part * 32, o);
           tmem_load_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_store32(tmem_o + lane_field + half * 32, o);
+          tmem_store32(tmem_o + lane_field + part * 32, o);
         }
         tmem_store_wait();
       }
@@ -327,10 +342,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       if (key0 < lo || key0 + kKeys > hi) {
         if (!mbar_wait(v_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 18)) { ok = false; break; }
         unsigned char* vt = generic_base + (v_smem - base) + stage * kTileBytes;
-        for (int e = threadIdx.x - 64; e < kKeys * 8; e += 128) {
-          const int key = e >> 3;
+        for (int e = threadIdx.x - 64; e < kSub * kKeys * 8; e += 128) {
+          const int sub = e / (kKeys * 8), key = (e >> 3) % kKeys;
           const int kpos = key0 + key;
-          if (kpos < lo || kpos >= hi) *reinterpret_cast<uint4*>(vt + key * 128 + ((e & 7) << 4)) = make_uint4(0, 0, 0, 0);
+          if (kpos < lo || kpos >= hi)
+            *reinterpret_cast<uint4*>(vt + sub * kKeySubBytes + key * 128 + ((e & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
       fence_async_shared();
@@ -343,9 +359,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       tcgen05_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-      bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * kHeadDim;
+      bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int half = 0; half < D / 32; ++half) {
         unsigned o[32];
         __syncwarp();
         tmem_load32(tmem_o + lane_field + half * 32, o);
@@ -375,10 +391,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   }
 }
 
-// The pool [pages, kv_heads, page_size, 64] as a 2-D map of rows of 64, one page of one head per box.
-static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int page_size) {
-  static std::map<std::tuple<const void*, long, int>, CUtensorMap> cache;
-  const auto key = std::make_tuple(pool, rows, page_size);
+// The pool [pages, kv_heads, page_size, head_dim] as a 2-D map of rows of head_dim; a box is 64 dimensions of one
+// page of one head.
+static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int page_size, int head_dim) {
+  static std::map<std::tuple<const void*, long, int, int>, CUtensorMap> cache;
+  const auto key = std::make_tuple(pool, rows, page_size, head_dim);
   const auto found = cache.find(key);
   if (found != cache.end()) {
     *map = found->second;
@@ -386,9 +403,9 @@ static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int pag
   }
   EncodeTiledFn encode = encode_tiled();
   if (!encode) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)kHeadDim * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)kHeadDim, (cuuint32_t)page_size};
+  const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
   const cuuint32_t elem[2] = {1, 1};
   if (encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -399,19 +416,34 @@ static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int pag
   return true;
 }
 
+template <int D>
+static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
+                               cudaStream_t stream) {
+  constexpr size_t smem = (size_t)(D / 64 + 2) * kRows * 64 * 2 + 2 * kKvStages * (size_t)kKeys * D * 2 +
+                          8 * (3 * kKvStages + 8) + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  attention_tcgen05_kernel<D><<<grid, kAttnThreads, smem, stream>>>(mk, mv, p);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace li
 
 using namespace li;
 
 // Whether li_paged_attention_tcgen05 takes these sizes.
 LI_EXPORT int li_paged_attention_tcgen05_supports(int heads, int kv_heads, int head_dim, int page_size) {
-  if (kv_heads < 1 || heads % kv_heads || head_dim != kHeadDim) return 0;
+  if (kv_heads < 1 || heads % kv_heads || (head_dim != 64 && head_dim != 128)) return 0;
   const int groups = heads / kv_heads;
   if (groups > kRows || (kRows % groups)) return 0;
   return page_size == 16 || page_size == 32 || page_size == 64;
 }
 
-// bfloat16; head_dim 64; page_size 16, 32 or 64; groups dividing 128.  Sequences may bring any number of queries
+// bfloat16; head_dim 64 or 128; page_size 16, 32 or 64; groups dividing 128.  Sequences may bring any number of queries
 // (the kernel is meant for those that bring many).  error_flag (device int, zero): set if a wait inside gave up.
 LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* out, int out_row_stride,
                                          const void* k_pool, const void* v_pool, const int* block_table,
@@ -427,24 +459,15 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
     return LI_ERR_ALIGNMENT;
   CUtensorMap mk, mv;
   const long rows = (long)num_pages * kv_heads * page_size;
-  if (!make_pool_map(&mk, k_pool, rows, page_size) || !make_pool_map(&mv, v_pool, rows, page_size))
+  if (!make_pool_map(&mk, k_pool, rows, page_size, head_dim) || !make_pool_map(&mv, v_pool, rows, page_size, head_dim))
     return LI_ERR_UNSUPPORTED;
   int shift = 0;
   while ((1 << shift) < page_size) ++shift;
   TcAttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, block_table, table_stride,
                  query_start_loc, context_lens, seq_index, heads, kv_heads, page_size, shift, num_pages,
                  scale * kLog2eF, window, error_flag};
-  constexpr size_t smem = 3 * (size_t)kRows * kHeadDim * 2 + 2 * kKvStages * (size_t)kKeys * kHeadDim * 2 +
-                          8 * (3 * kKvStages + 8) + 16 + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
   const int groups = heads / kv_heads;
   const int tq = kRows / groups;
   const dim3 grid((max_q_len + tq - 1) / tq, kv_heads, num_seqs);
-  attention_tcgen05_kernel<<<grid, kAttnThreads, smem, stream>>>(mk, mv, p);
-  return (int)cudaGetLastError();
+  return head_dim == 64 ? launch_tc_attention<64>(mk, mv, p, grid, stream) : launch_tc_attention<128>(mk, mv, p, grid, stream);
 }

@@ -522,12 +522,12 @@ def test_gemm_tcgen05_gated_epilogue(M, inter, K, act):
 
 @pytest.mark.parametrize("heads,kv_heads,page_size", [(4, 1, 16), (32, 8, 16), (8, 8, 32), (16, 2, 64), (128, 1, 16)])
 @pytest.mark.parametrize("window", [0, 100])
-def test_tcgen05_attention_against_the_plain_kernel(heads, kv_heads, page_size, window):
+@pytest.mark.parametrize("d", [64, 128])
+def test_tcgen05_attention_against_the_plain_kernel(heads, kv_heads, page_size, window, d):
     """The tcgen05 / TMA / tensor-memory attention kernel: portions, whole prompts and single tokens over shuffled
     pages, NaN in every slot no request owns, contexts that straddle the 64-key tiles; no wait may give up."""
     from liteinfer_b200 import ops
 
-    d = 64
     q_lens, ctx_lens = [1, 130, 1, 7, 64, 2, 257], [700, 190, 1, 7, 64, 129, 300]
     case = _paged_case(torch.bfloat16, heads, kv_heads, d, page_size, q_lens, ctx_lens)
     qkv, k_pool, v_pool = case["qkv"], case["k_pool"], case["v_pool"]
@@ -548,6 +548,6 @@ def test_tcgen05_attention_refuses_what_it_cannot_do():
     from liteinfer_b200 import ops
 
     assert not ops.tcgen05_attention_supports(torch.bfloat16, 6, 2, 64, 16)      # groups of 3 do not divide 128
-    assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 128, 16)     # head size 128: the mma.sync kernel
+    assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 96, 16)      # head size 96: the plain kernel
     assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 64, 8)       # pages of 8
     assert not ops.tcgen05_attention_supports(torch.float32, 4, 2, 64, 16)
