@@ -36,6 +36,14 @@ LLAMA_1B = {
                      "original_max_position_embeddings": 8192},
     "tie_word_embeddings": True, "max_position_embeddings": 131072, "hidden_act": "silu",
 }
+# The other shapes of the reference's configurations, for `--shape` (the default run and the contract are the 1B shape).
+LLAMA_3B = dict(LLAMA_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, head_dim=128)
+LLAMA_8B = dict(LLAMA_1B, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, head_dim=128,
+                tie_word_embeddings=False,
+                rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                              "original_max_position_embeddings": 8192})
+SHAPES = {"1b": ("Llama 3.2 1B", LLAMA_1B, 4096), "3b": ("Llama 3.2 3B", LLAMA_3B, 4096),
+          "8b": ("Llama 3.1 8B", LLAMA_8B, 8192)}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
@@ -137,7 +145,8 @@ def run_ours(args) -> dict:
     from liteinfer_b200.sampling.sampler import Sampler
     from liteinfer_b200.weights.random_init import write_random_model
 
-    cfg = dict(LLAMA_1B)
+    model_name, shape, CONTEXT = SHAPES[args.shape]     # the context length of the chosen shape
+    cfg = dict(shape)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -220,15 +229,15 @@ def run_ours(args) -> dict:
         llm.close()
 
     return {
-        "metric": "decode tok/s at batch 8 (Llama 3.2 1B shape)", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "metric": f"decode tok/s at batch 8 ({model_name} shape)", "value": value, "unit": "tokens/s", "n_gpus": 1,
         "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": value / BASELINE_DECODE_B8_TOKS, "dtype": "bf16", "data": "synthetic ids, random weights",
+        "vs_baseline": value / BASELINE_DECODE_B8_TOKS if args.shape == "1b" and not args.layers else None, "dtype": "bf16", "data": "synthetic ids, random weights",
         "impl": "ours",
-        "config": {"model": "llama-3.2-1b-shape", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+        "config": {"model": model_name.lower().replace(" ", "-") + "-shape", "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
                    "hidden": hidden, "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": inter, "vocab": vocab, "global_batch": batch,
                    "seq_len": CONTEXT, "page_size": PAGE, "parallelism": "single-gpu",
-                   "l2": "inputs larger than L2 (weights 2.5 GB + cache read every step)",
+                   "l2": "inputs larger than L2 (weights and cache are read every step)",
                    "baseline": "reference A40 batch-8 decode, 1248 tok/s"},
         "clocks": clock_record, "e2e": e2e, "gpu_launches": launches * steps,
         "prefill": prefill, "roofline": roofline, "points": {"decode_b1": b1, "decode_b64": b64},
@@ -263,6 +272,7 @@ def main() -> int:
     parser.add_argument("--section", default="all", choices=["all", "decode", "prefill"],
                         help="run one part only (for profiling); the JSON line then lacks the other parts")
     parser.add_argument("--batch", type=int, default=8, help="decode batch of --section decode")
+    parser.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes: Llama 3.2 1B (the contract's), 3B or 3.1 8B")
     args = parser.parse_args()
     if args.gpus != 1:
         if int(os.environ.get("RANK", "0")) == 0:

@@ -439,11 +439,11 @@ using namespace li;
 LI_EXPORT int li_paged_attention_tcgen05_supports(int heads, int kv_heads, int head_dim, int page_size) {
   if (kv_heads < 1 || heads % kv_heads || (head_dim != 64 && head_dim != 128)) return 0;
   const int groups = heads / kv_heads;
-  if (groups > kRows || (kRows % groups)) return 0;
+  if (groups > kRows) return 0;      // a block's 128 rows hold 128 / groups query tokens (the rest is padding)
   return page_size == 16 || page_size == 32 || page_size == 64;
 }
 
-// bfloat16; head_dim 64 or 128; page_size 16, 32 or 64; groups dividing 128.  Sequences may bring any number of queries
+// bfloat16; head_dim 64 or 128; page_size 16, 32 or 64; groups of at most 128 heads.  Sequences may bring any number of queries
 // (the kernel is meant for those that bring many).  error_flag (device int, zero): set if a wait inside gave up.
 LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* out, int out_row_stride,
                                          const void* k_pool, const void* v_pool, const int* block_table,

@@ -488,7 +488,7 @@ def fused_decode_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_di
 def paged_attention_tcgen05(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
                             seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0) -> torch.Tensor:
     """The tcgen05 / TMA / tensor-memory attention kernel for prompts and portions (bfloat16, head size 64,
-    pages of 16, 32 or 64 tokens, groups dividing 128).  `gemm_error_flag(device)` tells afterwards whether a
+    pages of 16, 32 or 64 tokens, groups of at most 128 heads).  `gemm_error_flag(device)` tells afterwards whether a
     wait inside the kernel ever gave up."""
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
     pages, kvh, page_size, hd = k_pool.shape

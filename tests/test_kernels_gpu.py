@@ -520,7 +520,8 @@ def test_gemm_tcgen05_gated_epilogue(M, inter, K, act):
     torch.testing.assert_close(got.float(), two.float(), rtol=2 ** -6, atol=2 ** -6)
 
 
-@pytest.mark.parametrize("heads,kv_heads,page_size", [(4, 1, 16), (32, 8, 16), (8, 8, 32), (16, 2, 64), (128, 1, 16)])
+@pytest.mark.parametrize("heads,kv_heads,page_size", [(4, 1, 16), (32, 8, 16), (8, 8, 32), (16, 2, 64), (128, 1, 16),
+                                                      (24, 8, 16), (5, 1, 32), (7, 7, 16)])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("d", [64, 128])
 def test_tcgen05_attention_against_the_plain_kernel(heads, kv_heads, page_size, window, d):
@@ -547,7 +548,7 @@ def test_tcgen05_attention_against_the_plain_kernel(heads, kv_heads, page_size, 
 def test_tcgen05_attention_refuses_what_it_cannot_do():
     from liteinfer_b200 import ops
 
-    assert not ops.tcgen05_attention_supports(torch.bfloat16, 6, 2, 64, 16)      # groups of 3 do not divide 128
+    assert not ops.tcgen05_attention_supports(torch.bfloat16, 129, 1, 64, 16)    # a group larger than a block's rows
     assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 96, 16)      # head size 96: the plain kernel
     assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 64, 8)       # pages of 8
     assert not ops.tcgen05_attention_supports(torch.float32, 4, 2, 64, 16)
