@@ -51,8 +51,11 @@ def _cdiv(a: int, b: int) -> int:
 
 
 class EngineCore:
-    def __init__(self, config: EngineConfig) -> None:
+    def __init__(self, config: EngineConfig, text_every_step: bool = True) -> None:
+        """`text_every_step` False: a request's text is decoded when it finishes (and step by step only if it
+        has stop strings, which must be looked for in the text); nobody reads it earlier in a batch call."""
         self.config = config
+        self.text_every_step = text_every_step
         self.device = config.resolved_device()
         self.stats = EngineStats()
         self.sampler = Sampler(config.seed)
@@ -191,10 +194,14 @@ class EngineCore:
             sampled = self.sampler(logits, [s.sampling_params for s in sampling], [s.request_id for s in sampling])
             for seq, token_id in zip(sampling, sampled.tolist()):   # one device-to-host read per step
                 seq.output_token_ids.append(int(token_id))
-                seq.output_text = seq.detokenizer.update(self.tokenizer, seq.output_token_ids)
+                needs_text = self.text_every_step or bool(seq.sampling_params.stop)
+                if needs_text:
+                    seq.output_text = seq.detokenizer.update(self.tokenizer, seq.output_token_ids)
                 status = resolve_stop_status(seq, int(token_id), self.tokenizer.eos_token_ids,
                                              self.config.max_model_len)
                 if status is not None:
+                    if not needs_text:      # the detokenizer catches up on everything it has not seen
+                        seq.output_text = seq.detokenizer.catch_up(self.tokenizer, seq.output_token_ids)
                     seq.status = status
                     self.stats.num_requests_finished += 1
             result.sampled = sampling

@@ -23,7 +23,7 @@ from liteinfer_b200.sampling.params import SamplingParams
 class LLM:
     def __init__(self, model: str, **engine_kwargs) -> None:
         self.config = EngineConfig(model=str(model), **engine_kwargs)
-        self.engine = EngineCore(self.config)
+        self.engine = EngineCore(self.config, text_every_step=False)   # a batch call hands text out at the end only
         self.engine.load()
         self._ids = count(0)
 

@@ -110,3 +110,13 @@ class IncrementalDetokenizer:
         self.prefix_offset = self.read_offset
         self.read_offset = len(token_ids)
         return self.text
+
+    def catch_up(self, tokenizer, token_ids: list[int]) -> str:
+        """The text of all of `token_ids` for a detokenizer that was not called at every step: what `update`
+        gives, and if the ids end inside a character, everything before that character."""
+        text = self.update(tokenizer, token_ids)
+        if self.read_offset == len(token_ids):
+            return text
+        prefix = tokenizer.decode(token_ids[self.prefix_offset:self.read_offset])
+        whole = tokenizer.decode(token_ids[self.prefix_offset:])
+        return text + whole[len(prefix):].rstrip(_REPLACEMENT_CHAR)

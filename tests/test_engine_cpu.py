@@ -52,6 +52,12 @@ def test_stop_rules_through_the_engine(cpu_kernels, model_dirs):
         gated = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, min_tokens=6,
                                                       stop_token_ids=[stop_at]))[0]
         assert len(gated.token_ids) >= 6
+        # A stop string is looked for in the text, which is then decoded at every step (otherwise at the end only).
+        text_stop = " " + str(free[3])
+        by_text = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=8, stop=[text_stop]))[0]
+        first = next(n for n in range(1, 9) if text_stop in " ".join(map(str, free[:n])))
+        assert by_text.finish_reason == "stop" and by_text.token_ids == free[:first]
+        assert by_text.text == " ".join(map(str, free[:first]))
         long = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=100))[0]
         assert long.finish_reason == "length" and len(prompt) + len(long.token_ids) == 32   # max_model_len
         with pytest.raises(ValueError, match="max_model_len"):
