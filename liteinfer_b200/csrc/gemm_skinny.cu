@@ -10,7 +10,7 @@
 // in flight at once, no shared-memory staging; x comes through L1/L2.
 //
 // Work unit: one block = 16 rows of w x one slice of k.  The warps of a block
-// (4, or 8 or 16 where the weight has few rows: the output and down projections)
+// (4; 8 or 16 where the weight has few rows: the output and down projections; 2 where it has very many)
 // take interleaved 32-wide k blocks and add their partial sums through shared
 // memory in a fixed order.  When k is also cut into several slices every block
 // writes its 16 x M partial tile to scratch memory and bumps the tile's counter;
@@ -68,15 +68,19 @@ LI_EXPORT int li_gemm_skinny(const void* x, const void* w, const void* bias, voi
     }
   }
   switch (nt * 100 + warps) {
+    case 102: return launch_skinny<1, 2>(p, stream);
     case 104: return launch_skinny<1, 4>(p, stream);
     case 108: return launch_skinny<1, 8>(p, stream);
     case 116: return launch_skinny<1, 16>(p, stream);
+    case 202: return launch_skinny<2, 2>(p, stream);
     case 204: return launch_skinny<2, 4>(p, stream);
     case 208: return launch_skinny<2, 8>(p, stream);
     case 216: return launch_skinny<2, 16>(p, stream);
+    case 402: return launch_skinny<4, 2>(p, stream);
     case 404: return launch_skinny<4, 4>(p, stream);
     case 408: return launch_skinny<4, 8>(p, stream);
     case 416: return launch_skinny<4, 16>(p, stream);
+    case 802: return launch_skinny<8, 2>(p, stream);
     case 804: return launch_skinny<8, 4>(p, stream);
     case 808: return launch_skinny<8, 8>(p, stream);
     default: return launch_skinny<8, 16>(p, stream);

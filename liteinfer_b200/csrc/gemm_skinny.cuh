@@ -5,7 +5,7 @@
 
 namespace li {
 
-constexpr int kSkinnyWarps = 4;                                   // warps of the narrow block; wide blocks have 8 or 16
+constexpr int kSkinnyWarps = 4;                                   // warps of the usual block; others have 2, 8 or 16
 constexpr int kBlocksPerWarp = 8;                                  // 32-wide k blocks per warp and pass
 constexpr int kMaxSlices = 16;
 
@@ -112,7 +112,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
 #pragma unroll
   for (int i = 0; i < kOwned; ++i) running[i] = 0.f;
 #pragma unroll
-  for (int round = 0; round < kWarps / 4; ++round) {
+  for (int round = 0; round < (kWarps + 3) / 4; ++round) {
     if (warp / 4 == round) {
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
@@ -129,7 +129,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
       if (e < 16 * kCols) {
         const int r = e % 16, m = e / 16;
 #pragma unroll
-        for (int wv = 0; wv < 4; ++wv) running[i] += partial[wv][r][m];
+        for (int wv = 0; wv < (kWarps < 4 ? kWarps : 4); ++wv) running[i] += partial[wv][r][m];
       }
     }
     __syncthreads();
@@ -217,13 +217,14 @@ inline int skinny_slices(int N, int K, int* slice_k) {
 // 16-row tiles is better served by wider blocks, whose warps add up through shared memory, than by slices,
 // which add up through scratch memory and a counter.  Measured on B200 at 8 rows: 3072 x 2048 with 8 warps
 // uncut 4.3 us (4 warps in 4 slices: 7.4 us); 2048 x 2048 likewise 3.7 us (5.5 us); 2048 x 8192 with 16
-// warps uncut 9.2 us (4 warps in 8 slices: 12.1 us); 16384 x 2048 stays at 4 warps uncut (15.2 us).
+// warps uncut 9.2 us (4 warps in 8 slices: 12.1 us); 16384 x 2048 with 2 warps 13.8 us (4 warps: 15.3 us: its
+// 1,024 blocks came to a wave and a third).
 // The aim is some 2,400 warps in all with at least one full pass (256 k) each; k is cut only if wide blocks
 // still leave the GPU half empty and the slices stay long.
 inline int skinny_plan(int N, int K, int* warps_out, int* slice_k) {
   const int tiles = (N + 15) / 16;
-  int warps = 4;
-  while (warps < 16 && tiles * warps < 2400 && K / (2 * warps) >= 256) warps *= 2;
+  int warps = tiles > 5 * 148 ? 2 : 4;   // more tiles than blocks of four warps fit at once: blocks of two, twice as many at once
+  while (warps >= 4 && warps < 16 && tiles * warps < 2400 && K / (2 * warps) >= 256) warps *= 2;
   int slices = 1;
   while (slices < kMaxSlices && tiles * warps * (slices + 1) <= 1200 && K / (slices + 1) >= warps * 512) ++slices;
   int per = (K + slices - 1) / slices;

@@ -473,7 +473,8 @@ def test_skinny_slices_leave_their_counters_at_zero():
     from liteinfer_b200.ops.kernels import scratch_for
 
     # Few rows of w: wide blocks; very few and a long k: slices of k as well.
-    assert ops.gemm_skinny_plan(16384, 2048) == (4, 1) and ops.gemm_skinny_plan(3072, 2048) == (8, 1)
+    assert ops.gemm_skinny_plan(16384, 2048) == (2, 1) and ops.gemm_skinny_plan(3072, 2048) == (8, 1)
+    assert ops.gemm_skinny_plan(8192, 2048) == (8, 1) and ops.gemm_skinny_plan(9600, 64) == (4, 1)
     assert ops.gemm_skinny_plan(2048, 8192) == (16, 1) and ops.gemm_skinny_plan(64, 32768) == (16, 4)
     x, w = _randn(8, 32768, dtype=torch.bfloat16), _randn(64, 32768, dtype=torch.bfloat16, seed=1, scale=0.02)
     outs = [ops.gemm_skinny(x, w, torch.empty(8, 64, dtype=torch.bfloat16, device="cuda")) for _ in range(3)]
