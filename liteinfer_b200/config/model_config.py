@@ -65,6 +65,11 @@ def _require(raw: dict[str, Any], key: str, kind: type) -> Any:
     return kind(value)
 
 
+# What the architecture's configuration class assumes for keys a config.json leaves out (sizes have no defaults here).
+_DEFAULT_ROPE_THETA = 10000.0
+_DEFAULT_RMS_NORM_EPS = 1e-6
+
+
 def _parse_rope(raw: dict[str, Any]) -> tuple[float, RopeScaling]:
     """Both spellings: legacy `rope_theta` + `rope_scaling`, and the merged `rope_parameters`."""
     merged: dict[str, Any] = {}
@@ -72,9 +77,11 @@ def _parse_rope(raw: dict[str, Any]) -> tuple[float, RopeScaling]:
         merged.update(raw["rope_scaling"])
     if isinstance(raw.get("rope_parameters"), dict):
         merged.update(raw["rope_parameters"])
-    theta = merged.get("rope_theta", raw.get("rope_theta"))
+    # A config.json that names no base gets the architecture's own default, as it does through the reference's
+    # configuration class (liteinfer/models/llama.py:64-70 reads what that class filled in).
+    theta = merged.get("rope_theta", raw.get("rope_theta", _DEFAULT_ROPE_THETA))
     if theta is None:
-        raise ConfigError("config.json has no 'rope_theta'")
+        theta = _DEFAULT_ROPE_THETA
     rope_type = merged.get("rope_type", merged.get("type", "default"))
     scaling = RopeScaling(
         rope_type=str(rope_type),
@@ -160,7 +167,7 @@ class LlamaConfig:
             num_attention_heads=heads,
             num_key_value_heads=int(kv_heads) if kv_heads is not None else heads,
             head_dim=int(head_dim),
-            rms_norm_eps=_require(raw, "rms_norm_eps", float),
+            rms_norm_eps=_require(raw, "rms_norm_eps", float) if raw.get("rms_norm_eps") is not None else _DEFAULT_RMS_NORM_EPS,
             rope_theta=theta,
             rope_scaling=scaling,
             max_position_embeddings=int(raw.get("max_position_embeddings") or 0),

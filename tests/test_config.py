@@ -46,11 +46,22 @@ def test_round_trip_through_config_json():
 
 
 @pytest.mark.parametrize("key", ["vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
-                                 "num_attention_heads", "rms_norm_eps", "rope_theta"])
+                                 "num_attention_heads"])
 def test_a_missing_size_is_refused(key):
     raw = {k: v for k, v in tiny_configs.TINY_A.items() if k != key}
     with pytest.raises(ConfigError, match=key):
         LlamaConfig.from_dict(raw)
+
+
+def test_options_a_config_leaves_out_take_the_architectures_defaults():
+    """No size has a default; the options do, as through the reference's configuration class: KV heads = heads,
+    head size = hidden / heads, rotary base 10,000 unscaled, eps 1e-6, untied head, silu, no biases."""
+    raw = {k: tiny_configs.TINY_A[k] for k in ("architectures", "vocab_size", "hidden_size", "intermediate_size",
+                                               "num_hidden_layers", "num_attention_heads")}
+    cfg = LlamaConfig.from_dict(raw)
+    assert cfg.num_key_value_heads == cfg.num_attention_heads and cfg.head_dim == cfg.hidden_size // cfg.num_attention_heads
+    assert cfg.rope_theta == 10000.0 and cfg.rope_scaling.rope_type == "default" and cfg.rms_norm_eps == 1e-6
+    assert not cfg.tie_word_embeddings and cfg.hidden_act == "silu" and not cfg.attention_bias and not cfg.mlp_bias
 
 
 @pytest.mark.parametrize("change,match", [
