@@ -42,3 +42,45 @@ def test_graph_replay_equals_eager(model_dirs, name, dtype):
             torch.testing.assert_close(eager.float(), replayed.float(), rtol=2 ** -6, atol=2 ** -6)
         else:
             assert torch.equal(eager, replayed)
+
+
+@pytest.mark.parametrize("name,dtype", [("tiny_b", torch.float32), ("tiny_d", torch.bfloat16)])
+def test_graph_rows_follow_the_requests(model_dirs, name, dtype):
+    """A graph's staged batch keeps a request's rows from step to step; they must follow when the same width is
+    filled by other requests, when requests change places, and when a request named again is a new one."""
+    from liteinfer_b200.engine.loading import build_runner
+    from liteinfer_b200.engine.runner import StepEntry
+
+    config, _, page = tiny_configs.ALL[name]
+    vocab = config["vocab_size"]
+    prompts = {f"r{i}": tiny_configs.prompt(vocab, n, 7 + i) for i, n in enumerate((5, 40, 130, 23, 64))}
+    forced = {r: tiny_configs.prompt(vocab, 40, 90 + i) for i, r in enumerate(prompts)}
+    plan = [(["r0", "r1", "r2"], 6), (["r0", "r3", "r2"], 5), (["r2", "r0", "r3"], 9), (["r3", "r4", "r0"], 4),
+            (["r1", "r4", "r0"], 7)]            # r1 comes back after it was released: the same name, a new request
+    runs = []
+    for graphs in (False, True):
+        runner = build_runner(model_dirs[name], dtype, "cuda:0", page, 120, 4)
+        if graphs:
+            runner.enable_decode_graphs(4, 400)
+        rows, live, taken = [], [], {r: 0 for r in prompts}
+        for members, steps in plan:
+            for r in [r for r in live if r not in members]:
+                runner.release(r)
+                taken[r] = 0
+            for r in [r for r in members if r not in live]:
+                rows.append(runner.step([StepEntry(r, prompts[r], (len(prompts[r]) - 1,))]))
+            live = members
+            for _ in range(steps):
+                tokens = [forced[r][taken[r]] for r in live]
+                for r in live:
+                    taken[r] += 1
+                rows.append(runner.step([StepEntry(r, [t], (0,)) for r, t in zip(live, tokens)]))
+        runs.append(rows)
+        if graphs:
+            assert runner.graph_replays == sum(steps for _, steps in plan)
+    for eager, replayed in zip(*runs):
+        assert eager.shape == replayed.shape
+        if dtype == torch.float32:
+            assert torch.equal(eager, replayed)
+        else:
+            torch.testing.assert_close(eager.float(), replayed.float(), rtol=2 ** -6, atol=2 ** -6)
