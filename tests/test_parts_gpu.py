@@ -403,3 +403,77 @@ def test_prenorm_block_alone(dtype):
     cache = CacheManager([layer.cache_needs()], (ScheduleEntry(0),), 8, 16, 2, dtype, DEV)
     hidden, pending = layer.block.forward(x.clone(), delta, _context_for(cache, [("a", 40)]), cache.layer_caches()[0])
     torch.testing.assert_close((hidden.float() + pending.float()), want, **_tol(dtype))
+
+
+@dataclass(frozen=True)
+class WindowConfig:
+    vocab_size: int
+    window: int
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw["vocab_size"], raw["window"])
+
+    def to_dict(self):
+        return {"architectures": ["ToyWindowLM"], "vocab_size": self.vocab_size, "window": self.window}
+
+
+def window_spec(cfg: WindowConfig):
+    """Two attention layers of head size 64, one behind a window, nothing that works on the host: the decode
+    steps of this model run the tensor-core kernels and replay from graphs."""
+    from liteinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    h = 128
+    norm = PartSpec("rmsnorm", {"size": h, "eps": 1e-5})
+    ffn = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": 192, "activation": "silu"})
+
+    def layer(i, window):
+        mixer = PartSpec("attention", {"hidden_size": h, "heads": 4, "kv_heads": 2, "head_dim": 64, "window": window,
+                                       "position": PartSpec("rotary", {"head_dim": 64, "theta": 10000.0})})
+        return LayerSpec("prenorm_residual",
+                         {"mixer_norm": norm, "mixer": mixer, "feed_forward_norm": norm, "feed_forward": ffn},
+                         {"mixer_norm": f"l{i}.n1.", "mixer": f"l{i}.mixer.", "feed_forward_norm": f"l{i}.n2.",
+                          "feed_forward": f"l{i}.ffn."})
+
+    sizes = {"vocab_size": cfg.vocab_size, "hidden_size": h}
+    return ModelSpec(cfg.vocab_size, h, PartSpec("token_embedding", sizes), "emb.", (layer(0, cfg.window), layer(1, None)),
+                     (ScheduleEntry(0), ScheduleEntry(1)), norm, "final.", PartSpec("linear", sizes), "head.",
+                     tied={"head.weight": "emb.weight"})
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_window_pages_come_back_under_graphs(tmp_path, dtype):
+    """Long decoding behind a window, replayed from graphs: the window's pages are given back as it moves (the
+    staged block tables must follow), and every token's logits equal those of the same tokens fed whole."""
+    from liteinfer_b200.config.registry import register_architecture
+    from liteinfer_b200.engine.loading import build_runner
+    from liteinfer_b200.engine.runner import StepEntry
+    from liteinfer_b200.weights.random_init import write_random_model
+
+    register_architecture("ToyWindowLM", WindowConfig, window_spec, replace=True)
+    cfg = WindowConfig(vocab_size=300, window=40)
+    folder = write_random_model(cfg.to_dict(), tmp_path / "window", seed=5)
+    tokens = {"a": tiny_configs.prompt(300, 230, 1), "b": tiny_configs.prompt(300, 150, 2)}
+    heads = {"a": 70, "b": 3}
+
+    whole = build_runner(folder, dtype, DEV, 16, 40, 2)
+    want = {r: whole.step([StepEntry(r, t, tuple(range(len(t))))]) for r, t in tokens.items()}
+
+    runner = build_runner(folder, dtype, DEV, 16, 40, 2)
+    runner.enable_decode_graphs(2, 256)
+    got = {r: [runner.step([StepEntry(r, tokens[r][:heads[r]], (heads[r] - 1,))])] for r in tokens}
+    for step in range(147):                       # b ends with this loop, a goes on alone in a narrower graph
+        live = [r for r in tokens if heads[r] + step < len(tokens[r])]
+        rows = runner.step([StepEntry(r, [tokens[r][heads[r] + step]], (0,)) for r in live])
+        for i, r in enumerate(live):
+            got[r].append(rows[i:i + 1])
+    assert runner.graph_replays == 147
+    windowed = next(g for g in runner.cache.groups if g.need.window == 40)
+    assert windowed.allocator.num_held <= 2 * 4                  # what the window has passed came back
+    for r in tokens:
+        have = torch.cat(got[r]).float()
+        ref = want[r][heads[r] - 1:heads[r] - 1 + have.shape[0]].float()
+        if dtype == torch.float32:
+            torch.testing.assert_close(have, ref, rtol=1e-4, atol=1e-5)
+        else:
+            torch.testing.assert_close(have, ref, rtol=2 ** -5, atol=2 ** -5)
