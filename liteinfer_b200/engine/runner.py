@@ -167,13 +167,13 @@ class _DecodeGraph:
         """Called with the buffers holding a real batch: one eager pass on a side stream, then the capture."""
         stream = torch.cuda.Stream(device=runner.device)
         stream.wait_stream(torch.cuda.current_stream(runner.device))
-        with torch.cuda.stream(stream):
+        with torch.cuda.stream(stream), kernels.on_current_stream():
             runner.model.forward(self.ctx, runner.layer_caches)
         torch.cuda.current_stream(runner.device).wait_stream(stream)
         torch.cuda.synchronize(runner.device)
         before = kernels.launch_count
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, pool=runner.graph_pool):
+        with torch.cuda.graph(self.graph, pool=runner.graph_pool), kernels.on_current_stream():
             self.logits = runner.model.forward(self.ctx, runner.layer_caches)
         self.launches = kernels.launch_count - before
 
@@ -277,7 +277,9 @@ class ModelRunner:
             if graph is not None:
                 logits = self._replay(graph, entries)
             else:
-                logits = self.model.forward(self.build_context(entries), self.layer_caches)
+                context = self.build_context(entries)
+                with kernels.on_current_stream():
+                    logits = self.model.forward(context, self.layer_caches)
         except BaseException:
             self.cache.rollback(ids)
             raise
