@@ -8,6 +8,8 @@ its `EngineConfig` fields (liteinfer/config.py:13-67) and `SamplingParams` field
     generate        generate from prompts (text, or token ids for a model without a tokenizer)
     random-weights  write a model folder (config.json, model.safetensors) from a config and a seed
     replay          trace replay (the same program as bin/trace_run)
+    bench run       throughput and latency on synthetic requests, with the option names and the summaries of the
+                    reference's `bench dataset` / `bench run` (benchmarks/cli.py:209-265)
     build           compile every CUDA library now
 """
 
@@ -98,6 +100,18 @@ def main(argv=None) -> int:
     rnd.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
 
     sub.add_parser("replay", help="trace replay; arguments as bin/trace_run", add_help=False)
+    bench = sub.add_parser("bench", help="benchmarks in the reference's manner")
+    bench_sub = bench.add_subparsers(dest="bench_command", required=True)
+    run = bench_sub.add_parser("run", help="make the synthetic dataset and run it")
+    run.add_argument("--model", required=True)
+    run.add_argument("--isl", required=True, help="tokens per prompt, or 'mixed'")
+    run.add_argument("--osl", type=int, required=True, help="tokens generated per request (forced)")
+    run.add_argument("--max-isl", type=int, default=2048, help="longest prompt of a mixed dataset")
+    run.add_argument("-n", "--num-samples", type=int, default=200)
+    run.add_argument("--mode", choices=["throughput", "latency", "both"], default="both")
+    run.add_argument("--results-dir", default=None, help="also write the result as a JSON file here")
+    run.add_argument("--dataset-seed", type=int, default=0)
+    _add_engine_options(run)
     sub.add_parser("build", help="compile every CUDA library")
 
     argv = list(sys.argv[1:] if argv is None else argv)
@@ -109,6 +123,9 @@ def main(argv=None) -> int:
         return _generate(args)
     if args.command == "random-weights":
         return _random_weights(args)
+    if args.command == "bench":
+        from liteinfer_b200.benchmark import main as bench_main
+        return bench_main(args)
     if args.command == "build":
         from liteinfer_b200.ops import build_all
         for path in build_all():

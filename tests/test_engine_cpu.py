@@ -212,3 +212,25 @@ def test_sample_rule_properties():
     draws = {sample_row(logits, 1.0, 0, float(probs[1]) - 1e-3, u / 50) for u in range(50)}
     assert draws == {1}
     assert sample_row(logits, 0.0, 0, 1.0, 0.5) == 1                   # temperature 0: the first arg-max
+
+
+def test_bench_run_reports_the_references_summaries(cpu_kernels, model_dirs, capsys):
+    """`bench run` on a CPU with the stand-in kernels: forced output lengths, the two modes' fields."""
+    import json
+
+    from liteinfer_b200.benchmark import make_prompts, percentile
+    from liteinfer_b200.cli import main
+
+    assert percentile([1.0, 2.0, 3.0, 4.0], 50) == 2.5 and percentile([5.0], 99) == 5.0
+    mixed = make_prompts(100, None, 200, 64, 0)
+    assert all(1 <= len(p) <= 64 for p in mixed) and len({len(p) for p in mixed}) > 10
+    assert make_prompts(100, 7, 3, 64, 0) == make_prompts(100, 7, 3, 64, 0)
+    code = main(["bench", "run", "--model", str(model_dirs["tiny_a"]), "--isl", "9", "--osl", "4", "-n", "5",
+                 "--dtype", "float32", "--device", "cpu", "--max-num-seqs", "2", "--max-model-len", "32"])
+    assert code == 0
+    result = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert result["dataset"]["num_samples"] == 5 and result["dataset"]["input_tokens"] == 45
+    assert set(result["summary"]["throughput"]) == {"output_tokens_per_s", "requests_per_s", "wall_time_s", "step_phases"}
+    assert set(result["summary"]["latency"]) == {"ttft_p50_ms", "ttft_p95_ms", "ttft_p99_ms", "itl_p50_ms",
+                                                 "itl_p95_ms", "itl_p99_ms", "e2e_p50_ms"}
+    assert result["summary"]["throughput"]["output_tokens_per_s"] > 0
