@@ -29,7 +29,7 @@ namespace li {
 template <int NT, int kWarps = kSkinnyWarps>
 int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
   const dim3 grid((p.N + 15) / 16, p.num_slices);
-  return (int)launch_maybe_early(pdl_mode() >= 1 && p.M <= kEarlyLaunchRows, gemm_skinny_kernel<NT, kWarps>, grid, dim3(kWarps * 32), 0, s, p);
+  return (int)launch_maybe_early(pdl_mode() >= 1, gemm_skinny_kernel<NT, kWarps>, grid, dim3(kWarps * 32), 0, s, p);
 }
 
 }  // namespace li
