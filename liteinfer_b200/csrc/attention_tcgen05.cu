@@ -147,6 +147,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  grid_dependency_wait();   // q and the newest keys and values come from the kernel before; what is above waits for nobody
   // Q: each softmax thread copies its row (128 bytes) into the swizzled tile; rows of padding are zero.
   if (warp >= 2) {
     const int row = (warp & 3) * 32 + lane;
@@ -427,8 +428,7 @@ static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, con
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_tcgen05_kernel<D><<<grid, kAttnThreads, smem, stream>>>(mk, mv, p);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(0, attention_tcgen05_kernel<D>, grid, dim3(kAttnThreads), smem, stream, mk, mv, p);
 }
 
 }  // namespace li

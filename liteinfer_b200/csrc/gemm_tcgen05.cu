@@ -465,13 +465,15 @@ static int launch_gemm_pair(const CUtensorMap& mx, const CUtensorMap& mw, const 
   config.blockDim = dim3(kPairThreads);
   config.dynamicSmemBytes = smem;
   config.stream = s;
-  cudaLaunchAttribute attribute[1];
+  cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeClusterDimension;
   attribute[0].val.clusterDim.x = 2;
   attribute[0].val.clusterDim.y = 1;
   attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // barriers and tensor memory are set up early
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = 1;
+  config.numAttrs = pdl_enabled(0) ? 2 : 1;
   return (int)cudaLaunchKernelEx(&config, gemm_tcgen05_pair_kernel<STAGES>, mx, mw, p);
 }
 
