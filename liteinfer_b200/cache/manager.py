@@ -163,6 +163,11 @@ class CacheManager:
         """
         if len(set(request_ids)) != len(request_ids):
             raise ValueError("a request appears twice in one reservation")
+        # The common decode step: every request is known and grows by tokens that still fit its last page.
+        page = self.page_size
+        lengths = self._length
+        if all(r in lengths and 0 < total - lengths[r] <= -lengths[r] % page for r, total in zip(request_ids, new_totals, strict=True)):
+            return
         for request_id, total in zip(request_ids, new_totals, strict=True):
             if total < self.length(request_id):
                 raise ValueError(f"{request_id} holds {self.length(request_id)} tokens and cannot shrink to {total}")
