@@ -300,6 +300,20 @@ def test_gemm_skinny_rows_do_not_depend_on_the_batch():
         assert torch.equal(part, full[:rows])
 
 
+def test_linear_hands_narrow_batches_to_the_streaming_kernel():
+    """Up to 8 rows of x always, up to 16 for weights of few rows: `linear` then gives what the kernel gives."""
+    from liteinfer_b200 import ops
+
+    for M, N, streams in ((8, 8192, True), (12, 2048, True), (16, 4096, True), (17, 2048, False), (12, 8192, False)):
+        x, w = _randn(M, 512, dtype=torch.bfloat16), _randn(N, 512, dtype=torch.bfloat16, seed=1, scale=0.05)
+        before = ops.kernels.launch_count
+        out = ops.linear(x, w, torch.empty(M, N, dtype=torch.bfloat16, device="cuda"))
+        assert (ops.kernels.launch_count > before) == streams     # library products are not counted
+        torch.testing.assert_close(out.double(), x.double() @ w.double().t(), rtol=2 ** -7, atol=2 ** -7)
+        if streams:
+            assert torch.equal(out, ops.gemm_skinny(x, w, torch.empty(M, N, dtype=torch.bfloat16, device="cuda")))
+
+
 def test_gemm_skinny_refuses_what_it_cannot_do():
     from liteinfer_b200 import ops
     from liteinfer_b200.ops import KernelLibraryError
