@@ -147,6 +147,39 @@ class ScalePositions:
         k.mul_(scale)
 
 
+class RoutedFeedForward:
+    """A feed-forward with routing: every token goes through its `top_k` best of `experts` small two-layer
+    networks, weighted by the router's renormalised probabilities.  The router's weight stays 32-bit."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top_k: int, dtype, device):
+        self.h, self.i, self.experts, self.top_k = hidden_size, intermediate_size, experts, top_k
+        self.router = self.up = self.down = None
+
+    def tensor_specs(self):
+        from liteinfer_b200.parts.spec import TensorSpec
+        specs = {"router.weight": TensorSpec((self.experts, self.h), kind="f32")}
+        for e in range(self.experts):
+            specs[f"experts.{e}.up.weight"] = TensorSpec((self.i, self.h))
+            specs[f"experts.{e}.down.weight"] = TensorSpec((self.h, self.i))
+        return specs
+
+    def bind(self, tensors):
+        self.router = tensors["router.weight"]
+        assert self.router.dtype == torch.float32
+        self.up = [tensors[f"experts.{e}.up.weight"] for e in range(self.experts)]
+        self.down = [tensors[f"experts.{e}.down.weight"] for e in range(self.experts)]
+
+    def forward(self, x, ctx):
+        probs = torch.softmax(x.float() @ self.router.t(), dim=-1)
+        best, chosen = probs.topk(self.top_k, dim=-1)
+        gate = torch.zeros_like(probs).scatter_(1, chosen, best / best.sum(-1, keepdim=True))
+        out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+        for e in range(self.experts):
+            hidden = torch.relu(x.float() @ self.up[e].float().t())
+            out += gate[:, e:e + 1] * (hidden @ self.down[e].float().t())
+        return out.to(x.dtype)
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     vocab_size: int
@@ -169,17 +202,18 @@ def toy_spec(cfg: ToyConfig):
     norm = PartSpec("rmsnorm", {"size": h, "eps": 1e-5})
     ffn = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": 2 * h, "activation": "silu"})
 
-    def layer(i, mixer):
+    def layer(i, mixer, feed_forward=ffn):
         return LayerSpec("prenorm_residual",
-                         {"mixer_norm": norm, "mixer": mixer, "feed_forward_norm": norm, "feed_forward": ffn},
+                         {"mixer_norm": norm, "mixer": mixer, "feed_forward_norm": norm, "feed_forward": feed_forward},
                          {"mixer_norm": f"l{i}.n1.", "mixer": f"l{i}.mixer.", "feed_forward_norm": f"l{i}.n2.",
                           "feed_forward": f"l{i}.ffn."})
 
     attention = lambda position, window=None: PartSpec("attention", {
         "hidden_size": h, "heads": 4, "kv_heads": 2, "head_dim": 16, "position": position, "window": window})
+    routed = PartSpec("toy_routed", {"hidden_size": h, "intermediate_size": 24, "experts": 3, "top_k": 2})
     layers = (
         layer(0, PartSpec("toy_ema", {"hidden_size": h, "decay": 0.5})),                      # a state of its own
-        layer(1, attention(PartSpec("toy_scale_positions", {}), cfg.window)),                 # a window, odd positions
+        layer(1, attention(PartSpec("toy_scale_positions", {}), cfg.window), routed),         # a window, odd positions, routing
         layer(2, attention(PartSpec("rotary", {"head_dim": 16, "theta": 100.0, "rotary_dim": 8}))),   # partial rotary
     )
     sizes = {"vocab_size": cfg.vocab_size, "hidden_size": h}
@@ -213,9 +247,22 @@ def _plain_toy(weights, cfg: ToyConfig, tokens):
         o = plain_llama.causal_attention(q, k, v, 16 ** -0.5, window)
         return o.reshape(T, 64) @ w[p + "o_proj.weight"].t(), (k, v)
 
+    def routed(h, f):
+        probs = torch.softmax(h @ w[f + "router.weight"].t(), dim=-1)
+        out = torch.zeros_like(h)
+        for t in range(T):
+            best = sorted(range(3), key=lambda e: -float(probs[t, e]))[:2]
+            total = sum(probs[t, e] for e in best)
+            for e in best:
+                hidden = torch.relu(w[f + f"experts.{e}.up.weight"] @ h[t])
+                out[t] += probs[t, e] / total * (w[f + f"experts.{e}.down.weight"] @ hidden)
+        return out
+
     def block(x, i, mix):
         x = x + mix(plain_llama.rms_norm(x, w[f"l{i}.n1.weight"], 1e-5))
         f = f"l{i}.ffn."
+        if f + "router.weight" in w:
+            return x + routed(plain_llama.rms_norm(x, w[f"l{i}.n2.weight"], 1e-5), f)
         return x + plain_llama.gated_mlp(plain_llama.rms_norm(x, w[f"l{i}.n2.weight"], 1e-5), w[f + "gate_proj.weight"],
                                          w[f + "up_proj.weight"], w[f + "down_proj.weight"], "silu")
 
@@ -242,10 +289,11 @@ def _plain_toy(weights, cfg: ToyConfig, tokens):
 @pytest.fixture(scope="module")
 def toy_model(tmp_path_factory):
     from liteinfer_b200.config.registry import register_architecture
-    from liteinfer_b200.parts.registry import register_mixer, register_position_encoding
+    from liteinfer_b200.parts.registry import register_feed_forward, register_mixer, register_position_encoding
     from liteinfer_b200.weights.random_init import write_random_model
 
     register_mixer("toy_ema", EmaMixer, replace=True)
+    register_feed_forward("toy_routed", RoutedFeedForward, replace=True)
     register_position_encoding("toy_scale_positions", ScalePositions, replace=True)
     register_architecture("ToyStateLM", ToyConfig, toy_spec, replace=True)
     cfg = ToyConfig(vocab_size=211, hidden_size=64, window=9)
