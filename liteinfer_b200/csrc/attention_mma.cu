@@ -73,6 +73,7 @@ attention_mma_kernel(const AttnParams p) {
 
   // Tables and lengths are inputs of the step; what an earlier kernel wrote is read after the wait below.
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
+  if (seq < 0) return;        // a place of padding in the list of sequences
   const int kvh = blockIdx.y;
   const int split = blockIdx.x % p.num_splits, qtile = blockIdx.x / p.num_splits;
   const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;

@@ -72,6 +72,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   __shared__ int slot_filled[kWarps * kMaxRing];           // whether the slot's current group was fetched at all
 
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
+  if (seq < 0) return;        // a place of padding in the list of sequences
   const int kvh = blockIdx.y, split = blockIdx.x;
   const int q_begin = p.query_start_loc[seq];
   const int groups = p.heads / p.kv_heads;

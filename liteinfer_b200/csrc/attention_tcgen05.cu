@@ -112,6 +112,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
+  if (seq < 0) return;        // a place of padding in the list of sequences
   const int kvh = blockIdx.y;
   const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
   const int groups = p.heads / p.kv_heads;

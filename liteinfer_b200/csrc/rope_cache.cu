@@ -36,7 +36,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     sinv[i] = sinf(angle);
   }
   const int seq = seq_of_token[t];
-  const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+  const int page = seq < 0 ? -1 : block_table[(size_t)seq * table_stride + pos / page_size];   // a row of padding belongs to no sequence
   grid_dependency_wait();           // q, k and v come from the projection before this kernel
   __syncthreads();
 
@@ -96,7 +96,7 @@ __global__ void rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const int* __re
     sinv[i] = sinf(angle);
   }
   const int seq = seq_of_token[t];
-  const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+  const int page = seq < 0 ? -1 : block_table[(size_t)seq * table_stride + pos / page_size];   // a row of padding belongs to no sequence
   grid_dependency_wait();
   __syncthreads();
 

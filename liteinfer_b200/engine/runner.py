@@ -16,7 +16,12 @@ A step that holds only single decoded tokens, each wanting its logits, can be
 replayed from a CUDA graph (one graph per batch width, captured on first use,
 as liteinfer/engine/cuda_graphs.py:105-260 does): the batch is then written
 into buffers of fixed size and place, and the kernels read their bounds from
-those buffers.
+those buffers.  Every other step of moderate size (portions of prompts, alone
+or beside decoded tokens) is replayed from a graph too, one per padded shape:
+the step's tokens, sequences and wanted rows are rounded up to the next size of
+a ladder, the places of padding belong to no sequence (kernels skip them), and
+only the real rows are returned.  A step launched kernel by kernel costs the
+host a few milliseconds, more than the device needs for a short prompt.
 """
 
 from __future__ import annotations
@@ -178,6 +183,71 @@ class _DecodeGraph:
         self.launches = kernels.launch_count - before
 
 
+def _token_bucket(n: int) -> int:
+    """The padded number of tokens of a step: steps of 16 up to 128, then of an eighth of the next power of two."""
+    for limit, step in ((128, 16), (256, 32), (512, 64), (1024, 128), (2048, 256)):
+        if n <= limit:
+            return -(-n // step) * step
+    return -(-n // 512) * 512
+
+
+def _pow2(n: int) -> int:
+    return 1 if n <= 1 else 1 << (n - 1).bit_length()
+
+
+class _PaddedGraph:
+    """One captured forward for any step that fits a padded shape: up to `tokens` tokens in up to `seqs` sequences,
+    of which up to `prefill` bring more than one token, with up to `rows` wanted rows."""
+
+    def __init__(self, runner: ModelRunner, tokens: int, seqs: int, decode: bool, prefill: int, rows: int,
+                 max_model_len: int) -> None:
+        cache = runner.cache
+        pages = -(-max_model_len // cache.page_size)
+        n_decode = seqs if decode else 0
+        self.batch = batch = _Batch(seqs, tokens, rows, [pages] * len(cache.groups), n_decode, prefill)
+        self.device_buffer = torch.zeros(batch.total, dtype=torch.int32, device=runner.device)
+        tok, pos, seq, qsl, ctxl, slots, wanted, dseq, dtok, pseq, *tables = batch.views(self.device_buffer)
+        tables = [t.view(seqs, w) for t, w in zip(tables, batch.widths)]
+        # The kernels' launch bounds are those of the padded shape; what a step really holds is in the buffers.
+        plan = AttentionPlan(num_decode=n_decode, decode_seqs=dseq, decode_tokens=dtok, num_prefill=prefill,
+                             prefill_seqs=pseq, max_prefill_query_len=tokens if prefill else 0,
+                             max_decode_context_len=max_model_len)
+        self.ctx = StepContext(
+            num_tokens=tokens, num_seqs=seqs, token_ids=tok, positions=pos, seq_of_token=seq, query_start_loc=qsl,
+            context_lens=ctxl, block_tables=tables, state_slots=slots, logit_rows=wanted, num_logit_rows=rows,
+            max_query_len=tokens if prefill else 1, max_context_len=max_model_len,
+            decode_splits=runner.decode_splits, plan=plan)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.launches = 0
+        self.host = torch.zeros(batch.total, dtype=torch.int32, pin_memory=True)
+        self.views = batch.views(self.host.numpy())
+        self.copied = torch.cuda.Event()
+
+    def stage(self, entries: list[StepEntry], cache: CacheManager, starts: list[int]) -> int:
+        """Writes this step's batch and the padding around it into the pinned buffer; returns the wanted rows."""
+        self.copied.synchronize()
+        _fill(self.batch, self.host.numpy(), entries, cache, starts)
+        tok, pos, seq, qsl, ctxl, slots, wanted, dseq, dtok, pseq, *_ = self.views
+        B = len(entries)
+        T = int(qsl[B])
+        R = sum(len(e.want) for e in entries)
+        n_decode = sum(1 for e in entries if len(e.tokens) == 1)
+        tok[T:] = 0
+        pos[T:] = 0
+        seq[T:] = -1            # a token of padding belongs to no sequence: nothing is stored for it
+        qsl[B + 1:] = T         # a sequence of padding brings no token
+        ctxl[B:] = 0
+        slots[B:] = 0
+        wanted[R:] = 0
+        dseq[n_decode:] = -1    # the attention launches skip these places
+        dtok[n_decode:] = 0
+        pseq[B - n_decode:] = -1
+        return R
+
+    capture = _DecodeGraph.capture
+
+
 class ModelRunner:
     def __init__(self, model: Model, cache: CacheManager, decode_splits: int | None = None) -> None:
         self.model, self.cache = model, cache
@@ -187,7 +257,9 @@ class ModelRunner:
         self._pinned = self.device.type == "cuda"
         self.num_steps = 0
         self._graphs: dict[int, _DecodeGraph] = {}
+        self._padded_graphs: dict[tuple, _PaddedGraph] = {}
         self._graph_limits: tuple[int, int] | None = None
+        self._padded_limit = 0      # most tokens of a step that is replayed from a padded graph
         self.graph_pool = None
         self.graph_launches = 0     # launches of this package's kernels replayed from graphs
         self.graph_replays = 0
@@ -228,13 +300,16 @@ class ModelRunner:
         return _context(batch, dev, self.device, counts, totals, self.decode_splits, decode_bound)
 
     # --------------------------------------------------------------- graphs
-    def enable_decode_graphs(self, max_num_seqs: int, max_model_len: int) -> None:
-        """Replay steps that hold single decoded tokens only from CUDA graphs."""
+    def enable_decode_graphs(self, max_num_seqs: int, max_model_len: int, max_padded_tokens: int = 2048) -> None:
+        """Replay steps from CUDA graphs: steps of single decoded tokens from a graph of their exact width, other
+        steps of at most `max_padded_tokens` tokens from a graph of their padded shape (0: those run kernel by
+        kernel; larger steps always do, their time on the device dwarfs the host's)."""
         if self.device.type != "cuda":
             raise ValueError("CUDA graphs need a CUDA device")
         if not self.model.graph_safe:
             return          # a part works on the host inside forward: every step launches kernel by kernel
         self._graph_limits = (max_num_seqs, max_model_len)
+        self._padded_limit = max_padded_tokens
         self.graph_pool = torch.cuda.graph_pool_handle()
 
     def _graph_for(self, entries: list[StepEntry], totals: list[int]) -> _DecodeGraph | None:
@@ -253,9 +328,29 @@ class ModelRunner:
             graph = self._graphs[width] = _DecodeGraph(self, width, max_len)
         return graph
 
-    def _replay(self, graph: _DecodeGraph, entries: list[StepEntry]) -> torch.Tensor:
+    def _padded_graph_for(self, entries: list[StepEntry], totals: list[int]) -> _PaddedGraph | None:
+        if self._graph_limits is None or not self._padded_limit:
+            return None
+        max_seqs, max_len = self._graph_limits
+        tokens = sum(len(e.tokens) for e in entries)
+        if len(entries) > max_seqs or max(totals) > max_len or tokens > self._padded_limit:
+            return None
+        seqs = min(_pow2(len(entries)), max(max_seqs, 1))
+        n_decode = sum(1 for e in entries if len(e.tokens) == 1)
+        prefill = min(_pow2(len(entries) - n_decode), seqs) if n_decode < len(entries) else 0
+        wanted = sum(len(e.want) for e in entries)
+        rows = seqs if wanted <= seqs else _token_bucket(wanted)
+        key = (_token_bucket(tokens), seqs, n_decode > 0, prefill, rows)
+        graph = self._padded_graphs.get(key)
+        if graph is None:
+            if len(self._graphs) + len(self._padded_graphs) >= _MAX_GRAPHS:
+                return None
+            graph = self._padded_graphs[key] = _PaddedGraph(self, *key, max_len)
+        return graph
+
+    def _replay(self, graph: _DecodeGraph | _PaddedGraph, entries: list[StepEntry]) -> torch.Tensor:
         starts = [self.cache.length(e.request_id) for e in entries]
-        graph.stage(entries, self.cache, starts)
+        wanted = graph.stage(entries, self.cache, starts)
         graph.device_buffer.copy_(graph.host, non_blocking=True)
         graph.copied.record()
         if graph.graph is None:
@@ -263,7 +358,7 @@ class ModelRunner:
         graph.graph.replay()
         self.graph_launches += graph.launches
         self.graph_replays += 1
-        return graph.logits.clone()
+        return graph.logits.clone() if wanted is None else graph.logits[:wanted].clone()
 
     # ----------------------------------------------------------------- step
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
@@ -273,7 +368,7 @@ class ModelRunner:
         totals = [self.cache.length(e.request_id) + len(e.tokens) for e in entries]
         self.cache.reserve(ids, totals)   # raises before anything changes
         try:
-            graph = self._graph_for(entries, totals)
+            graph = self._graph_for(entries, totals) or self._padded_graph_for(entries, totals)
             if graph is not None:
                 logits = self._replay(graph, entries)
             else:

@@ -39,6 +39,9 @@ def _parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
     parser.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
     parser.add_argument("--device", default="cuda:0")
+    parser.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false",
+                        help="launch every step kernel by kernel (by default steps are replayed from CUDA graphs, "
+                             "as the engine does when it serves)")
     return parser.parse_args(argv)
 
 
@@ -61,6 +64,8 @@ def main(argv=None) -> int:
     print(f"[trace_run] loading {args.model} ({args.dtype}); cache of {num_pages} pages x {args.page_size} tokens",
           file=sys.stderr, flush=True)
     runner = build_runner(args.model, dtype, args.device, args.page_size, num_pages, args.max_requests)
+    if args.cuda_graphs and args.device.startswith("cuda"):
+        runner.enable_decode_graphs(args.max_requests, num_pages * args.page_size)
 
     for line in sys.stdin:
         line = line.strip()

@@ -33,7 +33,7 @@ def test_graph_replay_equals_eager(model_dirs, name, dtype):
             rows.append(runner.step([StepEntry(r, [t], (0,)) for r, t in zip(live, tokens)]))
         runs.append(rows)
         if graphs:
-            assert runner.graph_replays == 20 and len(runner._graphs) == 2
+            assert runner.graph_replays == 21 and len(runner._graphs) == 2 and len(runner._padded_graphs) == 1   # the prompts too
     for eager, replayed in zip(*runs):
         assert eager.shape == replayed.shape
         if name == "tiny_d":
@@ -77,7 +77,7 @@ def test_graph_rows_follow_the_requests(model_dirs, name, dtype):
                 rows.append(runner.step([StepEntry(r, [t], (0,)) for r, t in zip(live, tokens)]))
         runs.append(rows)
         if graphs:
-            assert runner.graph_replays == sum(steps for _, steps in plan)
+            assert runner.graph_replays == sum(steps for _, steps in plan) + 6     # and the six prompts, padded
     for eager, replayed in zip(*runs):
         assert eager.shape == replayed.shape
         if dtype == torch.float32:

@@ -515,7 +515,7 @@ def test_window_pages_come_back_under_graphs(tmp_path, dtype):
         rows = runner.step([StepEntry(r, [tokens[r][heads[r] + step]], (0,)) for r in live])
         for i, r in enumerate(live):
             got[r].append(rows[i:i + 1])
-    assert runner.graph_replays == 147
+    assert runner.graph_replays == 147 + 2          # the two prompts went through padded graphs
     windowed = next(g for g in runner.cache.groups if g.need.window == 40)
     assert windowed.allocator.num_held <= 2 * 4                  # what the window has passed came back
     for r in tokens:
