@@ -84,3 +84,56 @@ def test_graph_rows_follow_the_requests(model_dirs, name, dtype):
             assert torch.equal(eager, replayed)
         else:
             torch.testing.assert_close(eager.float(), replayed.float(), rtol=2 ** -6, atol=2 ** -6)
+
+
+@pytest.mark.parametrize("name,dtype", [("tiny_b", torch.float32), ("tiny_a", torch.float32), ("tiny_d", torch.bfloat16)])
+def test_padded_graphs_equal_eager_over_random_steps(model_dirs, name, dtype):
+    """Steps of every kind (portions of prompts down to two tokens, alone or beside single tokens, logits wanted
+    anywhere, nowhere, or at more places than there are sequences) replayed from graphs of padded shapes against
+    the same steps launched kernel by kernel.  Shapes repeat with other real sizes inside them, so a graph's buffers
+    hold what a larger step left there; requests end and their pages are used again."""
+    import random
+
+    from liteinfer_b200.engine.loading import build_runner
+    from liteinfer_b200.engine.runner import StepEntry
+
+    config, _, page = tiny_configs.ALL[name]
+    vocab = config["vocab_size"]
+    rng = random.Random(11)
+    eager = build_runner(model_dirs[name], dtype, "cuda:0", page, 64, 4)
+    replayed = build_runner(model_dirs[name], dtype, "cuda:0", page, 64, 4)
+    replayed.enable_decode_graphs(4, 64 * page)
+    live: dict[str, int] = {}              # request -> tokens it still owes before it ends
+    born = 0
+    worst = 0.0
+    for step in range(120):
+        while len(live) < 4 and (not live or rng.random() < 0.4):
+            live[f"q{born}"] = rng.randint(3, 90)
+            born += 1
+        entries = []
+        for request, owed in list(live.items()):
+            if rng.random() < 0.15:
+                continue                                    # sits this step out
+            n = 1 if rng.random() < 0.5 else rng.randint(2, min(owed, 40)) if owed >= 2 else 1
+            n = min(n, owed)
+            tokens = [rng.randrange(vocab) for _ in range(n)]
+            kind = rng.random()
+            want = () if kind < 0.2 else (n - 1,) if kind < 0.7 else tuple(sorted(rng.sample(range(n), rng.randint(1, n))))
+            entries.append(StepEntry(request, tokens, want))
+            live[request] = owed - n
+        if not entries:
+            continue
+        a, b = eager.step(entries), replayed.step(entries)
+        assert a.shape == b.shape
+        if dtype == torch.float32:
+            assert torch.equal(a, b), f"step {step}: {[(e.request_id, len(e.tokens), e.want) for e in entries]}"
+        elif a.numel():
+            worst = max(worst, float((a.float() - b.float()).abs().max()))
+        for request in [r for r, owed in live.items() if owed == 0]:
+            eager.release(request)
+            replayed.release(request)
+            del live[request]
+        replayed.cache.check_invariants()
+    assert worst <= 2 ** -6, worst
+    assert replayed.graph_replays >= 100 and 5 <= len(replayed._padded_graphs) <= 60
+    replayed.check_kernels()
