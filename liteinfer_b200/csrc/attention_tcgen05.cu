@@ -111,14 +111,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   unsigned char* generic_base = smem_raw + (base - smem_addr(smem_raw));   // the same place as a generic pointer
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
+  const int seq = p.seq_index ? p.seq_index[blockIdx.y] : blockIdx.y;
   if (seq < 0) return;        // a place of padding in the list of sequences
-  const int kvh = blockIdx.y;
+  const int kvh = blockIdx.x;
   const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
   const int groups = p.heads / p.kv_heads;
   const int tq = kRows / groups;
-  // The last query tiles see the most keys: they are handed out first, so that the long blocks do not end up alone.
-  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tq;
+  // The last query tiles see the most keys: they are handed out first, across all heads and sequences (the query
+  // tile is the slowest index of the grid), so that the long blocks do not end up alone at the end of the launch.
+  const int q0 = (int)(gridDim.z - 1 - blockIdx.z) * tq;
   if (q0 >= q_len) return;
   const int ctx = p.context_lens[seq];
   const int tile_q = min(tq, q_len - q0);
@@ -454,7 +455,7 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
                                          int* error_flag, cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (!li_paged_attention_tcgen05_supports(heads, kv_heads, head_dim, page_size)) return LI_ERR_UNSUPPORTED;
-  if (kv_heads > 65535 || num_seqs > 65535) return LI_ERR_UNSUPPORTED;
+  if (num_seqs > 65535 || (max_q_len + 0L) * heads / kv_heads / kRows >= 65535) return LI_ERR_UNSUPPORTED;
   if ((q_row_stride % 8) || (out_row_stride % 8) || !aligned16(q) || !aligned16(out) || !aligned16(k_pool) ||
       !aligned16(v_pool))
     return LI_ERR_ALIGNMENT;
@@ -469,6 +470,6 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
                  scale * kLog2eF, window, error_flag};
   const int groups = heads / kv_heads;
   const int tq = kRows / groups;
-  const dim3 grid((max_q_len + tq - 1) / tq, kv_heads, num_seqs);
+  const dim3 grid(kv_heads, num_seqs, (max_q_len + tq - 1) / tq);
   return head_dim == 64 ? launch_tc_attention<64>(mk, mv, p, grid, stream) : launch_tc_attention<128>(mk, mv, p, grid, stream);
 }
