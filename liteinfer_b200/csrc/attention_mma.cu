@@ -75,7 +75,8 @@ attention_mma_kernel(const AttnParams p) {
   const int seq = p.seq_index ? p.seq_index[blockIdx.z] : blockIdx.z;
   if (seq < 0) return;        // a place of padding in the list of sequences
   const int kvh = blockIdx.y;
-  const int split = blockIdx.x % p.num_splits, qtile = blockIdx.x / p.num_splits;
+  // The last query tiles see the most keys: they are handed out first.
+  const int split = blockIdx.x % p.num_splits, qtile = (int)(gridDim.x / p.num_splits) - 1 - (int)(blockIdx.x / p.num_splits);
   const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
   const int groups = p.heads / p.kv_heads;
   const int tq = (kDecode ? 16 : kBlockM) / groups;       // query tokens per tile
