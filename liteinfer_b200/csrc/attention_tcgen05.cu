@@ -99,11 +99,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   const unsigned k_smem = p_smem + 2 * kRowTileBytes;               // kKvStages
   const unsigned v_smem = k_smem + kKvStages * kTileBytes;          // kKvStages
   const unsigned bars = v_smem + kKvStages * kTileBytes;
-  auto k_full = [&](int s) { return bars + 8u * s; };
-  auto v_full = [&](int s) { return bars + 8u * (kKvStages + s); };
+  auto kv_full = [&](int s) { return bars + 8u * s; };                    // keys and values of a stage have landed
   auto kv_empty = [&](int s) { return bars + 8u * (2 * kKvStages + s); };
   auto s_full = [&](int b) { return bars + 8u * (3 * kKvStages + b); };
-  auto s_free = [&](int b) { return bars + 8u * (3 * kKvStages + 2 + b); };
   auto p_full = [&](int b) { return bars + 8u * (3 * kKvStages + 4 + b); };
   auto pv_done = [&](int b) { return bars + 8u * (3 * kKvStages + 6 + b); };
   const unsigned tmem_slot = bars + 8u * (3 * kKvStages + 8);
@@ -133,13 +131,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kKvStages; ++s) {
-      mbar_init(k_full(s), 1);
-      mbar_init(v_full(s), 1);
+      mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(s_full(b), 1);
-      mbar_init(s_free(b), 4);
       mbar_init(p_full(b), 4);
       mbar_init(pv_done(b), 1);
     }
@@ -186,32 +182,32 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 
   if (warp == 0) {
     // ------------------------------------------------------------------ loader
-    if (lane == 0) {
-      const int boxes = kKeys / p.page_size;
-      const unsigned box_bytes = (unsigned)p.page_size * 64 * 2;
-      for (int t = 0; t < ntiles; ++t) {
-        const int stage = t % kKvStages;
-        const unsigned phase = (unsigned)(t / kKvStages) & 1;
-        if (!mbar_wait(kv_empty(stage), phase ^ 1, p.error_flag, 11)) break;
-        const int key0 = (tile_lo + t) * kKeys;
-        int rows[4];
-        int valid = 0;
-        for (int b = 0; b < boxes; ++b) {
-          const int kpos = key0 + b * p.page_size;
-          int page = -1;
-          if (kpos < hi && kpos + p.page_size > lo) page = table[kpos >> p.page_shift];
-          rows[b] = (page >= 0 && page < p.num_pages) ? (page * p.kv_heads + kvh) * p.page_size : -1;
-          valid += rows[b] >= 0;
-        }
-        mbar_expect_tx(k_full(stage), valid * kSub * box_bytes);
-        mbar_expect_tx(v_full(stage), valid * kSub * box_bytes);
-        for (int b = 0; b < boxes; ++b) {
-          if (rows[b] < 0) continue;
+    // Lane b of the warp looks up page b of a tile and asks for its boxes (keys and values, per 64 dimensions),
+    // so that the lookups and the requests of a tile's pages run side by side.
+    const int boxes = kKeys / p.page_size;
+    const unsigned box_bytes = (unsigned)p.page_size * 64 * 2;
+    bool fine = true;
+    for (int t = 0; t < ntiles; ++t) {
+      const int stage = t % kKvStages;
+      const unsigned phase = (unsigned)(t / kKvStages) & 1;
+      const int kpos = (tile_lo + t) * kKeys + lane * p.page_size;
+      int row = -1;
+      if (lane < boxes && kpos < hi && kpos + p.page_size > lo) {
+        const int page = table[kpos >> p.page_shift];
+        if (page >= 0 && page < p.num_pages) row = (page * p.kv_heads + kvh) * p.page_size;
+      }
+      const int valid = __popc(__ballot_sync(0xffffffffu, row >= 0));
+      if (lane == 0) {
+        fine = mbar_wait(kv_empty(stage), phase ^ 1, p.error_flag, 11);
+        if (fine) mbar_expect_tx(kv_full(stage), 2 * valid * kSub * box_bytes);
+      }
+      fine = __shfl_sync(0xffffffffu, fine, 0);
+      if (!fine) break;
+      if (row >= 0) {
 #pragma unroll
-          for (int sub = 0; sub < kSub; ++sub) {
-            tma_load_2d(k_smem + stage * kTileBytes + sub * kKeySubBytes + b * box_bytes, &map_k, k_full(stage), sub * 64, rows[b]);
-            tma_load_2d(v_smem + stage * kTileBytes + sub * kKeySubBytes + b * box_bytes, &map_v, v_full(stage), sub * 64, rows[b]);
-          }
+        for (int sub = 0; sub < kSub; ++sub) {
+          tma_load_2d(k_smem + stage * kTileBytes + sub * kKeySubBytes + lane * box_bytes, &map_k, kv_full(stage), sub * 64, row);
+          tma_load_2d(v_smem + stage * kTileBytes + sub * kKeySubBytes + lane * box_bytes, &map_v, kv_full(stage), sub * 64, row);
         }
       }
     }
@@ -221,15 +217,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       // f32 accumulate, bf16 x bf16, M 128, N 64; for P V the second operand (values) is N-major.
       constexpr unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(kKeys >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
       constexpr unsigned idesc_pv = idesc_qk | (1u << 16);
+      // A descriptor's low bits are its address in units of 16 bytes, so the descriptor of a place further on in
+      // shared memory is the first one plus the distance: one addition per product instead of the whole encoding.
+      const unsigned long long desc_q = umma_desc(q_smem), desc_k = umma_desc(k_smem), desc_v = umma_desc(v_smem),
+                               desc_p = umma_desc(p_smem);
+      // S of tile t may overwrite its buffer: the softmax threads read tile t-2 out of it before they announced its
+      // probabilities, and that announcement was waited for before P V of tile t-2 was issued.
       auto issue_qk = [&](int t) -> bool {
         const int stage = t % kKvStages, buf = t & 1;
-        if (t >= 2 && !mbar_wait(s_free(buf), (unsigned)((t - 2) >> 1) & 1, p.error_flag, 12)) return false;
-        if (!mbar_wait(k_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 13)) return false;
+        if (!mbar_wait(kv_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 13)) return false;
         tcgen05_fence_after();
+        const unsigned long long dk = desc_k + (unsigned long long)((stage * kTileBytes) >> 4);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_bf16(tmem_s[buf], umma_desc(q_smem + (k / 4) * kRowSubBytes + (k % 4) * 32),
-                    umma_desc(k_smem + stage * kTileBytes + (k / 4) * kKeySubBytes + (k % 4) * 32), idesc_qk, k > 0);
+          umma_bf16(tmem_s[buf], desc_q + (unsigned long long)(((k / 4) * kRowSubBytes + (k % 4) * 32) >> 4),
+                    dk + (unsigned long long)(((k / 4) * kKeySubBytes + (k % 4) * 32) >> 4), idesc_qk, k > 0);
         umma_commit(s_full(buf));
         return true;
       };
@@ -237,15 +239,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       for (int t = 0; ok && t < ntiles; ++t) {
         if (t + 1 < ntiles && !issue_qk(t + 1)) { ok = false; break; }
         const int stage = t % kKvStages, buf = t & 1;
-        if (!mbar_wait(v_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 14)) { ok = false; break; }
+        // The stage's values landed with its keys, which S = Q K^T of this tile waited for.
         if (!mbar_wait(p_full(buf), (unsigned)(t >> 1) & 1, p.error_flag, 15)) { ok = false; break; }
         tcgen05_fence_after();
+        const unsigned long long dp = desc_p + (unsigned long long)((buf * kRowTileBytes) >> 4);
+        const unsigned long long dv = desc_v + (unsigned long long)((stage * kTileBytes) >> 4);
 #pragma unroll
         for (int sub = 0; sub < kSub; ++sub)
 #pragma unroll
           for (int k = 0; k < kKeys / 16; ++k)
-            umma_bf16(tmem_o + sub * 64, umma_desc(p_smem + buf * kRowTileBytes + k * 32),
-                      umma_desc(v_smem + stage * kTileBytes + sub * kKeySubBytes + k * 16 * 128), idesc_pv, t > 0 || k > 0);
+            umma_bf16(tmem_o + sub * 64, dp + (unsigned long long)((k * 32) >> 4),
+                      dv + (unsigned long long)((sub * kKeySubBytes + k * 16 * 128) >> 4), idesc_pv, t > 0 || k > 0);
         umma_commit(kv_empty(stage));
         umma_commit(pv_done(buf));
       }
@@ -268,9 +272,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       tmem_load32(tmem_s[buf] + lane_field, sa);
       tmem_load32(tmem_s[buf] + lane_field + 32, sb);
       tmem_load_wait();
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free(buf));
 
       const bool all_visible = key0 + kKeys - 1 <= first_qpos && (p.window <= 0 || key0 > last_qpos - p.window);
       float mx = m;
@@ -300,8 +301,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       }
       const bool rescale = alpha != 1.f && m != -INFINITY;   // a row that has seen no key yet holds zeros
       const float neg = m_new == -INFINITY ? 0.f : -m_new * p.scale_log2;
-      // P of this tile overwrites the buffer that P V of tile t-2 read.
-      if (t >= 2 && !mbar_wait(pv_done(buf), (unsigned)((t - 2) >> 1) & 1, p.error_flag, 17)) { ok = false; break; }
+      // P of this tile overwrites the buffer that P V of tile t-2 read: that product was issued before S of this
+      // tile, whose arrival (waited for above) says that every product issued before it is done.
       float2 sums[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg, neg);
       unsigned char* prow = generic_base + (p_smem - base) + buf * kRowTileBytes + row * 128;
@@ -343,7 +344,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       l = l * alpha + sum;
       // Value rows of keys outside [lo, hi) may hold anything (an unwritten slot): zero them before P V reads them.
       if (key0 < lo || key0 + kKeys > hi) {
-        if (!mbar_wait(v_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 18)) { ok = false; break; }
+        if (!mbar_wait(kv_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 18)) { ok = false; break; }
         unsigned char* vt = generic_base + (v_smem - base) + stage * kTileBytes;
         for (int e = threadIdx.x - 64; e < kSub * kKeys * 8; e += 128) {
           const int sub = e / (kKeys * 8), key = (e >> 3) % kKeys;
