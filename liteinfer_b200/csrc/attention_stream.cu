@@ -139,6 +139,16 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int i = 0; i < kRing - 1; ++i) request(i);
 
   const size_t token = (size_t)q_begin * p.q_row_stride;
+  // Q: rows g and g+8 of the group (zero beyond it), pieces t, t+4, ...  Asked for before the newest key and value
+  // below, so that both trips to L2 run side by side.
+  uint4 qa[2][D / 32];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = g + 8 * h;
+    const bf16* src = p.q + token + (size_t)(kvh * groups + row) * D;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) qa[h][c] = row < groups ? ldg16(src + (t + 4 * c) * 8) : make_uint4(0, 0, 0, 0);
+  }
   if (owns_newest) {
     // The rotated key and the value of the newest token: to their page for the steps to come, and to shared
     // memory for this one (the copy on its way from the page may be older than the store).
@@ -170,15 +180,10 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     __syncthreads();
   }
 
-  // Q: rows g and g+8 of the group (zero beyond it), pieces t, t+4, ...; rotated here when the rotation is fused in
-  // (pieces t+4c and t+4c+D/16 hold the two halves of the same pairs).
-  uint4 qa[2][D / 32];
+  // Q is rotated here when the rotation is fused in (pieces t+4c and t+4c+D/16 hold the two halves of the same pairs).
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int row = g + 8 * h;
-    const bf16* src = p.q + token + (size_t)(kvh * groups + row) * D;
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) qa[h][c] = row < groups ? ldg16(src + (t + 4 * c) * 8) : make_uint4(0, 0, 0, 0);
     if (fused && row < groups) {
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
@@ -350,11 +355,12 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int row = g + 8 * h;
-    float* dst = os + ((size_t)warp * 16 + row) * D;
+    if (row >= groups) continue;          // rows of padding are never read
+    float4* dst = reinterpret_cast<float4*>(os + ((size_t)warp * 16 + row) * D + (2 * t) * (D / 8));
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-      dst[(2 * t) * (D / 8) + j] = o[j][2 * h];
-      dst[(2 * t + 1) * (D / 8) + j] = o[j][2 * h + 1];
+    for (int j = 0; j < D / 8; j += 4) {
+      dst[j / 4] = make_float4(o[j][2 * h], o[j + 1][2 * h], o[j + 2][2 * h], o[j + 3][2 * h]);
+      dst[(D / 8 + j) / 4] = make_float4(o[j][2 * h + 1], o[j + 1][2 * h + 1], o[j + 2][2 * h + 1], o[j + 3][2 * h + 1]);
     }
     if (t == 0) {
       ms[warp * 16 + row] = m[h];
