@@ -6,12 +6,19 @@
 // in tiles of 64:
 //
 //   loader  (warp 0)    TMA: each page of a tile's keys and values is one box of the pool's tensor map per 64
-//                       dimensions, landing in 128-byte-swizzled shared memory, three tiles ahead at most.
+//                       dimensions, landing in 128-byte-swizzled shared memory, three tiles ahead at most; lane b
+//                       looks up and requests page b of a tile, and one barrier per stage counts keys and values.
 //   issuer  (warp 1)    tcgen05.mma: S = Q K^T (128 x 64, K = head size) into one of two score buffers in
 //                       tensor memory, then O += P V (128 x 64 per 64 dimensions, K 64 keys) into the output
 //                       accumulator;
 //                       S of the next tile is issued before P V of this one, so the tensor cores work
-//                       while the softmax of this tile is computed.
+//                       while the softmax of this tile is computed.  The thread waits twice per tile (the
+//                       next stage has landed; this tile's probabilities are written): what else must hold
+//                       follows from those two and from the order in which products complete.
+//
+// The single threads of loader and issuer, not the softmax, used to set the pace of a tile: each wait that was
+// already satisfied cost them some 200 cycles, each descriptor a dozen dependent instructions.  Blocks are handed
+// out longest first (the query tile is the slowest index of the grid).
 //   softmax (warps 2-5) one thread per row: tcgen05.ld brings the row's 64 scores into registers, so
 //                       maximum and sum need no exchange between threads; the probabilities go to
 //                       shared memory as bfloat16 in the layout tcgen05.mma reads; the accumulator in

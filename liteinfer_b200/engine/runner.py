@@ -343,7 +343,7 @@ class ModelRunner:
         key = (_token_bucket(tokens), seqs, n_decode > 0, prefill, rows)
         graph = self._padded_graphs.get(key)
         if graph is None:
-            if len(self._graphs) + len(self._padded_graphs) >= _MAX_GRAPHS:
+            if len(self._padded_graphs) >= _MAX_GRAPHS:      # the decode graphs have a table of their own
                 return None
             graph = self._padded_graphs[key] = _PaddedGraph(self, *key, max_len)
         return graph
