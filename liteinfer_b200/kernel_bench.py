@@ -122,6 +122,15 @@ CASES = {
     "decode_attention_b64": lambda: attention(64, 1, 4096),
     "prefill_attention_2048": lambda: attention(1, 2048, 2048),
     "prefill_attention_4x2048_ctx4096": lambda: attention(4, 2048, 4096),
+    "prefill_attention_512": lambda: attention(1, 512, 512),
+    "prefill_attention_8192": lambda: attention(1, 8192, 8192),
+    "prefill_attention_16384": lambda: attention(1, 16384, 16384),
+    "prefill_attention_32x1024": lambda: attention(32, 1024, 1024),
+    "decode_attention_b8_ctx1024": lambda: attention(8, 1, 1024),
+    "decode_attention_b8_ctx16384": lambda: attention(8, 1, 16384),
+    "decode_attention_b1_ctx32768": lambda: attention(1, 1, 32768),
+    "decode_attention_b64_ctx1024": lambda: attention(64, 1, 1024),
+    "decode_attention_b256_ctx1024": lambda: attention(256, 1, 1024),
     "prefill_attention_2048_head128": lambda: attention(1, 2048, 2048, heads=32, kv_heads=8, head_dim=128),
     "skinny_qkv_b8": lambda: skinny(8, 3072, 2048),
     "skinny_o_b8": lambda: skinny(8, 2048, 2048),
