@@ -153,6 +153,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   grid_dependency_wait();   // q and the newest keys and values come from the kernel before; what is above waits for nobody
+  // The loader's warp: lane b looks up page b of tile t and asks for its boxes (keys and values, per 64 dimensions),
+  // so that the lookups and the requests of a tile's pages run side by side.  Returns false if a wait gave up.
+  const int boxes = kKeys / p.page_size;
+  const unsigned box_bytes = (unsigned)p.page_size * 64 * 2;
+  auto load_tile = [&](int t, bool stage_is_new) -> bool {
+    const int stage = t % kKvStages;
+    const unsigned phase = (unsigned)(t / kKvStages) & 1;
+    const int kpos = (tile_lo + t) * kKeys + lane * p.page_size;
+    int row = -1;
+    if (lane < boxes && kpos < hi && kpos + p.page_size > lo) {
+      const int page = table[kpos >> p.page_shift];
+      if (page >= 0 && page < p.num_pages) row = (page * p.kv_heads + kvh) * p.page_size;
+    }
+    const int valid = __popc(__ballot_sync(0xffffffffu, row >= 0));
+    bool fine = true;
+    if (lane == 0) {
+      if (!stage_is_new) fine = mbar_wait(kv_empty(stage), phase ^ 1, p.error_flag, 11);
+      if (fine) mbar_expect_tx(kv_full(stage), 2 * valid * kSub * box_bytes);
+    }
+    fine = __shfl_sync(0xffffffffu, fine, 0);
+    if (!fine) return false;
+    if (row >= 0) {
+#pragma unroll
+      for (int sub = 0; sub < kSub; ++sub) {
+        tma_load_2d(k_smem + stage * kTileBytes + sub * kKeySubBytes + lane * box_bytes, &map_k, kv_full(stage), sub * 64, row);
+        tma_load_2d(v_smem + stage * kTileBytes + sub * kKeySubBytes + lane * box_bytes, &map_v, kv_full(stage), sub * 64, row);
+      }
+    }
+    return true;
+  };
+  // The first tiles set out while Q is copied and tensor memory is handed round (the barriers were made by lane 0
+  // of this same warp, above).
+  const int tiles_ahead = min(kKvStages, ntiles);
+  if (warp == 0) {
+    __syncwarp();
+    for (int t = 0; t < tiles_ahead; ++t) load_tile(t, true);
+  }
   // Q: each softmax thread copies its row (128 bytes) into the swizzled tile; rows of padding are zero.
   if (warp >= 2) {
     const int row = (warp & 3) * 32 + lane;
@@ -189,35 +226,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 
   if (warp == 0) {
     // ------------------------------------------------------------------ loader
-    // Lane b of the warp looks up page b of a tile and asks for its boxes (keys and values, per 64 dimensions),
-    // so that the lookups and the requests of a tile's pages run side by side.
-    const int boxes = kKeys / p.page_size;
-    const unsigned box_bytes = (unsigned)p.page_size * 64 * 2;
-    bool fine = true;
-    for (int t = 0; t < ntiles; ++t) {
-      const int stage = t % kKvStages;
-      const unsigned phase = (unsigned)(t / kKvStages) & 1;
-      const int kpos = (tile_lo + t) * kKeys + lane * p.page_size;
-      int row = -1;
-      if (lane < boxes && kpos < hi && kpos + p.page_size > lo) {
-        const int page = table[kpos >> p.page_shift];
-        if (page >= 0 && page < p.num_pages) row = (page * p.kv_heads + kvh) * p.page_size;
-      }
-      const int valid = __popc(__ballot_sync(0xffffffffu, row >= 0));
-      if (lane == 0) {
-        fine = mbar_wait(kv_empty(stage), phase ^ 1, p.error_flag, 11);
-        if (fine) mbar_expect_tx(kv_full(stage), 2 * valid * kSub * box_bytes);
-      }
-      fine = __shfl_sync(0xffffffffu, fine, 0);
-      if (!fine) break;
-      if (row >= 0) {
-#pragma unroll
-        for (int sub = 0; sub < kSub; ++sub) {
-          tma_load_2d(k_smem + stage * kTileBytes + sub * kKeySubBytes + lane * box_bytes, &map_k, kv_full(stage), sub * 64, row);
-          tma_load_2d(v_smem + stage * kTileBytes + sub * kKeySubBytes + lane * box_bytes, &map_v, kv_full(stage), sub * 64, row);
-        }
-      }
-    }
+    for (int t = tiles_ahead; t < ntiles; ++t)
+      if (!load_tile(t, false)) break;
   } else if (warp == 1) {
     // ------------------------------------------------------------------ issuer
     if (lane == 0) {
