@@ -183,16 +183,14 @@ class _DecodeGraph:
         self.launches = kernels.launch_count - before
 
 
-def _token_bucket(n: int) -> int:
-    """The padded number of tokens of a step: steps of 16 up to 128, then of an eighth of the next power of two."""
-    for limit, step in ((128, 16), (256, 32), (512, 64), (1024, 128), (2048, 256)):
-        if n <= limit:
-            return -(-n // step) * step
-    return -(-n // 512) * 512
-
-
 def _pow2(n: int) -> int:
     return 1 if n <= 1 else 1 << (n - 1).bit_length()
+
+
+def _token_bucket(n: int) -> int:
+    """The padded number of tokens of a step: steps of 16 up to 128, then of an eighth of the next power of two."""
+    step = 16 if n <= 128 else _pow2(n) // 8
+    return -(-n // step) * step
 
 
 class _PaddedGraph:

@@ -234,3 +234,19 @@ def test_bench_run_reports_the_references_summaries(cpu_kernels, model_dirs, cap
     assert set(result["summary"]["latency"]) == {"ttft_p50_ms", "ttft_p95_ms", "ttft_p99_ms", "itl_p50_ms",
                                                  "itl_p95_ms", "itl_p99_ms", "e2e_p50_ms"}
     assert result["summary"]["throughput"]["output_tokens_per_s"] > 0
+
+
+def test_padded_shapes_of_the_step_graphs():
+    """The ladder that steps are rounded up to before they are replayed from a graph: never below the step, less
+    than 16 tokens or an eighth of the next power of two above it, few distinct shapes, and stable (a padded size
+    pads to itself)."""
+    from liteinfer_b200.engine.runner import _pow2, _token_bucket
+
+    shapes = set()
+    for n in range(1, 8193):
+        padded = _token_bucket(n)
+        shapes.add(padded)
+        assert padded >= n and _token_bucket(padded) == padded
+        assert padded - n < max(16, _pow2(n) // 8)
+    assert len(shapes) <= 48
+    assert [_pow2(n) for n in (0, 1, 2, 3, 4, 5, 33, 64)] == [1, 1, 2, 4, 4, 8, 64, 64]
