@@ -75,9 +75,10 @@ def _find_number(tree, key: str):
 
 def measured_peaks() -> dict:
     """Copy bandwidth (GB/s) and bfloat16 product throughput (TFLOP/s) to measure against: the driver's
-    measurements if it left them, else the stated fallback.  The product peak is the sustained one where the
-    file has it (the prefill step runs for milliseconds, under the power cap)."""
-    fallback = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    measurements if it left them, else the stated fallback.  `bf16_tflops_burst` is the library product timed
+    alone, `bf16_tflops` the same held for seconds under the power cap; a prefill step of a few milliseconds
+    timed alone is measured against the burst figure."""
+    fallback = {"hbm_gbs": 6650.0, "bf16_tflops": 1400.0, "bf16_tflops_burst": 1590.0, "source": "fallback"}
     path = ROOT / "MEASURED_PEAKS.json"
     if not path.is_file():
         return fallback
@@ -86,14 +87,15 @@ def measured_peaks() -> dict:
     except (OSError, ValueError):
         return fallback
     hbm = _find_number(raw, "hbm_gbs")
-    flops = _find_number(raw, "bf16_tflops_sustained") or _find_number(raw, "bf16_tflops")
+    burst = _find_number(raw, "bf16_tflops")
+    flops = _find_number(raw, "bf16_tflops_sustained") or burst
     if hbm is not None and hbm < 100:          # given in TB/s
         hbm *= 1000.0
     if flops is not None and flops > 100000:   # given in GFLOP/s
-        flops /= 1000.0
+        flops, burst = flops / 1000.0, (burst or flops) / 1000.0
     if not hbm or not flops:
         return fallback
-    return {"hbm_gbs": hbm, "bf16_tflops": flops, "source": "measured"}
+    return {"hbm_gbs": hbm, "bf16_tflops": flops, "bf16_tflops_burst": burst or flops, "source": "measured"}
 
 
 class ClockSampler:
@@ -228,7 +230,8 @@ def run_ours(args) -> dict:
         attn_flops = layers * 4 * cfg["num_attention_heads"] * cfg["head_dim"] * PREFILL_TOKENS * (PREFILL_TOKENS + 1) / 2
         prefill_flops = 2 * linear_params * PREFILL_TOKENS + attn_flops + 2 * hidden * vocab
         prefill = {"value": PREFILL_TOKENS / prefill_ms * 1e3, "tokens": PREFILL_TOKENS, "ms": prefill_ms,
-                   "frac": prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
+                   "frac": prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops_burst"] * 1e12),
+                   "frac_of_sustained": prefill_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
         if args.section == "prefill":
             llm.close()
             return {"section": "prefill", **prefill}
@@ -255,12 +258,16 @@ def run_ours(args) -> dict:
         llm.stats.steps.clear()
         outs = llm.generate(prompts, greedy)
         assert all(len(o.token_ids) == warmup + steps + 1 for o in outs)
+        # A step's time end to end: from the end of the step before it to its own end (scheduling, the step
+        # function, sampling, the read of the tokens, the stop rules and the loop around them).
         decode_steps = [s for s in llm.stats.steps if s.phase == "decode" and s.num_seqs == batch][-steps:]
-        e2e_ms = sum(s.wall_time_s for s in decode_steps) / len(decode_steps) * 1e3
+        e2e_ms = sum(s.stages.loop for s in decode_steps) / len(decode_steps) * 1e3
+        stage_us = {name: round(sum(getattr(s.stages, name) for s in decode_steps) / len(decode_steps) * 1e6, 1)
+                    for name in ("schedule", "launch", "wait", "finish", "forward_device", "sample_device")}
         pages = -(-CONTEXT // PAGE)
         e2e = {"value": batch / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": 4 * (3 * batch + (batch + 1) + 3 * batch + batch * pages),
-               "d2h_bytes_per_step": 4 * batch}
+               "d2h_bytes_per_step": 4 * batch, "stage_us": stage_us}
         llm.close()
 
     return {
@@ -280,21 +287,22 @@ def run_ours(args) -> dict:
 
 
 def run_reference(args) -> dict:
-    """The unmodified reference through its own public API, if `baseline/_ref` holds an install of it.
-
-    The one offline install (`pip install --no-index --no-build-isolation --find-links /opt/wheelhouse
-    --target baseline/_ref <reference>`) fails where this was built: the reference's build backend,
-    hatchling, is neither installed nor in the wheelhouse.  Without an install the arm is unavailable.
-    """
+    """The unmodified reference through its own public API: `baseline/_ref` holds its package (put there by
+    `baseline/install_reference.py`), `baseline/reference_arm.py` drives it.  Whatever keeps it from running
+    here (the package missing, a dependency missing on this box, its Triton kernels failing to compile for
+    this GPU) is printed as the reason for `unavailable`."""
     if not (ROOT / "baseline" / "_ref" / "liteinfer").is_dir():
-        return {"impl": "reference", "unavailable": "reference not installed: its build backend hatchling is "
-                "missing from the offline wheelhouse, so pip cannot build it (--no-deps does not help)"}
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no copy of the reference package "
+                "(run python baseline/install_reference.py <reference checkout> where one exists)"}
     try:
         sys.path.insert(0, str(ROOT / "baseline"))
         from reference_arm import run  # noqa: PLC0415
-        return run(args, LLAMA_1B, CONTEXT, PAGE)
+        helpers = {"ClockSampler": ClockSampler, "peaks": measured_peaks(), "baseline_toks": BASELINE_DECODE_B8_TOKS}
+        return run(args, LLAMA_1B, CONTEXT, PAGE, helpers)
     except Exception as error:  # noqa: BLE001
-        return {"impl": "reference", "unavailable": f"{type(error).__name__}: {str(error)[:200]}"}
+        import traceback
+        traceback.print_exc()
+        return {"impl": "reference", "unavailable": f"{type(error).__name__}: {str(error)[:300]}"}
 
 
 def main() -> int:

@@ -23,7 +23,7 @@ from liteinfer_b200.cache.manager import CacheManager
 from liteinfer_b200.cache.pages import CacheExhaustedError
 from liteinfer_b200.config.engine_config import EngineConfig
 from liteinfer_b200.engine.loading import resolve_model_path
-from liteinfer_b200.engine.metrics import EngineStats, StepMetrics
+from liteinfer_b200.engine.metrics import EngineStats, StageTimes, StepMetrics
 from liteinfer_b200.engine.runner import ModelRunner, StepEntry
 from liteinfer_b200.engine.scheduler import Scheduler, rows_to_shed
 from liteinfer_b200.engine.sequence import Sequence, SequenceStatus, resolve_stop_status
@@ -64,7 +64,8 @@ class EngineCore:
         self.tokenizer = None
         self.model_config = None
         self._step_idx = 0
-        self._admitted_this_step = 0
+        self._last_step_end = 0.0
+        self._events = None     # three CUDA events that mark the forward and the sampler on the stream
 
     # ----------------------------------------------------------------- load
     def load(self) -> None:
@@ -151,6 +152,8 @@ class EngineCore:
             raise ValueError(f"prompt has {len(token_ids)} tokens, >= max_model_len={self.config.max_model_len}")
         seq = Sequence(request_id=request_id, prompt=text, prompt_token_ids=list(token_ids), sampling_params=params,
                        detokenizer=IncrementalDetokenizer())
+        if not self.scheduler.has_unfinished():
+            self._last_step_end = 0.0
         self.scheduler.add(seq)
         return seq
 
@@ -160,12 +163,15 @@ class EngineCore:
     # ----------------------------------------------------------------- step
     def step(self) -> StepResult:
         result = StepResult()
+        timed = self.config.collect_stats
+        t_begin = time.perf_counter()
         for seq in self.scheduler.remove_finished():
             self.runner.release(seq.request_id)
             self.sampler.forget(seq.sampling_params, seq.request_id)
             result.released.append(seq)
         sched = self.scheduler.schedule()
         if sched.is_empty:
+            self._last_step_end = 0.0      # idle: the next step's loop time starts with that step
             return result
 
         entries: list[StepEntry] = []
@@ -177,9 +183,14 @@ class EngineCore:
             completes = seq.num_computed_tokens + count >= len(seq.prompt_token_ids)
             entries.append(StepEntry(seq.request_id, seq.next_tokens(count), (count - 1,) if completes else ()))
 
+        events = self._stream_events() if timed else None
         start = time.perf_counter()
         try:
+            if events:
+                events[0].record()
             logits = self.runner.step(entries)
+            if events:
+                events[1].record()
         except CacheExhaustedError as error:
             self._abort(rows_to_shed(sched.seqs), error, result)
             return result
@@ -190,9 +201,14 @@ class EngineCore:
         for seq, entry in zip(sched.seqs, entries):
             seq.num_computed_tokens += len(entry.tokens)
         sampling = [seq for seq, entry in zip(sched.seqs, entries) if entry.want]
+        t_launched = t_read = time.perf_counter()
         if sampling:
             sampled = self.sampler(logits, [s.sampling_params for s in sampling], [s.request_id for s in sampling])
-            for seq, token_id in zip(sampling, sampled.tolist()):   # one device-to-host read per step
+            if events:
+                events[2].record()
+            token_ids = sampled.tolist()       # one device-to-host read per step
+            t_read = time.perf_counter()
+            for seq, token_id in zip(sampling, token_ids):
                 seq.output_token_ids.append(int(token_id))
                 needs_text = self.text_every_step or bool(seq.sampling_params.stop)
                 if needs_text:
@@ -205,15 +221,31 @@ class EngineCore:
                     seq.status = status
                     self.stats.num_requests_finished += 1
             result.sampled = sampling
-        if self.config.collect_stats:
+        if timed:
             if self.device.type == "cuda" and not sampling:
                 torch.cuda.synchronize(self.device)
+                t_read = time.perf_counter()
+            now = time.perf_counter()
+            stages = StageTimes(schedule=start - t_begin, launch=t_launched - start, wait=t_read - t_launched,
+                                finish=now - t_read, loop=now - (self._last_step_end or t_begin))
+            if events:      # the read above waited for the stream, so the events have happened
+                stages.forward_device = events[0].elapsed_time(events[1]) * 1e-3
+                if sampling:
+                    stages.sample_device = events[1].elapsed_time(events[2]) * 1e-3
+            self._last_step_end = now
             self.stats.record(StepMetrics(self._step_idx, len(entries), sum(len(e.tokens) for e in entries),
-                                          prompt_tokens, len(sampling), time.perf_counter() - start))
+                                          prompt_tokens, len(sampling), now - start, stages, now))
         self._step_idx += 1
         if self._step_idx % 256 == 1:
             self.runner.check_kernels()
         return result
+
+    def _stream_events(self):
+        if self.device.type != "cuda":
+            return None
+        if self._events is None:
+            self._events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        return self._events
 
     def _abort(self, seqs: list[Sequence], error: Exception, result: StepResult) -> None:
         for seq in seqs:

@@ -17,7 +17,7 @@ import tiny_configs
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"tiny_a": (5, 17, 33, 70, 129), "tiny_b": (1, 9, 40, 64, 100), "tiny_c": (3, 50, 66),
-           "tiny_d": (2, 70, 130, 300)}
+           "tiny_d": (2, 70, 130, 300), "tiny_e": (3, 66, 140, 260)}
 
 
 def _requests(vocab: int, lengths) -> dict[str, list[int]]:

@@ -44,8 +44,21 @@ TINY_D = {
 }
 TINY_D_SEED, TINY_D_PAGE = 3, 16
 
+# Head size 128 in groups of three (the 3B shape's grouping), projections wider than the model (6 x 128 = 768
+# against 384), untied head: the <128> instantiations of the tensor-core, TMA and tcgen05 attention kernels.
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "vocab_size": 411, "hidden_size": 384, "intermediate_size": 272,
+    "num_hidden_layers": 2, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128,
+    "rms_norm_eps": 3e-6, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 256},
+    "tie_word_embeddings": False, "max_position_embeddings": 2048, "hidden_act": "silu",
+}
+TINY_E_SEED, TINY_E_PAGE = 5, 16
+
 ALL = {"tiny_a": (TINY_A, TINY_A_SEED, TINY_A_PAGE), "tiny_b": (TINY_B, TINY_B_SEED, TINY_B_PAGE),
-       "tiny_c": (TINY_C, TINY_C_SEED, TINY_C_PAGE), "tiny_d": (TINY_D, TINY_D_SEED, TINY_D_PAGE)}
+       "tiny_c": (TINY_C, TINY_C_SEED, TINY_C_PAGE), "tiny_d": (TINY_D, TINY_D_SEED, TINY_D_PAGE),
+       "tiny_e": (TINY_E, TINY_E_SEED, TINY_E_PAGE)}
 
 
 def prompt(vocab: int, length: int, seed: int) -> list[int]:
