@@ -8,7 +8,9 @@ given back).  A group that keeps every key never frees a page before the
 request ends; a group with a window frees the pages that the window has passed
 after each step.  Beside the groups, every request holds one slot of
 fixed-size state for the mixers that declare a `StateNeed` (the slot exists
-even when no layer uses it, so the step function always passes one).
+even when no layer uses it, so the step function always passes one).  A layer
+may declare several needs of either kind (two mixers in one block, a mixer with
+a short convolution tail and a recurrent state); each is found under its name.
 
 The reference keeps one pool for all layers and frees only at release
 (liteinfer/cache/kv_cache.py:129-174, block_pool.py:28-100); its rule that a
@@ -36,14 +38,29 @@ def _cdiv(a: int, b: int) -> int:
 @dataclass
 class KVGroup:
     need: KVNeed
-    stops: list[int]                     # schedule stops that keep their cache here, in order
+    holders: list[tuple[int, str]]       # (schedule stop, need's name) of every cache kept here, in order
     allocator: PageAllocator
     page_size: int
-    pool: torch.Tensor | None = None     # [len(stops), 2, pages, kv_heads, page_size, head_dim]
+    pool: torch.Tensor | None = None     # [len(holders), 2, pages, kv_heads, page_size, head_dim]
     tables: dict[str, list[int]] = field(default_factory=dict)
 
+    @property
+    def stops(self) -> list[int]:
+        """Schedule stops that keep a cache here, in order (a stop with two such needs appears twice)."""
+        return [stop for stop, _ in self.holders]
+
     def bytes_per_page(self, element_size: int) -> int:
-        return len(self.stops) * 2 * self.need.kv_heads * self.page_size * self.need.head_dim * element_size
+        return len(self.holders) * 2 * self.need.kv_heads * self.page_size * self.need.head_dim * element_size
+
+    def pages_at(self, total: int, largest_step: int) -> int:
+        """The most pages a request holds here at any time on its way to `total` tokens, when no step brings it
+        more than `largest_step` of them: every block for a group that keeps all keys; for a group with a
+        window, the blocks that the window still reaches at a step's start plus those the step writes."""
+        every = _cdiv(total, self.page_size)
+        if self.need.window is None:
+            return every
+        span = self.need.window - 1 + max(1, min(largest_step, total))
+        return min(every, _cdiv(span, self.page_size) + 1)
 
     def first_needed_block(self, total: int) -> int:
         """First logical block a request holding `total` tokens can still read."""
@@ -71,8 +88,8 @@ class CacheManager:
         self.dtype, self.device = dtype, torch.device(device)
         self.schedule = schedule
         self.groups: list[KVGroup] = []
-        self._stop_kv: dict[int, tuple[int, int]] = {}      # owning stop -> (group, index in group)
-        self._stop_state: dict[int, torch.Tensor | None] = {}
+        self._stop_kv: dict[int, dict[str, tuple[int, int]]] = {}     # owning stop -> name -> (group, index in group)
+        self._stop_state: dict[int, dict[str, torch.Tensor | None]] = {}
         self.slots = SlotAllocator(max_requests)
         self._slot_of: dict[str, int] = {}
         self._length: dict[str, int] = {}
@@ -86,30 +103,34 @@ class CacheManager:
                 continue
             for need in layer_needs[entry.layer]:
                 if isinstance(need, KVNeed):
-                    if stop in self._stop_kv:
-                        raise ValueError(f"layer {entry.layer} declares two KV needs; one is supported")
+                    mine = self._stop_kv.setdefault(stop, {})
+                    if need.name in mine:
+                        raise ValueError(f"layer {entry.layer} declares two KV needs named {need.name!r}; "
+                                         "give each a name of its own")
                     group = by_need.get(need)
                     if group is None:
                         group = KVGroup(need, [], PageAllocator(num_pages), page_size)
                         by_need[need] = group
                         self.groups.append(group)
-                    self._stop_kv[stop] = (self.groups.index(group), len(group.stops))
-                    group.stops.append(stop)
+                    mine[need.name] = (self.groups.index(group), len(group.holders))
+                    group.holders.append((stop, need.name))
                 elif isinstance(need, StateNeed):
-                    if stop in self._stop_state:
-                        raise ValueError(f"layer {entry.layer} declares two state needs; one is supported")
+                    mine = self._stop_state.setdefault(stop, {})
+                    if need.name in mine:
+                        raise ValueError(f"layer {entry.layer} declares two state needs named {need.name!r}; "
+                                         "give each a name of its own")
                     state_dtype = torch.float32 if need.kind == "f32" else dtype
                     state = None
                     if allocate_storage:
                         state = torch.zeros((max_requests, *need.shape), dtype=state_dtype, device=self.device)
                         self._state_tensors.append(state)
-                    self._stop_state[stop] = state
+                    mine[need.name] = state
                 else:
                     raise TypeError(f"unknown cache need {need!r}")
         if allocate_storage:
             for group in self.groups:
                 group.pool = torch.zeros(
-                    (len(group.stops), 2, num_pages, group.need.kv_heads, page_size, group.need.head_dim),
+                    (len(group.holders), 2, num_pages, group.need.kv_heads, page_size, group.need.head_dim),
                     dtype=dtype, device=self.device)
 
     # ----------------------------------------------------------- sizes
@@ -146,6 +167,15 @@ class CacheManager:
     @property
     def live_requests(self) -> list[str]:
         return list(self._length)
+
+    def can_hold(self, final_totals: list[int], largest_step: int) -> bool:
+        """Whether requests that grow to `final_totals` tokens, in steps of at most `largest_step` tokens each,
+        fit into the cache all at once: every group's pages (a window bounds what a request holds there) and the
+        state slots.  A model without pages is held by its slots alone."""
+        if len(final_totals) > self.max_requests:
+            return False
+        return all(sum(group.pages_at(total, largest_step) for total in final_totals) <= group.allocator.num_pages
+                   for group in self.groups)
 
     def pages_missing(self, request_ids: list[str], new_totals: list[int]) -> list[int]:
         """Per group, how many more pages the reservation would take."""
@@ -257,11 +287,10 @@ class CacheManager:
         for stop, entry in enumerate(self.schedule):
             owner = stop if entry.cache_of is None else entry.cache_of
             cache = LayerCache(read_only=entry.cache_of is not None)
-            if owner in self._stop_kv:
-                g, index = self._stop_kv[owner]
+            for name, (g, index) in self._stop_kv.get(owner, {}).items():
                 group = self.groups[g]
-                cache.kv = KVCacheView(group.pool[index, 0], group.pool[index, 1], g, self.page_size)
-            cache.state = self._stop_state.get(owner)
+                cache.kvs[name] = KVCacheView(group.pool[index, 0], group.pool[index, 1], g, self.page_size)
+            cache.states.update(self._stop_state.get(owner, {}))
             caches.append(cache)
         return caches
 

@@ -101,4 +101,7 @@ class EngineConfig:
     def resolved_device(self) -> torch.device:
         if self.device == "auto":
             return torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
-        return torch.device(self.device)
+        device = torch.device(self.device)
+        if device.type == "cuda" and device.index is None:      # "cuda" and "cuda:0" compare and hash apart
+            device = torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)
+        return device

@@ -117,18 +117,15 @@ class EngineCore:
     # ------------------------------------------------------------- requests
     def _pages_free_for(self, seq: Sequence, admitted: list[Sequence]) -> bool:
         """Admission gate: can the cache hold this request to its very end, beside every request that is
-        running or was admitted earlier in this step, each grown to its own end?  With this rule a step
-        of admitted requests never runs out of pages; requests wait for room instead."""
-        cache = self.runner.cache
-        page = cache.page_size
+        running (those admitted earlier in this step are among them), each grown to its own end?  Each group of
+        the cache says what a request of that length costs it (a window bounds what it holds there), and a model
+        that keeps no pages is held by its state slots alone.  With this rule a step of admitted requests never
+        runs out of pages; requests wait for room instead."""
+        def end_of(s: Sequence) -> int:
+            return min(len(s.prompt_token_ids) + s.sampling_params.max_tokens, self.config.max_model_len)
 
-        def pages_at_end(s: Sequence) -> int:
-            end = min(len(s.prompt_token_ids) + s.sampling_params.max_tokens, self.config.max_model_len)
-            return _cdiv(end, page)
-
-        live = [s for s in self.scheduler.running if not s.is_finished]
-        need = sum(pages_at_end(s) for s in [seq, *admitted, *live])
-        return all(need <= g.allocator.num_pages for g in cache.groups)
+        live = [s for s in self.scheduler.running if not s.is_finished and s is not seq]
+        return self.runner.cache.can_hold([end_of(s) for s in [seq, *live]], self.config.token_budget)
 
     @property
     def num_waiting(self) -> int:

@@ -140,7 +140,12 @@ class _DecodeGraph:
         self.views = self.batch.views(self.host.numpy())
         self.copied = torch.cuda.Event()       # recorded behind the copy of `host` to the device
         self.row_keys: list[tuple[str, int] | None] = [None] * width
+        self._write_fixed_parts()
+
+    def _write_fixed_parts(self) -> None:
+        """What is the same for every batch of this width: sequence i brings token i and wants its logits."""
         tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = self.views
+        width = self.batch.B
         seq[:] = np.arange(width, dtype=np.int32)
         qsl[:] = np.arange(width + 1, dtype=np.int32)
         rows[:] = seq
@@ -148,6 +153,15 @@ class _DecodeGraph:
         dtok[:] = seq
         for table in tables:
             table.fill(-1)
+        self.row_keys = [None] * width
+
+    def stage_padding(self) -> None:
+        """A batch that is all padding: no token belongs to a sequence, no sequence brings a token or holds a
+        context, the attention launches find no work.  Kernels run on it and touch neither pages nor state."""
+        _write_padding(self.views)
+
+    def after_capture(self) -> None:
+        self._write_fixed_parts()
 
     def stage(self, entries: list[StepEntry], cache: CacheManager, starts: list[int]) -> None:
         """Writes this step's batch (every entry one token, logits wanted) into the pinned buffer."""
@@ -169,7 +183,13 @@ class _DecodeGraph:
                 row[len(blocks):] = -1
 
     def capture(self, runner: ModelRunner) -> None:
-        """Called with the buffers holding a real batch: one eager pass on a side stream, then the capture."""
+        """One eager pass on a side stream, then the capture, both on a batch that is all padding: a live batch
+        would be run twice more than it should (harmless for keys and values, which are written to the same
+        places each time, but a part that updates a request's state in place would apply its step three times).
+        The graph is kept only if the capture succeeded."""
+        self.copied.synchronize()
+        self.stage_padding()
+        self.device_buffer.copy_(self.host, non_blocking=True)
         stream = torch.cuda.Stream(device=runner.device)
         stream.wait_stream(torch.cuda.current_stream(runner.device))
         with torch.cuda.stream(stream), kernels.on_current_stream():
@@ -177,10 +197,20 @@ class _DecodeGraph:
         torch.cuda.current_stream(runner.device).wait_stream(stream)
         torch.cuda.synchronize(runner.device)
         before = kernels.launch_count
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, pool=runner.graph_pool), kernels.on_current_stream():
-            self.logits = runner.model.forward(self.ctx, runner.layer_caches)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=runner.graph_pool), kernels.on_current_stream():
+            logits = runner.model.forward(self.ctx, runner.layer_caches)
         self.launches = kernels.launch_count - before
+        self.graph, self.logits = graph, logits
+        self.after_capture()
+
+
+def _write_padding(views) -> None:
+    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = views
+    for array in (tok, pos, qsl, ctxl, slots, rows, dtok):
+        array[:] = 0
+    for array in (seq, dseq, pseq, *tables):
+        array[:] = -1
 
 
 def _pow2(n: int) -> int:
@@ -242,6 +272,12 @@ class _PaddedGraph:
         dtok[n_decode:] = 0
         pseq[B - n_decode:] = -1
         return R
+
+    def stage_padding(self) -> None:
+        _write_padding(self.views)
+
+    def after_capture(self) -> None:
+        pass        # `stage` writes the whole batch every step
 
     capture = _DecodeGraph.capture
 
@@ -347,12 +383,18 @@ class ModelRunner:
         return graph
 
     def _replay(self, graph: _DecodeGraph | _PaddedGraph, entries: list[StepEntry]) -> torch.Tensor:
+        if graph.graph is None:
+            try:
+                graph.capture(self)
+            except BaseException:
+                # A graph whose capture failed (out of memory, say) must not be found again by the next step.
+                self._graphs = {k: g for k, g in self._graphs.items() if g is not graph}
+                self._padded_graphs = {k: g for k, g in self._padded_graphs.items() if g is not graph}
+                raise
         starts = [self.cache.length(e.request_id) for e in entries]
         wanted = graph.stage(entries, self.cache, starts)
         graph.device_buffer.copy_(graph.host, non_blocking=True)
         graph.copied.record()
-        if graph.graph is None:
-            graph.capture(self)
         graph.graph.replay()
         self.graph_launches += graph.launches
         self.graph_replays += 1
@@ -382,16 +424,19 @@ class ModelRunner:
         return logits
 
     def check_kernels(self) -> None:
-        """Raises if a bounded wait inside a tcgen05 kernel ever gave up (the results since the last check are then
-        not to be trusted).  Reads one integer from the device, so callers do it where they synchronise anyway."""
+        """Raises if a kernel has flagged a fault since the last check: a bounded wait inside a tcgen05 or TMA
+        kernel that gave up, or a token id outside the embedding table (the results since the last check are then
+        not to be trusted).  Reads two integers from the device, so callers do it where they synchronise anyway."""
         if self.device.type != "cuda":
             return
         from liteinfer_b200 import ops
 
-        where = ops.gemm_error_flag(self.device)
+        where, bad_token = ops.error_flags(self.device)
         if where:
             raise RuntimeError(f"a tcgen05 kernel stopped waiting on its pipeline (wait number {where}); "
                                "its output is unreliable")
+        if bad_token:
+            raise RuntimeError("a token id outside the vocabulary reached the embedding kernel")
 
     def release(self, request_id: str) -> None:
         """The request is finished: what it holds is given back."""

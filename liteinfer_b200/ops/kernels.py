@@ -158,13 +158,27 @@ class _Scratch:
         self.argmax_value = torch.empty(self.ARGMAX_ROWS * 32, dtype=torch.float32, device=device)
         self.argmax_index = torch.empty(self.ARGMAX_ROWS * 32, dtype=torch.int32, device=device)
         self.argmax_counters = torch.zeros(self.ARGMAX_ROWS, dtype=torch.int32, device=device)
-        self.gemm_error = torch.zeros(1, dtype=torch.int32, device=device)
+        # Error flags that kernels raise and the engine reads where it synchronises anyway: [0] the number of a
+        # bounded wait that gave up (tcgen05 and TMA kernels), [1] a token id outside the embedding table.
+        self.errors = torch.zeros(2, dtype=torch.int32, device=device)
+        self.gemm_error = self.errors[0:1]
+        self.token_error = self.errors[1:2]
 
 
 _scratch: dict[torch.device, _Scratch] = {}
 
 
-def scratch_for(device: torch.device) -> _Scratch:
+def normalise_device(device: torch.device | str) -> torch.device:
+    """`cuda` and `cuda:0` are one device (torch compares and hashes them apart): the index is filled in with the
+    current device's."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)
+    return device
+
+
+def scratch_for(device: torch.device | str) -> _Scratch:
+    device = normalise_device(device)
     found = _scratch.get(device)
     if found is None:
         found = _scratch[device] = _Scratch(device)
@@ -319,14 +333,25 @@ def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias:
     return out
 
 
-def gemm_error_flag(device: torch.device) -> int:
-    """0, or the number of the wait that gave up in a tcgen05 product since the flag was last cleared
+def gemm_error_flag(device: torch.device | str) -> int:
+    """0, or the number of the wait that gave up in a tcgen05 or TMA kernel since the flag was last cleared
     (synchronises the device)."""
-    flag = scratch_for(torch.device(device)).gemm_error
-    value = int(flag.item())
-    if value:
-        flag.zero_()
-    return value
+    return error_flags(device)[0]
+
+
+def token_error_flag(device: torch.device | str) -> torch.Tensor:
+    """The device's flag that the embedding kernel raises for a token id outside its table."""
+    return scratch_for(device).token_error
+
+
+def error_flags(device: torch.device | str) -> tuple[int, int]:
+    """(the number of a bounded wait that gave up, whether a token id lay outside an embedding table) since the
+    flags were last read; reading clears them (one small copy that synchronises the device)."""
+    flags = scratch_for(device).errors
+    wait, token = flags.tolist()
+    if wait or token:
+        flags.zero_()
+    return int(wait), int(token)
 
 
 def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:

@@ -2,9 +2,14 @@
 
 Interface of a block:
 
-    __init__(parts: {role: built part}, ...)
-    roles                                   # the roles it expects, in order
+    roles = {role: registry}                # its parts by role, and the registry each is built from
+                                            # ("mixer", "feed_forward", "norm", "position")
+    __init__(parts: {role: built part})
     forward(hidden, delta, ctx, cache) -> (hidden, delta)
+
+A block may have any roles (two mixers side by side, a third norm); it hands
+each part what it needs of `cache`, where every part finds its own pages or
+state under the name its need declared.
 
 The residual stream travels as a pair: `hidden` [tokens, hidden_size] and a
 `delta` not yet added to it (None at the first layer).  A block's first norm
@@ -23,7 +28,7 @@ from liteinfer_b200.parts.registry import register_block
 class PreNormResidualBlock:
     """h = h + mixer(norm(h)); h = h + feed_forward(norm(h)) — liteinfer/models/llama.py:174-192."""
 
-    roles = ("mixer_norm", "mixer", "feed_forward_norm", "feed_forward")
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
 
     def __init__(self, parts: dict) -> None:
         self.mixer_norm = parts["mixer_norm"]

@@ -16,21 +16,26 @@ import torch
 
 @dataclass(frozen=True)
 class KVNeed:
-    """A mixer that keeps keys and values per token: `window` None keeps every
-    token, a number keeps the newest `window` of them."""
+    """A part that keeps keys and values per token: `window` None keeps every
+    token, a number keeps the newest `window` of them.  `name` is the key under
+    which the part finds its pages in its layer's `LayerCache.kvs`; a layer whose
+    parts declare several needs gives each its own name.  Needs that are equal
+    apart from the name share a group of pages."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    name: str = field(default="kv", compare=False)
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A mixer that keeps a fixed-size state per request, of `shape` per request.
-    `kind`: "weight" (engine dtype) or "f32"."""
+    """A part that keeps a fixed-size state per request, of `shape` per request.
+    `kind`: "weight" (engine dtype) or "f32".  `name`: its key in `LayerCache.states`."""
 
     shape: tuple[int, ...]
     kind: str = "f32"
+    name: str = "state"
 
 
 @dataclass
@@ -43,9 +48,24 @@ class KVCacheView:
 
 @dataclass
 class LayerCache:
-    kv: KVCacheView | None = None
-    state: torch.Tensor | None = None   # [slots, *StateNeed.shape] of this layer
+    """What one stop of the schedule keeps: pages and states, each under its need's name."""
+
+    kvs: dict[str, KVCacheView] = field(default_factory=dict)
+    states: dict[str, torch.Tensor] = field(default_factory=dict)   # each [slots, *StateNeed.shape]
     read_only: bool = False             # this stop reads another stop's cache and stores nothing
+
+    @property
+    def kv(self) -> KVCacheView | None:
+        """The pages of a layer that keeps one set of them (the one named "kv", else the only one)."""
+        return self.kvs.get("kv") or (next(iter(self.kvs.values())) if len(self.kvs) == 1 else None)
+
+    @property
+    def state(self) -> torch.Tensor | None:
+        """The state of a layer that keeps one (the one named "state", else the only one)."""
+        found = self.states.get("state")
+        if found is None and len(self.states) == 1:
+            found = next(iter(self.states.values()))
+        return found
 
 
 @dataclass

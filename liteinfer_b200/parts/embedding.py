@@ -19,8 +19,6 @@ class TokenEmbedding:
     def __init__(self, vocab_size: int, hidden_size: int, dtype: torch.dtype, device: torch.device) -> None:
         self.vocab_size, self.hidden_size, self.dtype, self.device = vocab_size, hidden_size, dtype, device
         self.weight: torch.Tensor | None = None
-        # Set by the kernel when a token id lies outside the table; the step function reads it.
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=device)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {"weight": TensorSpec((self.vocab_size, self.hidden_size))}
@@ -30,7 +28,9 @@ class TokenEmbedding:
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.numel(), self.hidden_size), dtype=self.weight.dtype, device=token_ids.device)
-        return ops.embedding(token_ids, self.weight, out, self.error_flag)
+        # An id outside the table gives a zero row and raises the device's token flag, which
+        # `ModelRunner.check_kernels` reports (the step function refuses such ids on the host before that).
+        return ops.embedding(token_ids, self.weight, out, ops.token_error_flag(token_ids.device))
 
 
 class LinearHead:

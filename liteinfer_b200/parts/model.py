@@ -21,23 +21,19 @@ from liteinfer_b200.parts.context import LayerCache, StepContext
 from liteinfer_b200.parts.registry import BLOCKS, build_part
 from liteinfer_b200.parts.spec import ModelSpec, TensorSpec
 
-_ROLE_TABLE = {"mixer": "mixer", "feed_forward": "feed_forward"}
-
-
-def _role_kind(role: str) -> str:
-    """The registry a block's role is built from: '*_norm' roles are norms."""
-    if role.endswith("norm"):
-        return "norm"
-    return _ROLE_TABLE.get(role, role)
-
-
 class Layer:
+    """One layer: its block class says which roles it has and from which registry each is built
+    (`roles = {"mixer": "mixer", "mixer_norm": "norm", ...}`); the layer's spec names a part for every role."""
+
     def __init__(self, spec, dtype: torch.dtype, device: torch.device) -> None:
         if spec.block not in BLOCKS:
             raise ValueError(f"no block of kind {spec.block!r} is registered; known: {sorted(BLOCKS)}")
         self.spec = spec
-        self.parts = {role: build_part(_role_kind(role), part, dtype=dtype, device=device)
-                      for role, part in spec.parts.items()}
+        roles = dict(BLOCKS[spec.block].roles)
+        if set(roles) != set(spec.parts):
+            raise ValueError(f"block {spec.block!r} has the roles {sorted(roles)}, the layer names parts for "
+                             f"{sorted(spec.parts)}")
+        self.parts = {role: build_part(roles[role], spec.parts[role], dtype=dtype, device=device) for role in roles}
         self.block = BLOCKS[spec.block](self.parts)
 
     def cache_needs(self) -> tuple:

@@ -12,7 +12,7 @@ learn which model they are in.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Mapping
+from typing import Any, Callable, Mapping
 
 
 @dataclass(frozen=True)
@@ -21,13 +21,15 @@ class TensorSpec:
 
     kind: "weight" is kept in the engine's dtype (bfloat16 or float32); "int" is
     an integer table kept as int32; "f32" stays 32-bit whatever the engine dtype.
-    init: how the random-weights mode draws it ("normal": N(0, 0.02);
-    "ones_normal": 1 + N(0, 0.01); "zeros").
+    init: how the random-weights mode draws it: "normal" (N(0, 0.02)),
+    "ones_normal" (1 + N(0, 0.01)), "zeros", or a function `(shape, generator) ->
+    float32 tensor` for a part whose parameters need a distribution of their own
+    (a decay kept in log space, a gate that must be positive).
     """
 
     shape: tuple[int, ...]
     kind: str = "weight"
-    init: str = "normal"
+    init: str | Callable[[tuple[int, ...], Any], Any] = "normal"
 
 
 @dataclass(frozen=True)

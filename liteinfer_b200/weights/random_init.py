@@ -3,7 +3,8 @@
 Every tensor the architecture's parts read is drawn with a CPU generator seeded
 once, in the fixed order of `Model.tensor_specs()`: "normal" tensors from
 N(0, 0.02), "ones_normal" (norm weights) from 1 + N(0, 0.01), "zeros" as zeros,
-integer tables uniformly; each is drawn in float32 and then stored in `dtype`.
+a tensor whose spec brings its own init function from that function (given the
+same generator), integer tables uniformly; each is drawn in float32 and then stored in `dtype`.
 Names that alias another tensor (a tied head) are not written, as in a real
 checkpoint.  The folder is what any other loader of this architecture reads.
 """
@@ -33,7 +34,11 @@ def random_tensors(raw_config: dict[str, Any], seed: int, dtype: torch.dtype = t
         if want.kind == "int":
             tensors[name] = torch.randint(0, 2 ** 15, want.shape, generator=generator, dtype=torch.int32)
             continue
-        if want.init == "zeros":
+        if callable(want.init):
+            value = torch.as_tensor(want.init(tuple(want.shape), generator), dtype=torch.float32)
+            if tuple(value.shape) != tuple(want.shape):
+                raise ValueError(f"the init function of {name!r} returned shape {tuple(value.shape)}, not {tuple(want.shape)}")
+        elif want.init == "zeros":
             value = torch.zeros(want.shape, dtype=torch.float32)
         elif want.init == "ones_normal":
             value = 1.0 + 0.01 * torch.randn(want.shape, generator=generator, dtype=torch.float32)

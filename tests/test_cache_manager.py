@@ -227,3 +227,45 @@ def test_slot_addressing_follows_the_block_tables():
     assert table[1, 5:11].tolist() == packed.slots[0, 7:].tolist()
     assert newest_slots(tables, [6, 10], 4).tolist() == [[int(table[0, 6]), int(table[1, 10])]]
     assert len(set(table[table >= 0].tolist())) == 18                  # no slot named twice
+
+
+def test_a_layer_may_keep_several_named_needs():
+    """Two mixers in one block, or a mixer with two states: every need is found under its name; needs that are
+    equal apart from the name share a group of pages (and its block tables)."""
+    needs = [(KVNeed(2, 8), KVNeed(2, 8, name="cross"), StateNeed((3,), "f32", name="tail"), StateNeed((5, 2), "weight", name="memory")),
+             (KVNeed(2, 8),)]
+    m = CacheManager(needs, (ScheduleEntry(0), ScheduleEntry(1)), 4, 6, 2, torch.float32, "cpu")
+    assert len(m.groups) == 1 and m.groups[0].holders == [(0, "kv"), (0, "cross"), (1, "kv")]
+    assert m.groups[0].pool.shape[0] == 3
+    first, second = m.layer_caches()
+    assert set(first.kvs) == {"kv", "cross"} and set(first.states) == {"tail", "memory"}
+    assert first.kvs["kv"].k_pool.data_ptr() != first.kvs["cross"].k_pool.data_ptr()
+    assert first.states["tail"].shape == (2, 3) and first.states["memory"].shape == (2, 5, 2)
+    assert first.kv is first.kvs["kv"] and first.state is None          # two states, neither named "state"
+    assert second.kv is not None and second.state is None and not second.states
+    with pytest.raises(ValueError, match="named 'kv'"):
+        CacheManager([(KVNeed(2, 8), KVNeed(4, 8))], (ScheduleEntry(0),), 4, 6, 2, torch.float32, "cpu")
+
+
+def test_a_window_bounds_what_a_request_costs_its_group():
+    needs = [(KVNeed(1, 4),), (KVNeed(1, 4, window=10),)]
+    m = CacheManager(needs, (ScheduleEntry(0), ScheduleEntry(1)), 4, 12, 8, torch.float32, "cpu", allocate_storage=False)
+    full, windowed = m.groups
+    assert full.pages_at(40, 8) == 10 and windowed.pages_at(40, 8) == 6 and windowed.pages_at(3, 8) == 1
+    assert m.can_hold([40], 8) and not m.can_hold([40, 20], 8)             # the group that keeps all keys decides
+    only_window = CacheManager([(KVNeed(1, 4, window=10),)], (ScheduleEntry(0),), 4, 12, 8, torch.float32, "cpu",
+                               allocate_storage=False)
+    assert only_window.can_hold([400, 400], 8) and not only_window.can_hold([400, 400, 400], 8)
+    stateless = CacheManager([(StateNeed((3,)),)], (ScheduleEntry(0),), 4, 1, 2, torch.float32, "cpu",
+                             allocate_storage=False)
+    assert stateless.can_hold([10 ** 6, 10 ** 6], 64) and not stateless.can_hold([1, 1, 1], 64)   # slots alone
+    # What it promises holds: a request stepped to its end in steps of at most 8 never holds more.
+    m2 = CacheManager([(KVNeed(1, 4, window=10),)], (ScheduleEntry(0),), 4, 6, 1, torch.float32, "cpu",
+                      allocate_storage=False)
+    total = 0
+    for n in (8, 8, 1, 1, 7, 8, 2, 8, 8, 8):
+        total += n
+        m2.reserve(["r"], [total])
+        assert m2.groups[0].allocator.num_held <= m2.groups[0].pages_at(61, 8)
+        m2.commit("r", total)
+        m2.check_invariants()

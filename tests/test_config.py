@@ -109,3 +109,13 @@ def test_engine_config_checks_and_budget():
         with pytest.raises(ValueError):
             EngineConfig(model="m", **bad)
     assert parse_dtype("bf16") == torch.bfloat16
+
+
+def test_cuda_and_cuda_0_are_one_device():
+    """Scratch buffers and error flags are kept per device; `cuda` must find what `cuda:0` left."""
+    import torch
+
+    from liteinfer_b200.ops import normalise_device
+
+    assert normalise_device("cuda") == normalise_device("cuda:0") == torch.device("cuda", 0)
+    assert normalise_device("cuda:1") == torch.device("cuda", 1) and normalise_device("cpu") == torch.device("cpu")

@@ -137,3 +137,25 @@ def test_padded_graphs_equal_eager_over_random_steps(model_dirs, name, dtype):
     assert worst <= 2 ** -6, worst
     assert replayed.graph_replays >= 100 and 5 <= len(replayed._padded_graphs) <= 60
     replayed.check_kernels()
+
+
+def test_a_wait_that_gave_up_is_reported(model_dirs):
+    """Kernels that wait on mbarriers poll a bounded number of times and then raise a flag on the device instead of
+    hanging; the engine reads it where it synchronises anyway.  The flag is set here by the host (no kernel is
+    made to give up): `check_kernels` must raise, name the wait, and clear the flag, whichever way the device was
+    named."""
+    from liteinfer_b200 import ops
+    from liteinfer_b200.engine.loading import build_runner
+    from liteinfer_b200.ops.kernels import scratch_for
+
+    config, _, page = tiny_configs.ALL["tiny_a"]
+    runner = build_runner(model_dirs["tiny_a"], torch.bfloat16, "cuda", page, 8, 2)      # "cuda", not "cuda:0"
+    runner.check_kernels()
+    scratch_for("cuda:0").gemm_error.fill_(7)
+    with pytest.raises(RuntimeError, match="wait number 7"):
+        runner.check_kernels()
+    runner.check_kernels()                                  # reading cleared it
+    ops.token_error_flag("cuda").fill_(1)
+    with pytest.raises(RuntimeError, match="outside the vocabulary"):
+        runner.check_kernels()
+    assert ops.error_flags("cuda:0") == (0, 0)

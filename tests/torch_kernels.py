@@ -14,6 +14,8 @@ import math
 
 import torch
 
+from liteinfer_b200.cache import addressing
+
 
 def _r(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return x.to(dtype).float()
@@ -121,12 +123,42 @@ def rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv
     qkv[:, :heads * head_dim] = q.reshape(T, -1).to(dtype)
     if not store:
         return
-    pos = positions.long()
-    pages = block_table.long()[seq_of_token.long(), pos // page_size]
-    ok = (pages >= 0) & (pages < k_pool.shape[0])
-    slot = pos % page_size
-    k_pool[pages[ok], :, slot[ok], :] = k.to(dtype)[ok]
-    v_pool[pages[ok], :, slot[ok], :] = v[ok]
+    # Where each token is written: its slot, from the block tables (tokens of padding belong to no sequence).
+    real = seq_of_token >= 0
+    tables = block_table.tolist()
+    seqs, pos = seq_of_token[real].tolist(), positions[real].tolist()
+    if all(n == 1 for n in _run_lengths(seqs)):
+        slots = addressing.newest_slots([tables[s] for s in seqs], pos, page_size, qkv.device)[0]
+    else:
+        runs = _runs(seqs, pos)
+        slots = addressing.packed_addresses([tables[s] for s, _, _ in runs], [a for _, a, _ in runs],
+                                            [n for _, _, n in runs], page_size, qkv.device).slots[0]
+    ok = (slots >= 0) & (slots < k_pool.shape[0] * page_size)
+    rows = torch.nonzero(real)[:, 0][ok]
+    k_pool[slots[ok] // page_size, :, slots[ok] % page_size, :] = k.to(dtype)[rows]
+    v_pool[slots[ok] // page_size, :, slots[ok] % page_size, :] = v[rows]
+
+
+def _run_lengths(seqs):
+    lengths, last = [], object()
+    for s in seqs:
+        if s == last:
+            lengths[-1] += 1
+        else:
+            lengths.append(1)
+            last = s
+    return lengths
+
+
+def _runs(seqs, positions):
+    """(sequence, first position, count) of each run of consecutive tokens of one sequence."""
+    runs = []
+    for s, p in zip(seqs, positions):
+        if runs and runs[-1][0] == s and runs[-1][1] + runs[-1][2] == p:
+            runs[-1][2] += 1
+        else:
+            runs.append([s, p, 1])
+    return runs
 
 
 def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens, num_seqs,
@@ -137,6 +169,11 @@ def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_sta
     qsl = query_start_loc.tolist()
     ctx = context_lens.tolist()
     qmat = q[:, :heads * head_dim].float().view(-1, heads, head_dim)
+    # What each sequence reads: the slots of its whole context, from the block tables.
+    slots_of = addressing.slot_table(block_table.tolist()[:num_seqs], [max(c, 0) for c in ctx[:num_seqs]], page_size,
+                                     q.device)
+    k_flat = k_pool.permute(0, 2, 1, 3).reshape(-1, kv_heads, head_dim)      # [slot, kv_heads, head_dim]
+    v_flat = v_pool.permute(0, 2, 1, 3).reshape(-1, kv_heads, head_dim)
     for s in range(num_seqs):
         q0, q1 = qsl[s], qsl[s + 1]
         n, c = q1 - q0, ctx[s]
@@ -144,10 +181,10 @@ def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_sta
             continue
         first = 0 if window <= 0 else max(0, (c - n) - window + 1)
         kpos = torch.arange(first, c, device=q.device)
-        pages = block_table[s].long()[kpos // page_size]
-        # keys / values [keys, kv_heads, head_dim]
-        keys = k_pool[pages, :, kpos % page_size, :].float()
-        vals = v_pool[pages, :, kpos % page_size, :].float()
+        slots = slots_of[s, first:c]
+        pages = torch.where(slots >= 0, slots // page_size, slots)
+        keys = k_flat[slots.clamp(min=0)].float()
+        vals = v_flat[slots.clamp(min=0)].float()
         keys = keys.repeat_interleave(groups, dim=1)
         vals = vals.repeat_interleave(groups, dim=1)
         scores = torch.einsum("qhd,khd->hqk", qmat[q0:q1], keys) * scale
@@ -167,6 +204,14 @@ def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_sta
 
 def gemm_error_flag(device):
     return 0
+
+
+def error_flags(device):
+    return (0, 0)
+
+
+def token_error_flag(device):
+    return None
 
 
 def argmax(logits, out):
@@ -214,4 +259,4 @@ def fused_decode_supports(*args) -> bool:
 
 
 ALL = ("fused_decode_supports", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
-       "gated_linear", "gemm_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
+       "gated_linear", "gemm_error_flag", "error_flags", "token_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
