@@ -29,6 +29,8 @@ namespace li {
 template <int NT, int kWarps = kSkinnyWarps>
 int launch_skinny(const SkinnyParams& p, cudaStream_t s) {
   const dim3 grid((p.N + 15) / 16, p.num_slices);
+  if (p.norm_weight)
+    return (int)launch_maybe_early(pdl_mode() >= 1, gemm_skinny_kernel<NT, kWarps, true>, grid, dim3(kWarps * 32), 0, s, p);
   return (int)launch_maybe_early(pdl_mode() >= 1, gemm_skinny_kernel<NT, kWarps>, grid, dim3(kWarps * 32), 0, s, p);
 }
 
@@ -46,15 +48,9 @@ LI_EXPORT int li_gemm_skinny_plan(int N, int K, int* warps, int* slice_k) { retu
 // tiles * slices * 16 * 8 * ceil(M/8) and num_counters at least tiles, with tiles = ceil(N/16).
 // gated_act: -1 plain; 0 silu, 1 gelu, 2 gelu-tanh, 3 relu on rows interleaved in eights (N a multiple of 16);
 // out is then [M, N/2].
-LI_EXPORT int li_gemm_skinny(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                             int gated_act, float* scratch, size_t scratch_floats, unsigned* counters,
-                             int num_counters, cudaStream_t stream) {
-  if (M == 0 || N == 0) return 0;
-  if (M > 64 || K < 8 || (K % 8)) return LI_ERR_UNSUPPORTED;
-  if (gated_act > 3 || (gated_act >= 0 && (N % 16))) return LI_ERR_UNSUPPORTED;
-  if (!aligned16(x) || !aligned16(w)) return LI_ERR_ALIGNMENT;
-  SkinnyParams p{(const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)out, M, N, K, 0, 1, gated_act,
-                 scratch, counters};
+static int run_skinny(SkinnyParams p, float* scratch, size_t scratch_floats, unsigned* counters, int num_counters,
+                      cudaStream_t stream) {
+  const int M = p.M, N = p.N, K = p.K;
   int warps = kSkinnyWarps;
   p.num_slices = li_gemm_skinny_plan(N, K, &warps, &p.slice_k);
   const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
@@ -85,4 +81,46 @@ LI_EXPORT int li_gemm_skinny(const void* x, const void* w, const void* bias, voi
     case 808: return launch_skinny<8, 8>(p, stream);
     default: return launch_skinny<8, 16>(p, stream);
   }
+}
+
+LI_EXPORT int li_gemm_skinny(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                             int gated_act, float* scratch, size_t scratch_floats, unsigned* counters,
+                             int num_counters, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M > 64 || K < 8 || (K % 8)) return LI_ERR_UNSUPPORTED;
+  if (gated_act > 3 || (gated_act >= 0 && (N % 16))) return LI_ERR_UNSUPPORTED;
+  if (!aligned16(x) || !aligned16(w)) return LI_ERR_ALIGNMENT;
+  SkinnyParams p{(const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)out, M, N, K, 0, 1, gated_act,
+                 scratch, counters};
+  return run_skinny(p, scratch, scratch_floats, counters, num_counters, stream);
+}
+
+// The same product with the steps around it fused in (either, both or neither):
+//   norm_weight != null: x holds unnormalised rows (row m is x[x_rows[m]] when x_rows is given); the product is
+//     that of weight * x / rms(x), where rms uses in_sumsq [in_parts][in_stride], the sums of squares of every
+//     row of x in parts.  The weight multiply is rounded to bfloat16; 1 / rms multiplies the 32-bit sums.
+//   out_sumsq != null (plain product only): out [M, N] is added to, out = round(out + round(product + bias)), and
+//     out_sumsq [ceil(N/16)][out_stride] receives the sums of squares of the new rows, one part per 16 columns.
+LI_EXPORT int li_gemm_skinny_fused(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                                   int gated_act, float* scratch, size_t scratch_floats, unsigned* counters,
+                                   int num_counters, const void* norm_weight, const float* in_sumsq, int in_parts,
+                                   int in_stride, float eps, const int* x_rows, float* out_sumsq, int out_stride,
+                                   cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M > 64 || K < 8 || (K % 8)) return LI_ERR_UNSUPPORTED;
+  if (gated_act > 3 || (gated_act >= 0 && (N % 16))) return LI_ERR_UNSUPPORTED;
+  if (out_sumsq && (gated_act >= 0 || out_stride < M)) return LI_ERR_UNSUPPORTED;
+  if (norm_weight && (!in_sumsq || in_parts < 1)) return LI_ERR_UNSUPPORTED;
+  if (!aligned16(x) || !aligned16(w) || (norm_weight && !aligned16(norm_weight))) return LI_ERR_ALIGNMENT;
+  SkinnyParams p{(const bf16*)x, (const bf16*)w, (const bf16*)bias, (bf16*)out, M, N, K, 0, 1, gated_act,
+                 scratch, counters};
+  p.norm_weight = (const bf16*)norm_weight;
+  p.in_sumsq = in_sumsq;
+  p.in_parts = in_parts;
+  p.in_stride = in_stride;
+  p.eps = eps;
+  p.x_rows = norm_weight ? x_rows : nullptr;
+  p.out_sumsq = out_sumsq;
+  p.out_stride = out_stride;
+  return run_skinny(p, scratch, scratch_floats, counters, num_counters, stream);
 }

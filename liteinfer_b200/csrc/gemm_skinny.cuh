@@ -8,6 +8,16 @@ namespace li {
 constexpr int kSkinnyWarps = 4;                                   // warps of the usual block; others have 2, 8 or 16
 constexpr int kBlocksPerWarp = 8;                                  // 32-wide k blocks per warp and pass
 constexpr int kMaxSlices = 16;
+constexpr int kStatsFloats = 2048;                                  // parts x rows of statistics a block keeps in shared memory
+
+// Copies `bytes` (4 or 16) from global to shared memory without passing through registers; the thread goes on.
+__device__ __forceinline__ void copy_async_4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -45,14 +55,49 @@ struct SkinnyParams {
   int gated_act;      // -1: plain product
   float* scratch;     // [tiles][num_slices][16][NT*8] partial tiles, when num_slices > 1
   unsigned* counters; // [tiles], zero between launches
+  // A root-mean-square norm of x fused in (kernels built with kNorm): x holds unnormalised rows, norm_weight [K]
+  // multiplies them on their way into the product, and the rows' inverse root mean squares multiply the sums at
+  // the end.  The sums of squares come in parts (what the product before this one left: one part per 16 columns
+  // it wrote), in_sumsq[part * in_stride + row], added here in a fixed order.
+  const bf16* norm_weight = nullptr;
+  const float* in_sumsq = nullptr;
+  int in_parts = 0;
+  int in_stride = 0;
+  float eps = 0.f;
+  const int* x_rows = nullptr;   // optional: row m of x is x[x_rows[m]] (and its statistics those of that row)
+  // The residual sum fused in: out [M, N] is the residual stream; it becomes round(out + round(product)), and
+  // out_sumsq[tile * out_stride + m] receives the sum of the squares of the tile's 16 new values of row m.
+  float* out_sumsq = nullptr;
+  int out_stride = 0;
 };
 
-template <int NT, int kWarps = kSkinnyWarps>   // NT tiles of 8 rows of x; kWarps warps share a slice's k blocks
+// a * b for two pairs of bfloat16, each product rounded to bfloat16 (exact product, one rounding).
+__device__ __forceinline__ unsigned mul_bf16x2(unsigned a, unsigned b) {
+  unsigned d;
+  asm("mul.rn.bf16x2 %0, %1, %2;\n" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Starts the copy of the statistics' parts (if they fit) into the block's shared memory.
+__device__ __forceinline__ void request_stats(const SkinnyParams& p, float* stats) {
+  const int total = p.in_parts * p.in_stride;
+  if (total > kStatsFloats) return;
+  if ((total & 3) == 0 && aligned16(p.in_sumsq)) {
+    for (int i = threadIdx.x * 4; i < total; i += blockDim.x * 4) copy_async_16(stats + i, p.in_sumsq + i);
+  } else {
+    for (int i = threadIdx.x; i < total; i += blockDim.x) copy_async_4(stats + i, p.in_sumsq + i);
+  }
+}
+
+// NT tiles of 8 rows of x; kWarps warps share a slice's k blocks; kNorm: x is normalised on its way in.
+template <int NT, int kWarps = kSkinnyWarps, bool kNorm = false>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(const SkinnyParams p) {
   constexpr int kCols = NT * 8;
   constexpr int kSlicePass = kWarps * kBlocksPerWarp * 32;   // k per pass of the block
   __shared__ float partial[4][16][kCols + 1];   // four warps' tiles at a time; [0] ends up holding the block's sum
+  __shared__ float inv_rms[kNorm ? kCols : 1];
+  __shared__ __align__(16) float stats[kNorm ? kStatsFloats : 4];   // the parts of the rows' sums of squares
   __shared__ bool is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int tile = blockIdx.x, slice = blockIdx.y;
@@ -63,7 +108,7 @@ gemm_skinny_kernel(const SkinnyParams p) {
   const bf16* w_hi = p.w + (size_t)min(row0 + g + 8, N - 1) * K;
   const bf16* xr[NT];
 #pragma unroll
-  for (int j = 0; j < NT; ++j) xr[j] = p.x + (size_t)min(j * 8 + g, M - 1) * K;
+  for (int j = 0; j < NT; ++j) xr[j] = p.x + (size_t)min(j * 8 + g, M - 1) * K;   // (gathered rows: set after the wait)
 
   float acc[NT][4];
 #pragma unroll
@@ -87,21 +132,56 @@ gemm_skinny_kernel(const SkinnyParams p) {
     if (!waited) {
       grid_dependency_wait();
       waited = true;
+      if (kNorm) {
+        if (p.x_rows) {
+#pragma unroll
+          for (int j = 0; j < NT; ++j) xr[j] = p.x + (size_t)p.x_rows[min(j * 8 + g, M - 1)] * K;
+        }
+        // The parts of the rows' sums of squares start on their way to shared memory; they are added up at
+        // the very end, when they have long arrived.
+        request_stats(p, stats);
+      }
     }
 #pragma unroll
     for (int u = 0; u < kBlocksPerWarp; ++u) {
       const int k = pass + (u * kWarps + warp) * 32 + 8 * t;
       const bool in = k < k_end;
+      uint4 nw = zero;
+      if (kNorm && in) nw = *reinterpret_cast<const uint4*>(p.norm_weight + k);
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        const uint4 xv = (in && j * 8 + g < M) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
+        uint4 xv = (in && j * 8 + g < M) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
+        if (kNorm) {
+          xv.x = mul_bf16x2(xv.x, nw.x);
+          xv.y = mul_bf16x2(xv.y, nw.y);
+          xv.z = mul_bf16x2(xv.z, nw.z);
+          xv.w = mul_bf16x2(xv.w, nw.w);
+        }
         mma_16816(acc[j], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv.x, xv.y);
         mma_16816(acc[j], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv.z, xv.w);
       }
     }
   }
 
-  if (!waited) grid_dependency_wait();
+  if (!waited) {
+    grid_dependency_wait();
+    if (kNorm) request_stats(p, stats);
+  }
+  if (kNorm) {
+    // One warp per row of x adds the parts of its sum of squares: lane by lane, then across the lanes, an order
+    // that depends on nothing but the number of parts.  Read at the very end, behind block barriers.
+    copy_async_wait_all();
+    __syncthreads();
+    const bool local = p.in_parts * p.in_stride <= kStatsFloats;
+    for (int m = warp; m < M; m += kWarps) {
+      const int src = p.x_rows ? p.x_rows[m] : m;
+      float ss = 0.f;
+      for (int i = lane; i < p.in_parts; i += 32)
+        ss += local ? stats[i * p.in_stride + src] : __ldcg(p.in_sumsq + (size_t)i * p.in_stride + src);
+      ss = warp_sum(ss);
+      if (lane == 0) inv_rms[m] = 1.0f / sqrtf(ss / (float)K + p.eps);
+    }
+  }
   grid_launch_dependents();
   // acc[j]: c0,c1 = (w row g, x rows j*8 + 2t, +1); c2,c3 = (w row g+8, same x rows).
   // The warps' tiles are added in warp order, four warps per round through shared memory; every element of
@@ -169,12 +249,33 @@ gemm_skinny_kernel(const SkinnyParams p) {
   }
   __syncthreads();
 
-  if (p.gated_act < 0) {
+  if (p.gated_act < 0 && p.out_sumsq) {
+    // The residual sum: out = round(out + round(product)), and the squares of the tile's new values per row
+    // (sixteen neighbouring lanes hold one row's sixteen columns).
+    for (int e = threadIdx.x; e < 16 * kCols; e += kWarps * 32) {
+      const int r = e % 16, m = e / 16;
+      const int n = row0 + r;
+      float sq = 0.f;
+      if (m < M && n < N) {
+        float sum = partial[0][r][m];
+        if (kNorm) sum *= inv_rms[m];
+        if (p.bias) sum += __bfloat162float(p.bias[n]);
+        bf16* at = p.out + (size_t)m * N + n;
+        const float h = __bfloat162float(__float2bfloat16_rn(__bfloat162float(*at) + __bfloat162float(__float2bfloat16_rn(sum))));
+        *at = __float2bfloat16_rn(h);
+        sq = h * h;
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (r == 0 && m < M) p.out_sumsq[(size_t)tile * p.out_stride + m] = sq;
+    }
+  } else if (p.gated_act < 0) {
     for (int e = threadIdx.x; e < 16 * kCols; e += kWarps * 32) {
       const int r = e % 16, m = e / 16;     // consecutive threads write consecutive output columns
       const int n = row0 + r;
       if (m >= M || n >= N) continue;
       float sum = partial[0][r][m];
+      if (kNorm) sum *= inv_rms[m];
       if (p.bias) sum += __bfloat162float(p.bias[n]);
       p.out[(size_t)m * N + n] = __float2bfloat16_rn(sum);
     }
@@ -185,6 +286,10 @@ gemm_skinny_kernel(const SkinnyParams p) {
       const int n = tile * 8 + r;
       if (m >= M || n >= half) continue;
       float gate = partial[0][r][m], up = partial[0][r + 8][m];
+      if (kNorm) {
+        gate *= inv_rms[m];
+        up *= inv_rms[m];
+      }
       if (p.bias) {
         gate += __bfloat162float(p.bias[row0 + r]);
         up += __bfloat162float(p.bias[row0 + r + 8]);

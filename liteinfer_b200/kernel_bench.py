@@ -53,6 +53,65 @@ def skinny(M: int, N: int, K: int) -> dict:
             "warps": ops.gemm_skinny_plan(N, K)[0], "slices": ops.gemm_skinny_plan(N, K)[1]}
 
 
+def stream_gemm(M: int, N: int, K: int, gated: bool = False) -> dict:
+    copies = max(2, (300 << 20) // (N * K * 2) + 1)
+    w = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N // 2 if gated else N, device="cuda", dtype=torch.bfloat16)
+    us = _time(lambda i: ops.gemm_stream(x, w[i], out, None, "silu" if gated else None), copies)
+    return {"kernel": "gemm_stream" + ("+silu*up" if gated else ""), "M": M, "N": N, "K": K, "us": us,
+            "GBps": N * K * 2 / us / 1e3, "wait_that_gave_up": ops.gemm_error_flag("cuda:0")}
+
+
+def skinny_fused(M: int, N: int, K: int, norm: bool, residual: bool, gated: bool = False) -> dict:
+    """The weight-streaming product with the norm before it folded in and / or the residual sum after it."""
+    copies = max(2, (300 << 20) // (N * K * 2) + 1)
+    w = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wn = torch.ones(K, device="cuda", dtype=torch.bfloat16)
+    stats = ops.RowStats(torch.rand(K // 16, M, device="cuda") * 16)
+    source = ops.PendingNorm(x, wn, 1e-5, stats) if norm else x
+    stream = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N // 2 if gated else N, device="cuda", dtype=torch.bfloat16)
+
+    def run(i):
+        if gated:
+            ops.gated_linear(source, w[i], out, "silu")
+        else:
+            ops.linear(source, w[i], None if residual else out, residual=stream if residual else None)
+
+    us = _time(run, copies)
+    return {"kernel": "gemm_skinny" + ("+norm" if norm else "") + ("+residual" if residual else "") + ("+silu*up" if gated else ""),
+            "M": M, "N": N, "K": K, "us": us, "GBps": N * K * 2 / us / 1e3}
+
+
+def mlp_chain(M: int, fused: bool, hidden: int = 2048, inter: int = 8192) -> dict:
+    """norm -> gate_up + activation -> down -> residual sum, as one decode layer's second half runs it: kernel by
+    kernel (three launches, the sum inside the next norm) or fused (two launches)."""
+    copies = 4
+    gu = [torch.randn(2 * inter, hidden, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    dn = [torch.randn(hidden, inter, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    wn = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
+    stream = torch.randn(M, hidden, device="cuda", dtype=torch.bfloat16)
+    mid = torch.empty(M, inter, device="cuda", dtype=torch.bfloat16)
+    delta = torch.zeros(M, hidden, device="cuda", dtype=torch.bfloat16)
+    normed = torch.empty(M, hidden, device="cuda", dtype=torch.bfloat16)
+    state = {"stats": ops.RowStats(torch.rand(hidden // 16, M, device="cuda") * 16)}
+
+    def run(i):
+        if fused:
+            ops.gated_linear(ops.PendingNorm(stream, wn, 1e-5, state["stats"]), gu[i], mid, "silu")
+            state["stats"] = ops.linear(mid, dn[i], None, residual=stream)
+        else:
+            ops.rmsnorm(stream, wn, 1e-5, normed, delta=delta, write_residual=True)
+            ops.gated_linear(normed, gu[i], mid, "silu")
+            ops.linear(mid, dn[i], delta)
+
+    us = _time(run, copies)
+    return {"kernel": "mlp half layer " + ("fused" if fused else "kernel by kernel"), "M": M, "us": us,
+            "GBps": (3 * inter * hidden * 2) / us / 1e3}
+
+
 def tcgen05_gemm(M: int, N: int, K: int, gated: bool = False) -> dict:
     copies = max(2, (300 << 20) // (N * K * 2) + 1)
     w = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
@@ -137,6 +196,24 @@ CASES = {
     "skinny_gate_up_b8": lambda: skinny(8, 16384, 2048),
     "skinny_down_b8": lambda: skinny(8, 2048, 8192),
     "skinny_head_b8": lambda: skinny(8, 128256, 2048),
+    "skinny_gate_up_silu_b8": lambda: skinny_fused(8, 16384, 2048, False, False, True),
+    "skinny_gate_up_silu_norm_b8": lambda: skinny_fused(8, 16384, 2048, True, False, True),
+    "skinny_gate_up_silu_norm_b1": lambda: skinny_fused(1, 16384, 2048, True, False, True),
+    "skinny_qkv_norm_b8": lambda: skinny_fused(8, 3072, 2048, True, False),
+    "skinny_down_residual_b8": lambda: skinny_fused(8, 2048, 8192, False, True),
+    "skinny_o_residual_b8": lambda: skinny_fused(8, 2048, 2048, False, True),
+    "skinny_head_norm_b8": lambda: skinny_fused(8, 128256, 2048, True, False),
+    "stream_qkv_b8": lambda: stream_gemm(8, 3072, 2048),
+    "stream_o_b8": lambda: stream_gemm(8, 2048, 2048),
+    "stream_gate_up_silu_b8": lambda: stream_gemm(8, 16384, 2048, True),
+    "stream_down_b8": lambda: stream_gemm(8, 2048, 8192),
+    "stream_head_b8": lambda: stream_gemm(8, 128256, 2048),
+    "stream_gate_up_silu_b1": lambda: stream_gemm(1, 16384, 2048, True),
+    "stream_gate_up_silu_b16": lambda: stream_gemm(16, 16384, 2048, True),
+    "mlp_chain_b8": lambda: mlp_chain(8, False),
+    "mlp_chain_fused_b8": lambda: mlp_chain(8, True),
+    "mlp_chain_b1": lambda: mlp_chain(1, False),
+    "mlp_chain_fused_b1": lambda: mlp_chain(1, True),
     "skinny_gate_up_b16": lambda: skinny(16, 16384, 2048),
     "library_gate_up_b16": lambda: library_gemm(16, 16384, 2048),
     "skinny_gate_up_b32": lambda: skinny(32, 16384, 2048),
@@ -162,9 +239,9 @@ CASES = {
 
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--kernel", default="all", help="one of: all, " + ", ".join(CASES))
+    parser.add_argument("--kernel", default="all", help="all, or names of cases separated by commas: " + ", ".join(CASES))
     args = parser.parse_args()
-    names = list(CASES) if args.kernel == "all" else [args.kernel]
+    names = list(CASES) if args.kernel == "all" else args.kernel.split(",")
     for name in names:
         result = CASES[name]()
         print(json.dumps({"case": name, **{k: (round(v, 2) if isinstance(v, float) else v) for k, v in result.items()}}),

@@ -61,7 +61,13 @@ _SIGNATURES = {
     "li_paged_attention_tcgen05_supports": ("attention_tcgen05", [c_int, c_int, c_int, c_int]),
     "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_void_p, c_size_t, c_void_p, c_int, c_void_p]),
+    "li_gemm_skinny_fused": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                             c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                             c_float, c_void_p, c_void_p, c_int, c_void_p]),
     "li_gemm_skinny_plan": ("gemm_skinny", [c_int, c_int, c_void_p, c_void_p]),
+    "li_gemm_stream": ("gemm_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                       c_int, c_void_p, c_void_p]),
+    "li_gemm_stream_supports": ("gemm_stream", [c_int, c_int, c_int]),
     "li_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                          c_void_p]),
     "li_gemm_simt": ("gemm_simt", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
@@ -259,26 +265,101 @@ def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> torch.
 
 
 # ------------------------------------------------------------- matrix product
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+@dataclass
+class RowStats:
+    """What a product leaves behind when it has added its result into the residual stream itself: the sums of
+    squares of the stream's new rows, in parts (one per 16 columns the product wrote), [parts, rows] float32.
+    The norm that follows needs nothing else of the rows' statistics."""
+
+    sumsq: torch.Tensor
+
+
+@dataclass
+class PendingNorm:
+    """A root-mean-square norm that has not run yet: `x` (the residual stream, sums done), the norm's weight and
+    eps, the rows' statistics, and optionally the rows that are wanted (int32 indices).  `linear` and
+    `gated_linear` take one in place of x and fold the norm into the product where their kernel can; anything
+    else calls `materialise()`."""
+
+    x: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    stats: RowStats
+    rows: torch.Tensor | None = None
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        return ((self.x.shape[0] if self.rows is None else self.rows.numel()), self.x.shape[1])
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.x.dtype
+
+    @property
+    def device(self) -> torch.device:
+        return self.x.device
+
+    def materialise(self) -> torch.Tensor:
+        from liteinfer_b200 import ops      # through the module, so that a stand-in kernel is found
+        out = torch.empty(self.shape, dtype=self.x.dtype, device=self.x.device)
+        return ops.rmsnorm(self.x, self.weight, self.eps, out, rows=self.rows)
+
+
+# LITEINFER_FUSED_NORM=1: the weight-streaming products add into the residual stream themselves and fold the norm
+# after it into the next product, which takes 32 launches out of a decode step of 16 layers.  Off by default: measured
+# on B200 at the 1B shape, a norm launched early costs 1.3 us between two products (its launch hides behind the
+# product's weights, which are asked for before the wait), while multiplying x by the norm's weight inside the
+# product's loop costs more (gate_up at 8 rows 20.9 against 15.2 us, the head 130 against 91): 1.17 against 1.06 ms
+# per decode step at batch 8.
+FUSED_NORM = os.environ.get("LITEINFER_FUSED_NORM", "0") == "1"
+
+
+# LITEINFER_GEMM_STREAM=0: products of at most 16 rows run on the kernel that loads its weights through registers
+# (gemm_skinny) instead of the persistent kernel with per-warp TMA rings (gemm_stream).
+GEMM_STREAM = os.environ.get("LITEINFER_GEMM_STREAM", "1") != "0"
+
+
+def _streams(M: int, N: int, K: int) -> bool:
+    """Whether the weight-streaming kernel runs a bfloat16 product of these sizes."""
+    if K % 8 or K < 8 or M <= 0:
+        return False
+    return M <= SKINNY_MAX_ROWS or (M <= SKINNY_MAX_ROWS_SMALL and N <= SKINNY_SMALL_WEIGHT_ROWS)
+
+
+def linear(x: "torch.Tensor | PendingNorm", weight: torch.Tensor, out: torch.Tensor | None,
+           bias: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> "torch.Tensor | RowStats":
     """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias).
 
     float32 runs the FFMA kernel (a true 32-bit product: tensor cores have no such
     mode).  bfloat16 hands the product to the library GEMM, as the reference's
     `nn.Linear` does (liteinfer/models/llama.py:108-110,137-140), with 32-bit
-    accumulation.
+    accumulation, except for a handful of rows, which the weight-streaming kernel takes.
+
+    `x` may be a `PendingNorm`: the weight-streaming kernel then normalises on its way in; any other path runs
+    the norm first.  With `residual` [M, N] the weight-streaming kernel adds its result into it
+    (residual = round(residual + round(product))) and returns the new rows' `RowStats`, `out` being unused; any
+    other path returns the product in `out`, for the caller to add.
     """
-    _on_gpu(x, weight, out, bias)
+    pending = x if isinstance(x, PendingNorm) else None
     M, K = x.shape
     N = weight.shape[0]
-    assert weight.shape[1] == K and out.shape == (M, N) and x.dtype == weight.dtype == out.dtype
+    fused = x.dtype == torch.bfloat16 and _streams(M, N, K)
+    if pending is not None and not fused:
+        x, pending = pending.materialise(), None
+    if residual is not None and not (fused and FUSED_NORM):
+        residual = None
+    if out is None and residual is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    _on_gpu(x if pending is None else pending.x, weight, out, bias, residual)
+    assert weight.shape[1] == K and x.dtype == weight.dtype
+    assert residual is None or (residual.shape == (M, N) and residual.dtype == x.dtype)
+    assert out is None or (out.shape == (M, N) and out.dtype == x.dtype)
     if x.dtype == torch.float32:
         _check(_fn("li_gemm_simt")(0, x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K,
                                    _stream()), "gemm_simt")
         return out
-    if 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and K >= 8:
-        return _skinny(x, weight, out, bias, -1)
-    if 0 < M <= SKINNY_MAX_ROWS_SMALL and N <= SKINNY_SMALL_WEIGHT_ROWS and K % 8 == 0 and K >= 8:
-        return _skinny(x, weight, out, bias, -1)
+    if fused:
+        return _skinny(x, weight, out, bias, -1, residual)
     if M > 0:
         torch.mm(x, weight.t(), out=out)
         if bias is not None:
@@ -297,14 +378,48 @@ SKINNY_SMALL_WEIGHT_ROWS = 4096
 NUM_SMS = 148
 
 
-def _skinny(x, weight, out, bias, gated_act: int) -> torch.Tensor:
+def _skinny(x, weight, out, bias, gated_act: int, residual: torch.Tensor | None = None, rings: bool = True):
+    """A weight-streaming kernel, with what `x` (a tensor or a PendingNorm) and `residual` ask to be fused in:
+    the persistent kernel with TMA rings where it takes the sizes (and `rings`), else the one that loads through
+    registers."""
     M, K = x.shape
     N = weight.shape[0]
-    ws = scratch_for(x.device)
-    _check(_fn("li_gemm_skinny")(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, gated_act,
-                                 ws.gemm.data_ptr(), ws.gemm.numel(), ws.gemm_counters.data_ptr(),
-                                 ws.gemm_counters.numel(), _stream()), "gemm_skinny")
-    return out
+    pending = x if isinstance(x, PendingNorm) else None
+    ws = scratch_for(weight.device)
+    if pending is None and rings and GEMM_STREAM and M <= 16:
+        # The persistent kernel that streams the weights through per-warp TMA rings.
+        stats = None
+        if residual is not None:
+            stats = RowStats(torch.empty((-(-N // 16), M), dtype=torch.float32, device=weight.device))
+        code = _fn("li_gemm_stream")(x.data_ptr(), weight.data_ptr(), _ptr(bias),
+                                     (residual if residual is not None else out).data_ptr(), M, N, K, gated_act,
+                                     _ptr(stats.sumsq if stats is not None else None), M if stats is not None else 0,
+                                     ws.gemm_error.data_ptr(), _stream())
+        if code != 100001:          # sizes it refuses go to the kernel below
+            _check(code, "gemm_stream")
+            return stats if stats is not None else out
+    if pending is None and residual is None:
+        _check(_fn("li_gemm_skinny")(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(), M, N, K, gated_act,
+                                     ws.gemm.data_ptr(), ws.gemm.numel(), ws.gemm_counters.data_ptr(),
+                                     ws.gemm_counters.numel(), _stream()), "gemm_skinny")
+        return out
+    stats = None
+    if residual is not None:
+        stats = RowStats(torch.empty((-(-N // 16), M), dtype=torch.float32, device=weight.device))
+    source = pending.x if pending is not None else x
+    _int32(pending.rows if pending is not None else None, "rows")
+    _check(_fn("li_gemm_skinny_fused")(
+        source.data_ptr(), weight.data_ptr(), _ptr(bias), (residual if residual is not None else out).data_ptr(),
+        M, N, K, gated_act, ws.gemm.data_ptr(), ws.gemm.numel(), ws.gemm_counters.data_ptr(),
+        ws.gemm_counters.numel(),
+        _ptr(pending.weight if pending is not None else None),
+        _ptr(pending.stats.sumsq if pending is not None else None),
+        pending.stats.sumsq.shape[0] if pending is not None else 0,
+        pending.stats.sumsq.shape[1] if pending is not None else 0,
+        float(pending.eps) if pending is not None else 0.0,
+        _ptr(pending.rows if pending is not None else None),
+        _ptr(stats.sumsq if stats is not None else None), M if stats is not None else 0, _stream()), "gemm_skinny_fused")
+    return stats if stats is not None else out
 
 
 def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
@@ -313,7 +428,27 @@ def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: 
     M, K = x.shape
     N = weight.shape[0]
     assert weight.shape[1] == K and out.shape == (M, N) and x.dtype == weight.dtype == out.dtype == torch.bfloat16
-    return _skinny(x, weight, out, bias, -1)
+    return _skinny(x, weight, out, bias, -1, rings=False)
+
+
+def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
+                gated_activation: str | None = None, residual: torch.Tensor | None = None):
+    """The persistent weight-streaming product (per-warp TMA rings) for at most 16 rows of x: out = x @ weight^T
+    (+ bias); with `gated_activation`, act(gate) * up on a weight interleaved in eights (out is [M, N/2]); with
+    `residual` [M, N] the result is added into it and the new rows' `RowStats` are returned (`out` unused)."""
+    _on_gpu(x, weight, out, bias, residual)
+    M, K = x.shape
+    N = weight.shape[0]
+    assert weight.shape[1] == K and x.dtype == weight.dtype == torch.bfloat16
+    act = -1 if gated_activation is None else ACTIVATIONS[gated_activation]
+    stats = None
+    if residual is not None:
+        stats = RowStats(torch.empty((-(-N // 16), M), dtype=torch.float32, device=weight.device))
+    _check(_fn("li_gemm_stream")(x.data_ptr(), weight.data_ptr(), _ptr(bias),
+                                 (residual if residual is not None else out).data_ptr(), M, N, K, act,
+                                 _ptr(stats.sumsq if stats is not None else None), M if stats is not None else 0,
+                                 scratch_for(x.device).gemm_error.data_ptr(), _stream()), "gemm_stream")
+    return stats if stats is not None else out
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
@@ -383,7 +518,7 @@ def gemm_skinny_slices(N: int, K: int) -> int:
 TCGEN05_MIN_ROWS = 256 if os.environ.get("LITEINFER_TCGEN05_GATED", "1") != "0" else 1 << 30
 
 
-def gated_linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+def gated_linear_supported(x: "torch.Tensor | PendingNorm", weight: torch.Tensor) -> bool:
     """Whether product, activation and multiply can be one kernel for this x: at most 8 rows (the
     weight-streaming kernel) or at least `TCGEN05_MIN_ROWS` (the tcgen05 kernel)."""
     M, K = x.shape
@@ -396,9 +531,11 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, activ
     """out[M, N/2] = act(gate) * up, where `weight` [N, K] holds gate and up rows interleaved in eights
     (rows 16b..16b+7 are gate rows 8b..8b+7, rows 16b+8..16b+15 their up rows): product, activation and
     multiply in one kernel (bfloat16)."""
-    _on_gpu(x, weight, out, bias)
     M, K = x.shape
     N = weight.shape[0]
+    if isinstance(x, PendingNorm) and M > SKINNY_MAX_ROWS:
+        x = x.materialise()
+    _on_gpu(x.x if isinstance(x, PendingNorm) else x, weight, out, bias)
     assert weight.shape[1] == K and out.shape == (M, N // 2) and gated_linear_supported(x, weight)
     if M <= SKINNY_MAX_ROWS:
         return _skinny(x, weight, out, bias, ACTIVATIONS[activation])

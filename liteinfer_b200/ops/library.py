@@ -36,7 +36,7 @@ NVCC_FLAGS = [
 
 # Source file (without .cu) of every library.
 SOURCES = ("elementwise", "rope_cache", "attention_generic", "attention_mma", "attention_stream", "attention_tcgen05",
-           "gemm_simt", "gemm_skinny", "gemm_skinny_static", "gemm_tcgen05", "sampling")
+           "gemm_simt", "gemm_skinny", "gemm_skinny_static", "gemm_stream", "gemm_tcgen05", "sampling")
 
 
 class KernelLibraryError(RuntimeError):

@@ -34,13 +34,14 @@ class Attention:
 
     def __init__(self, hidden_size: int, heads: int, kv_heads: int, head_dim: int, position: PartSpec,
                  dtype: torch.dtype, device: torch.device, bias: bool = False, out_bias: bool | None = None,
-                 window: int | None = None, scale: float | None = None) -> None:
+                 window: int | None = None, scale: float | None = None, cache_name: str = "kv") -> None:
         if heads % kv_heads:
             raise ValueError(f"heads={heads} is not a multiple of kv_heads={kv_heads}")
         self.hidden_size, self.heads, self.kv_heads, self.head_dim = hidden_size, heads, kv_heads, head_dim
         self.bias = bias
         self.out_bias = bias if out_bias is None else out_bias
         self.window = window
+        self.cache_name = cache_name    # under which name this mixer's pages lie in its layer's cache
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.dtype, self.device = dtype, device
         self.position = build_part("position", position, dtype=dtype, device=device)
@@ -75,10 +76,13 @@ class Attention:
         self.position.bind({n[len("position."):]: t for n, t in tensors.items() if n.startswith("position.")})
 
     def cache_needs(self) -> tuple:
-        return (KVNeed(self.kv_heads, self.head_dim, self.window),)
+        return (KVNeed(self.kv_heads, self.head_dim, self.window, name=self.cache_name),)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
-        kv = cache.kv
+    takes_pending_norm = True       # x may be an ops.PendingNorm: the qkv product folds the norm in
+    adds_to_residual = True         # the output projection adds into the residual stream where its kernel can
+
+    def forward(self, x, ctx: StepContext, cache: LayerCache, residual: torch.Tensor | None = None):
+        kv = cache.kvs[self.cache_name]
         tokens = x.shape[0]
         q_width = self.heads * self.head_dim
         qkv = torch.empty((tokens, q_width + 2 * self.kv_heads * self.head_dim), dtype=x.dtype, device=x.device)
@@ -96,8 +100,7 @@ class Attention:
                                 ctx.context_lens, ctx.num_seqs, ctx.max_query_len, self.heads, self.kv_heads,
                                 self.head_dim, self.scale, self.window or 0, plan=ctx.plan,
                                 decode_splits=ctx.decode_splits, newest=newest)
-            out = torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device)
-            return ops.linear(attended, self.o_weight, out, self.o_bias)
+            return ops.linear(attended, self.o_weight, None, self.o_bias, residual=residual)
         if rotary is None:
             kv_width = self.kv_heads * self.head_dim
             self.position.apply(qkv[:, :q_width].unflatten(1, (self.heads, self.head_dim)),
@@ -109,8 +112,7 @@ class Attention:
                             ctx.context_lens, ctx.num_seqs, ctx.max_query_len, self.heads, self.kv_heads,
                             self.head_dim, self.scale, self.window or 0, plan=ctx.plan,
                             decode_splits=ctx.decode_splits)
-        out = torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device)
-        return ops.linear(attended, self.o_weight, out, self.o_bias)
+        return ops.linear(attended, self.o_weight, None, self.o_bias, residual=residual)
 
 
 register_mixer("attention", Attention)

@@ -47,9 +47,10 @@ class LinearHead:
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        out = torch.empty((x.shape[0], self.vocab_size), dtype=x.dtype, device=x.device)
-        return ops.linear(x, self.weight, out)
+    takes_pending_norm = True       # x may be an ops.PendingNorm: the product folds the final norm in
+
+    def forward(self, x) -> torch.Tensor:
+        return ops.linear(x, self.weight, None)
 
 
 register_embedding("token_embedding", TokenEmbedding)

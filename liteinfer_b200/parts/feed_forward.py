@@ -57,7 +57,10 @@ class GatedMLP:
         stacked = torch.stack([gate.reshape(-1, 8, *rest), up.reshape(-1, 8, *rest)], dim=1)
         return stacked.reshape(2 * gate.shape[0], *rest).contiguous()
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    takes_pending_norm = True       # x may be an ops.PendingNorm: the gate_up product folds the norm in
+    adds_to_residual = True         # the down projection adds into the residual stream where its kernel can
+
+    def forward(self, x, ctx: StepContext, residual: torch.Tensor | None = None):
         tokens = x.shape[0]
         hidden = torch.empty((tokens, self.intermediate_size), dtype=x.dtype, device=x.device)
         if self.interleaved and ops.gated_linear_supported(x, self.gate_up_weight):
@@ -69,8 +72,7 @@ class GatedMLP:
                 ops.act_mul_interleaved(gate_up, hidden, self.activation)
             else:
                 ops.act_mul(gate_up, hidden, self.activation)
-        out = torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device)
-        return ops.linear(hidden, self.down_weight, out, self.down_bias)
+        return ops.linear(hidden, self.down_weight, None, self.down_bias, residual=residual)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

@@ -17,6 +17,7 @@ import liteinfer_b200.parts.embedding  # noqa: F401
 import liteinfer_b200.parts.feed_forward  # noqa: F401
 import liteinfer_b200.parts.norm  # noqa: F401
 import liteinfer_b200.parts.position  # noqa: F401
+from liteinfer_b200.parts.block import apply_norm
 from liteinfer_b200.parts.context import LayerCache, StepContext
 from liteinfer_b200.parts.registry import BLOCKS, build_part
 from liteinfer_b200.parts.spec import ModelSpec, TensorSpec
@@ -111,5 +112,5 @@ class Model:
         hidden, delta = self.hidden(ctx, caches)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=hidden.dtype, device=hidden.device)
-        normed = self.final_norm.forward(hidden, delta, rows=ctx.logit_rows)
+        normed = apply_norm(self.final_norm, hidden, delta, self.head, rows=ctx.logit_rows)
         return self.head.forward(normed)

@@ -8,6 +8,13 @@
 what is normalised, and it is stored back into `x` (the residual stream moves on
 in place) unless `rows` is given.  With `rows` (int32 indices) only those rows are
 produced: the final norm computes just the rows whose logits are wanted.
+
+Two optional abilities, which a block asks for only of a norm that declares them
+(`apply_norm` in parts/block.py): `reads_row_stats`: `delta` may be an
+`ops.RowStats` (the part before has already added its result into `x` and hands
+on the new rows' sums of squares); `defers`: with `lazy=True` and such statistics
+the norm does not run but returns an `ops.PendingNorm`, which the next part's
+first product folds in.
 """
 
 from __future__ import annotations
@@ -35,8 +42,15 @@ class RMSNorm:
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
 
-    def forward(self, x: torch.Tensor, delta: torch.Tensor | None = None, rows: torch.Tensor | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+    reads_row_stats = True
+    defers = True
+
+    def forward(self, x: torch.Tensor, delta: "torch.Tensor | ops.RowStats | None" = None,
+                rows: torch.Tensor | None = None, out: torch.Tensor | None = None, lazy: bool = False):
+        if isinstance(delta, ops.RowStats):
+            if lazy and out is None:
+                return ops.PendingNorm(x, self.weight, self.eps, delta, rows)
+            delta = None            # x holds the sum already
         n = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = torch.empty((n, self.size), dtype=x.dtype, device=x.device)

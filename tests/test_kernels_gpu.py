@@ -311,7 +311,7 @@ def test_linear_hands_narrow_batches_to_the_streaming_kernel():
         assert (ops.kernels.launch_count > before) == streams     # library products are not counted
         torch.testing.assert_close(out.double(), x.double() @ w.double().t(), rtol=2 ** -7, atol=2 ** -7)
         if streams:
-            assert torch.equal(out, ops.gemm_skinny(x, w, torch.empty(M, N, dtype=torch.bfloat16, device="cuda")))
+            assert torch.equal(out, ops.gemm_stream(x, w, torch.empty(M, N, dtype=torch.bfloat16, device="cuda")))
 
 
 def test_gemm_skinny_refuses_what_it_cannot_do():
@@ -567,3 +567,145 @@ def test_tcgen05_attention_refuses_what_it_cannot_do():
     assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 96, 16)      # head size 96: the plain kernel
     assert not ops.tcgen05_attention_supports(torch.bfloat16, 4, 2, 64, 8)       # pages of 8
     assert not ops.tcgen05_attention_supports(torch.float32, 4, 2, 64, 16)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 13])
+@pytest.mark.parametrize("N,K", [(3072, 2048), (2048, 8192), (1000, 96), (64, 32768)])
+def test_streaming_product_adds_into_the_residual_stream(M, N, K, monkeypatch):
+    """With `residual` the weight-streaming kernel adds its result into the stream itself (the same bits as the
+    product followed by the 32-bit sum rounded once) and leaves the new rows' sums of squares in parts."""
+    from liteinfer_b200 import ops
+
+    monkeypatch.setattr(ops.kernels, "FUSED_NORM", True)       # the fusion is a switch (off by default)
+    x, w = _randn(M, K, dtype=torch.bfloat16), _randn(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    b = _randn(N, dtype=torch.bfloat16, seed=2)
+    stream = _randn(M, N, dtype=torch.bfloat16, seed=3, scale=2.0)
+    product = ops.linear(x, w, torch.empty(M, N, dtype=torch.bfloat16, device="cuda"), b)
+    want = (stream.float() + product.float()).to(torch.bfloat16)
+    got = stream.clone()
+    stats = ops.linear(x, w, None, b, residual=got)
+    assert isinstance(stats, ops.RowStats) and stats.sumsq.shape == (-(-N // 16), M)
+    assert torch.equal(got, want)
+    torch.testing.assert_close(stats.sumsq.sum(0), want.float().pow(2).sum(-1), rtol=1e-5, atol=1e-5)
+    again = stream.clone()
+    assert torch.equal(ops.linear(x, w, None, b, residual=again).sumsq, stats.sumsq) and torch.equal(again, got)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("N,K,gated", [(3072, 2048, False), (16384, 2048, True), (1000, 96, False), (352, 64, True),
+                                       (128256 // 4, 2048, False)])
+def test_streaming_product_folds_the_norm_in(M, N, K, gated):
+    """A pending norm as the product's input: weight * x / rms(x) with the statistics from the parts that the
+    product before left, for all rows or for rows picked by index; against the norm kernel followed by the
+    product, within bfloat16 rounding (the fused form rounds once less), and against float64."""
+    from liteinfer_b200 import ops
+
+    rows_total = M + 3
+    hidden = _randn(rows_total, K, dtype=torch.bfloat16, seed=4, scale=3.0)
+    wn = (1 + 0.1 * _randn(K, dtype=torch.float32, seed=5)).to(torch.bfloat16)
+    w = _randn(N, K, dtype=torch.bfloat16, seed=1, scale=0.02)          # results of magnitude one
+    # the statistics as a product of 7 column tiles would have left them
+    parts = torch.stack([c.float().pow(2).sum(-1) for c in hidden.chunk(7, dim=1)])
+    for rows in (None, torch.tensor(list(range(rows_total - 1, rows_total - 1 - M, -1)), dtype=torch.int32, device="cuda")):
+        if rows is None:
+            source, stats = hidden[:M].contiguous(), ops.RowStats(parts[:, :M].contiguous())
+        else:
+            source, stats = hidden, ops.RowStats(parts.contiguous())
+        pending = ops.PendingNorm(source, wn, 1e-5, stats, rows)
+        normed = pending.materialise()
+        picked = source if rows is None else source[rows.long()]
+        exact = (picked.double() / torch.sqrt(picked.double().pow(2).mean(-1, keepdim=True) + 1e-5)) * wn.double()
+        if gated:
+            got = ops.gated_linear(pending, w, torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda"), "silu")
+            two = ops.gated_linear(normed, w, torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda"), "silu")
+        else:
+            got = ops.linear(pending, w, None)
+            two = ops.linear(normed, w, None)
+            torch.testing.assert_close(got.double(), exact @ w.double().t(), rtol=2 ** -6, atol=2 ** -6)
+        # (the two-kernel form rounds the normalised row once more than the fused one: each is within a rounding of
+        # the exact product, so they are within two of each other)
+        torch.testing.assert_close(got.float(), two.float(), rtol=2 ** -5, atol=2 ** -5)
+
+
+def test_fused_decode_layer_chain_matches_the_unfused_one(monkeypatch):
+    """Norm -> product -> residual -> norm -> gated product -> product -> residual, as a decode step of five
+    tokens runs it (two fused products per half layer), against the same chain kernel by kernel."""
+    from liteinfer_b200.parts.block import apply_norm, run_part
+    from liteinfer_b200.parts.feed_forward import GatedMLP
+    from liteinfer_b200.parts.norm import RMSNorm
+    from liteinfer_b200 import ops
+
+    dev, dt, h, inter = torch.device("cuda:0"), torch.bfloat16, 256, 512
+    norm = RMSNorm(h, 1e-5, dt, dev)
+    hidden = _randn(5, h, dtype=dt, seed=2)
+    norm.bind({"weight": (1 + 0.1 * _randn(h, dtype=torch.float32, seed=1)).to(dt)})
+    mlp = GatedMLP(h, inter, "silu", dt, dev)
+    mlp.bind({n: _randn(*s.shape, dtype=dt, seed=10 + i, scale=0.05) for i, (n, s) in enumerate(mlp.tensor_specs().items())})
+    # unfused: materialised norms, deltas added by the next norm
+    a = hidden.clone()
+    d1 = mlp.forward(norm.forward(a, None), None)
+    d2 = mlp.forward(norm.forward(a, d1), None)
+    want = (a.float() + d2.float())
+    # fused: the parts add into the stream and hand on statistics
+    monkeypatch.setattr(ops.kernels, "FUSED_NORM", True)
+    b = hidden.clone()
+    s1 = run_part(mlp, apply_norm(norm, b, None, mlp), b, None)
+    assert isinstance(s1, ops.RowStats)
+    pending = apply_norm(norm, b, s1, mlp)
+    assert isinstance(pending, ops.PendingNorm)
+    s2 = run_part(mlp, pending, b, None)
+    assert isinstance(s2, ops.RowStats)
+    torch.testing.assert_close(b.float(), want, rtol=2 ** -6, atol=2 ** -6)
+    torch.testing.assert_close(s2.sumsq.sum(0), b.float().pow(2).sum(-1), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(3072, 2048), (2048, 8192), (1000, 96), (17, 40), (128256 // 8, 2048), (48, 16384),
+                                 (16384, 2048), (5000, 200)])
+def test_gemm_stream(M, N, K):
+    """The persistent product with per-warp TMA rings against a float64 product: tiles past N, chunks past K (a k
+    that is no multiple of 128, of 64, or smaller than one chunk), more tiles than blocks and fewer."""
+    from liteinfer_b200 import ops
+
+    x, w = _randn(M, K, dtype=torch.bfloat16), _randn(N, K, dtype=torch.bfloat16, seed=1, scale=0.05)
+    b = _randn(N, dtype=torch.bfloat16, seed=2)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    got = ops.gemm_stream(x, w, out, b)
+    want = x.double() @ w.double().t() + b.double()
+    assert ops.gemm_error_flag("cuda:0") == 0
+    torch.testing.assert_close(got.double(), want, rtol=2 ** -7, atol=2 ** -6 if K > 4096 else 2 ** -7)
+    again = ops.gemm_stream(x, w, torch.empty_like(out), b)
+    assert torch.equal(got, again)
+
+
+def test_gemm_stream_rows_do_not_depend_on_the_batch():
+    from liteinfer_b200 import ops
+
+    x, w = _randn(16, 2048, dtype=torch.bfloat16), _randn(555, 2048, dtype=torch.bfloat16, seed=1, scale=0.05)
+    full = ops.gemm_stream(x, w, torch.empty(16, 555, dtype=torch.bfloat16, device="cuda"))
+    for rows in (1, 5, 8, 12):
+        part = ops.gemm_stream(x[:rows].contiguous(), w, torch.empty(rows, 555, dtype=torch.bfloat16, device="cuda"))
+        assert torch.equal(part, full[:rows])
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("inter,K,act", [(8192, 2048, "silu"), (112, 120, "gelu_pytorch_tanh"), (176, 64, "relu")])
+def test_gemm_stream_epilogues(M, inter, K, act):
+    """act(gate) * up in the epilogue equals the product followed by the activation kernel; the residual sum equals
+    the product followed by a 32-bit sum rounded once, and leaves the sums of squares of the new rows."""
+    from liteinfer_b200 import ops
+
+    dt = torch.bfloat16
+    x = _randn(M, K, dtype=dt)
+    w = _interleave(_randn(inter, K, dtype=dt, seed=1, scale=0.05), _randn(inter, K, dtype=dt, seed=2, scale=0.05))
+    b = _interleave(_randn(inter, dtype=dt, seed=3), _randn(inter, dtype=dt, seed=4))
+    gu = ops.gemm_stream(x, w, torch.empty(M, 2 * inter, dtype=dt, device="cuda"), b)
+    two = ops.act_mul_interleaved(gu, torch.empty(M, inter, dtype=dt, device="cuda"), act)
+    got = ops.gemm_stream(x, w, torch.empty(M, inter, dtype=dt, device="cuda"), b, act)
+    assert torch.equal(got, two)
+    stream = _randn(M, 2 * inter, dtype=dt, seed=9, scale=2.0)
+    want = (stream.float() + gu.float()).to(dt)
+    stats = ops.gemm_stream(x, w, None, b, residual=stream)
+    assert torch.equal(stream, want)
+    torch.testing.assert_close(stats.sumsq.sum(0), want.float().pow(2).sum(-1), rtol=1e-5, atol=1e-5)
+    assert ops.gemm_error_flag("cuda:0") == 0

@@ -91,10 +91,16 @@ def gated_linear(x, weight, out, activation, bias=None):
     return act_mul_interleaved(gate_up, out, activation)
 
 
-def linear(x, weight, out, bias=None):
+def linear(x, weight, out, bias=None, residual=None):
+    """The product alone: a norm that is still pending runs first, and the result is never added into `residual`
+    here (the caller gets it back as the delta still to be added)."""
+    if hasattr(x, "materialise"):
+        x = x.materialise()
     y = x.float() @ weight.float().t()
     if bias is not None:
         y = y + bias.float()
+    if out is None:
+        out = torch.empty(y.shape, dtype=x.dtype, device=x.device)
     out.copy_(y.to(out.dtype))
     return out
 
