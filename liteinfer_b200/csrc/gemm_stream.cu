@@ -101,7 +101,9 @@ __device__ __forceinline__ void finish_tile(const StreamParams& p, int tile, int
 // kWarps warps with a ring of kRing stages each.  kWarpTiles: every warp multiplies whole tiles by itself (weights
 // of many tiles: nothing is added up across warps and the block never meets at a barrier); otherwise the warps
 // of a block split each tile's k (weights of few tiles).
-template <int NT, int kWarps, int kRing, bool kWarpTiles>
+// kCache > 0 (one tile of x's rows, warps that split k): a warp multiplies the same at most kCache chunks of k in every
+// tile, so it reads its share of x once and keeps it in registers.
+template <int NT, int kWarps, int kRing, bool kWarpTiles, int kCache = 0>
 __global__ void __launch_bounds__(kWarps * 32, kWarps * kRing <= 24 ? 2 : 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamParams p) {
   constexpr int kCols = NT * 8;
@@ -160,42 +162,65 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamParams
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
 
+  uint4 xq[kCache > 0 ? kCache : 1][4];
+  if (kCache > 0) {
+#pragma unroll
+    for (int c = 0; c < kCache; ++c)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int k = (chunk_first + c * chunk_step) * kChunkK + (q >> 1) * 64 + (2 * t + (q & 1)) * 8;
+        xq[c][q] = (c < per_tile && k < K && g < M) ? *reinterpret_cast<const uint4*>(xr[0] + k) : zero;
+      }
+  }
+
   int n = 0;
   bool gave_up = false;
+  // Waits for item n and multiplies it; `cached` (a compile-time index or -1) says where the warp keeps its x.
+  auto multiply = [&](int c, const uint4* cached) -> bool {
+    request(n + kRing - 1);
+    if (!mbar_wait(bars + 8u * (n % kRing), (unsigned)(n / kRing) & 1, p.error_flag, 31)) {
+      // Gave up: the copies still on their way get one more bounded chance to land before the memory is let go.
+      for (int r = n + 1; r < items && r < n + kRing; ++r)
+        mbar_wait(bars + 8u * (r % kRing), (unsigned)(r / kRing) & 1, nullptr, 0);
+      gave_up = true;
+      failed = 1;
+      return false;
+    }
+    const unsigned slot = ring + (unsigned)(n % kRing) * kStageBytes;
+    const int k0 = (chunk_first + c * chunk_step) * kChunkK;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        // Piece 2t + h of the box's 128-byte rows: the lanes of a quarter warp then hit eight different banks.
+        const unsigned piece = (unsigned)(2 * t + h);
+        const unsigned at = slot + (unsigned)b * (kStageBytes / 2) + ((piece ^ swz) << 4);
+        const uint4 wl = lds128(at + row_lo), wh = lds128(at + row_hi);
+        const int k = k0 + b * 64 + (int)piece * 8;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const uint4 xv = cached ? cached[b * 2 + h]
+                                  : ((k < K && j * 8 + g < M) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero);
+          mma_16816(acc[j], wl.x, wh.x, wl.y, wh.y, xv.x, xv.y);
+          mma_16816(acc[j], wl.z, wh.z, wl.w, wh.w, xv.z, xv.w);
+        }
+      }
+    }
+    __syncwarp();     // every lane has read the stage before lane 0 asks for new contents
+    ++n;
+    return true;
+  };
   // (With tiles split among the warps every warp walks the same tiles, so the block's barriers below are met by all.)
   const int rounds = kWarpTiles ? my_tiles : (blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0);
   for (int ti = 0; ti < rounds; ++ti) {
     const int tile = first_tile + ti * tile_step;
-    for (int c = 0; c < per_tile && !gave_up; ++c, ++n) {
-      request(n + kRing - 1);
-      if (!mbar_wait(bars + 8u * (n % kRing), (unsigned)(n / kRing) & 1, p.error_flag, 31)) {
-        // Gave up: the copies still on their way get one more bounded chance to land before the memory is let go.
-        for (int r = n + 1; r < items && r < n + kRing; ++r)
-          mbar_wait(bars + 8u * (r % kRing), (unsigned)(r / kRing) & 1, nullptr, 0);
-        gave_up = true;
-        failed = 1;
-        break;
-      }
-      const unsigned slot = ring + (unsigned)(n % kRing) * kStageBytes;
-      const int k0 = (chunk_first + c * chunk_step) * kChunkK;
+    if (kCache > 0) {
 #pragma unroll
-      for (int b = 0; b < 2; ++b) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          // Piece 2t + h of the box's 128-byte rows: the lanes of a quarter warp then hit eight different banks.
-          const unsigned piece = (unsigned)(2 * t + h);
-          const unsigned at = slot + (unsigned)b * (kStageBytes / 2) + ((piece ^ swz) << 4);
-          const uint4 wl = lds128(at + row_lo), wh = lds128(at + row_hi);
-          const int k = k0 + b * 64 + (int)piece * 8;
-#pragma unroll
-          for (int j = 0; j < NT; ++j) {
-            const uint4 xv = (k < K && j * 8 + g < M) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
-            mma_16816(acc[j], wl.x, wh.x, wl.y, wh.y, xv.x, xv.y);
-            mma_16816(acc[j], wl.z, wh.z, wl.w, wh.w, xv.z, xv.w);
-          }
-        }
-      }
-      __syncwarp();     // every lane has read the stage before lane 0 asks for new contents
+      for (int c = 0; c < kCache; ++c)
+        if (c < per_tile && !gave_up) multiply(c, xq[c]);
+    } else {
+      for (int c = 0; c < per_tile && !gave_up; ++c)
+        if (!multiply(c, nullptr)) break;
     }
     if (kWarpTiles && gave_up) break;
     // The tile's sum goes through shared memory: to meet the other warps' shares (added in warp order), or, for a
@@ -272,22 +297,22 @@ static int stream_sms() {
   return sms;
 }
 
-template <int NT, int kWarps, int kRing, bool kWarpTiles>
+template <int NT, int kWarps, int kRing, bool kWarpTiles, int kCache = 0>
 static int launch_stream_gemm(const CUtensorMap& map, const StreamParams& p, int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<NT, kWarps, kRing, kWarpTiles>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<NT, kWarps, kRing, kWarpTiles, kCache>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stream_gemm_smem<kWarps, kRing>());
     if (e != cudaSuccess) return (int)e;
     // Two blocks of six warps leave the SM a level-one cache that holds x (measured: gate_up at 8 rows 14.3 us with
     // 72 % of the SM's memory as shared memory, 16.0 us when all of it is).
     static const char* carve = getenv("LITEINFER_STREAM_CARVEOUT");
     const int percent = carve ? atoi(carve) : (kWarps * kRing <= 18 ? 72 : -1);
-    if (percent >= 0) cudaFuncSetAttribute(gemm_stream_kernel<NT, kWarps, kRing, kWarpTiles>,
+    if (percent >= 0) cudaFuncSetAttribute(gemm_stream_kernel<NT, kWarps, kRing, kWarpTiles, kCache>,
                                            cudaFuncAttributePreferredSharedMemoryCarveout, percent);
     configured = true;
   }
-  return (int)launch_maybe_early(pdl_mode() >= 1, gemm_stream_kernel<NT, kWarps, kRing, kWarpTiles>, dim3(grid),
+  return (int)launch_maybe_early(pdl_mode() >= 1, gemm_stream_kernel<NT, kWarps, kRing, kWarpTiles, kCache>, dim3(grid),
                                  dim3(kWarps * 32), stream_gemm_smem<kWarps, kRing>(), stream, map, p);
 }
 
@@ -306,7 +331,11 @@ static int plan_and_launch(const CUtensorMap& map, const StreamParams& p, cudaSt
   switch (plan) {
     case 'a': return launch_stream_gemm<NT, 7, 4, true>(map, p, min(sms, (tiles + 6) / 7), stream);
     case 'd': return launch_stream_gemm<NT, 6, 3, true>(map, p, min(2 * sms, (tiles + 5) / 6), stream);
-    case 'c': return launch_stream_gemm<NT, 6, 3, false>(map, p, min(tiles, 2 * sms), stream);
+    case 'c':
+      // (with at most three chunks of k a warp and one tile of rows, a warp keeps its share of x in registers)
+      if (NT == 1 && (p.K + kChunkK - 1) / kChunkK <= 18 && !getenv("LITEINFER_STREAM_NO_X_CACHE"))
+        return launch_stream_gemm<1, 6, 3, false, 3>(map, p, min(tiles, 2 * sms), stream);
+      return launch_stream_gemm<NT, 6, 3, false>(map, p, min(tiles, 2 * sms), stream);
     default: return launch_stream_gemm<NT, 8, 3, false>(map, p, tiles <= 2 * sms ? tiles : sms, stream);
   }
 }
