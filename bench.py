@@ -270,6 +270,18 @@ def run_ours(args) -> dict:
                "d2h_bytes_per_step": 4 * batch, "stage_us": stage_us}
         llm.close()
 
+    # ---- the reference's two larger configurations (full depth), each reported as a few flat numbers
+    points = {"decode_b1": b1, "decode_b64": b64}
+    workloads = {}
+    if args.shape == "1b" and not args.layers and not args.no_workloads:
+        args.workload = "all"
+        workloads = run_workloads(args)
+        for name, result in workloads.items():
+            for key, number in result.items():
+                if key in ("output_tok_s", "decode_hbm_frac", "decode_b1_tok_s", "decode_b8_tok_s", "decode_b64_tok_s",
+                           "decode_b1_hbm_frac", "decode_b8_hbm_frac", "decode_b64_hbm_frac", "failed"):
+                    points[f"w{name}_{key}"] = number
+
     return {
         "metric": f"decode tok/s at batch 8 ({model_name} shape)", "value": value, "unit": "tokens/s", "n_gpus": 1,
         "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -282,8 +294,112 @@ def run_ours(args) -> dict:
                    "l2": "inputs larger than L2 (weights and cache are read every step)",
                    "baseline": "reference A40 batch-8 decode, 1248 tok/s"},
         "clocks": clock_record, "e2e": e2e, "gpu_launches": launches * steps,
-        "prefill": prefill, "roofline": roofline, "points": {"decode_b1": b1, "decode_b64": b64},
+        "prefill": prefill, "roofline": roofline, "points": points, "workloads": workloads,
     }
+
+
+def _shape_numbers(cfg: dict) -> dict:
+    layers, hidden, vocab = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["vocab_size"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    linear = layers * (hidden * (q + 2 * kv) + q * hidden + 3 * hidden * cfg["intermediate_size"])
+    return {"weight_bytes": (linear + hidden * vocab + (2 * layers + 1) * hidden) * 2,     # every weight a step reads, once
+            "kv_bytes_per_token": layers * 2 * kv * 2}
+
+
+def workload_3b(args, peaks: dict) -> dict:
+    """The reference's serving workload at the Llama 3.2 3B layer sizes: 64 requests with prompts of 128 to 2,048
+    tokens (uniform, seeded) and 256 forced output tokens each, all offered at once to `LLM.generate` (continuous
+    batching under a token budget of 8,192).  One untimed run of the same requests comes first, as the reference's
+    harness warms up (benchmarks/harness.py:110-122).  Reported: output tokens per second over the whole run, and
+    for its decode steps the bytes they had to read (weights once, the live requests' cache) over their time."""
+    import random
+
+    import torch
+
+    from liteinfer_b200 import LLM, SamplingParams
+    from liteinfer_b200.weights.random_init import write_random_model
+
+    cfg = dict(LLAMA_3B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    numbers = _shape_numbers(cfg)
+    rng = random.Random(3)
+    lengths = [rng.randint(128, 2048) for _ in range(64)]
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in lengths]
+    params = SamplingParams(temperature=0.0, max_tokens=256, min_tokens=256, ignore_eos=True)
+    with tempfile.TemporaryDirectory() as tmp:
+        model_dir = write_random_model(cfg, Path(tmp) / "llama-3b", seed=0)
+        with LLM(str(model_dir), dtype="bfloat16", device="cuda:0", max_num_seqs=64, max_model_len=2048 + 256 + 1,
+                 block_size=PAGE, max_num_batched_tokens=8192) as llm:
+            llm.generate(prompts, params)                       # warm-up: every graph this run needs is captured
+            steps: list[tuple[str, float, int]] = []
+            scheduler = llm.engine.scheduler
+            llm.stats.on_step(lambda m: steps.append(
+                (m.phase, m.stages.loop, sum(len(s) for s in scheduler.running if not s.is_finished))))
+            torch.cuda.synchronize()
+            start = time.perf_counter()
+            outs = llm.generate(prompts, params)
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - start
+    assert all(len(o.token_ids) == 256 for o in outs)
+    decode = [(t, held) for phase, t, held in steps if phase == "decode"]
+    decode_bytes = sum(numbers["weight_bytes"] + held * numbers["kv_bytes_per_token"] for _, held in decode)
+    decode_s = sum(t for t, _ in decode)
+    return {"model": "llama-3.2-3b-shape", "layers": cfg["num_hidden_layers"], "layers_full": LLAMA_3B["num_hidden_layers"],
+            "requests": 64, "prompt_tokens": sum(lengths), "output_tokens": 64 * 256, "wall_s": wall,
+            "output_tok_s": 64 * 256 / wall, "total_tok_s": (sum(lengths) + 64 * 256) / wall, "steps": len(steps),
+            "decode_steps": len(decode), "decode_ms_per_step": decode_s / max(1, len(decode)) * 1e3,
+            "decode_hbm_frac": decode_bytes / decode_s / 1e9 / peaks["hbm_gbs"] if decode_s else None}
+
+
+def workload_8b(args, peaks: dict) -> dict:
+    """Decode at the Llama 3.1 8B layer sizes with every sequence at a context of 8,192: batch 1, 8 and 64, the cache
+    sized for 64 such sequences (68.7 GB beside 16 GB of weights).  Tokens per second of the step function and the
+    sampler, device-timed, and the fraction of the copy bandwidth that the bytes of a step come to."""
+    from liteinfer_b200 import LLM, SamplingParams
+    from liteinfer_b200.sampling.sampler import Sampler
+    from liteinfer_b200.weights.random_init import write_random_model
+
+    cfg = dict(LLAMA_8B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    numbers = _shape_numbers(cfg)
+    context, steps, warmup = 8192, args.steps, max(3, args.warmup)
+    start_len = context - (warmup + steps) - 1
+    greedy = SamplingParams(temperature=0.0, max_tokens=warmup + steps + 1, ignore_eos=True)
+    out = {"model": "llama-3.1-8b-shape", "layers": cfg["num_hidden_layers"], "layers_full": LLAMA_8B["num_hidden_layers"],
+           "context": context}
+    with tempfile.TemporaryDirectory() as tmp:
+        model_dir = write_random_model(cfg, Path(tmp) / "llama-8b", seed=0)
+        pages = 64 * (-(-(context + 1) // PAGE)) + 16
+        with LLM(str(model_dir), dtype="bfloat16", device="cuda:0", max_num_seqs=64, max_model_len=context + 1,
+                 block_size=PAGE, max_num_batched_tokens=8192, num_gpu_blocks=pages) as llm:
+            runner = llm.engine.runner
+            for group in runner.cache.groups:
+                group.pool.normal_(0.0, 0.5)
+            out["cache_gb"] = pages * runner.cache.bytes_per_page() / 1e9
+            for batch in (1, 8, 64):
+                value, ms, _ = _decode_rate(runner, Sampler(0), greedy, batch, start_len, steps, warmup, cfg["vocab_size"])
+                nbytes = numbers["weight_bytes"] + batch * (start_len + warmup + steps / 2) * numbers["kv_bytes_per_token"]
+                out[f"decode_b{batch}_tok_s"] = value
+                out[f"decode_b{batch}_ms"] = ms
+                out[f"decode_b{batch}_hbm_frac"] = nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]
+    return out
+
+
+def run_workloads(args) -> dict:
+    """The two larger configurations of the reference's benchmark set; a failure is reported, not raised."""
+    peaks = measured_peaks()
+    results = {}
+    for name, fn in (("3b", workload_3b), ("8b", workload_8b)):
+        if args.workload not in ("all", name):
+            continue
+        try:
+            started = time.perf_counter()
+            results[name] = {**fn(args, peaks), "took_s": round(time.perf_counter() - started, 1)}
+        except Exception as error:  # noqa: BLE001
+            results[name] = {"failed": f"{type(error).__name__}: {str(error)[:200]}"}
+    return results
 
 
 def run_reference(args) -> dict:
@@ -316,11 +432,19 @@ def main() -> int:
                         help="run one part only (for profiling); the JSON line then lacks the other parts")
     parser.add_argument("--batch", type=int, default=8, help="decode batch of --section decode")
     parser.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes: Llama 3.2 1B (the contract's), 3B or 3.1 8B")
+    parser.add_argument("--workload", default="none", choices=["none", "3b", "8b", "all"],
+                        help="run the reference's larger configurations instead (64 requests under continuous batching "
+                             "at the 3B sizes; decode at a context of 8,192 at the 8B sizes) and print their line")
+    parser.add_argument("--no-workloads", action="store_true",
+                        help="leave the 3B and 8B configurations out of the default run (they add about 80 s)")
     args = parser.parse_args()
     if args.gpus != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print("liteinfer_b200 is a single-GPU engine: bench.py runs at --gpus 1 only")
         return 2
+    if args.workload != "none" and args.impl == "ours":
+        print(json.dumps({"impl": "ours", "workloads": run_workloads(args)}))
+        return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0
