@@ -60,6 +60,11 @@ class EngineConfig:
 
     collect_stats: bool = True
 
+    # Launch a step before the tokens of the step before it have been read (they are copied into the batch on the
+    # device), so that planning and the stop rules run beside the device's work.  None: on.  False: every step's
+    # tokens are read before the next launch.
+    async_scheduling: bool | None = None
+
     block_size: int = 16
     gpu_memory_utilization: float = 0.85
     num_gpu_blocks: int | None = None

@@ -271,9 +271,26 @@ int launch_act_mul(const void* gate_up, void* out, size_t rows, int width, int a
   LI_LAUNCH_CHECK();
 }
 
+// tokens[dst[i]] = source[src[i]] for every i with dst[i] >= 0: token ids that were sampled on the device a step ago
+// take their places in this step's batch without a trip through the host.
+__global__ void scatter_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ dst, const int* __restrict__ src,
+                                      const int* __restrict__ source, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int d = dst[i];
+  if (d >= 0) tokens[d] = source[src[i]];
+}
+
 }  // namespace li
 
 using namespace li;
+
+LI_EXPORT int li_scatter_tokens(int* tokens, const int* dst, const int* src, const int* source, int n,
+                                cudaStream_t stream) {
+  if (n <= 0) return 0;
+  scatter_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, dst, src, source, n);
+  LI_LAUNCH_CHECK();
+}
 
 // out[t, :] = table[ids[t], :].  An id outside [0, vocab) sets *error_flag (if given) and yields zeros.
 LI_EXPORT int li_embedding(int dtype, const int* ids, const void* table, void* out, int tokens, int width, int vocab,

@@ -40,13 +40,36 @@ from liteinfer_b200.parts.model import Model
 _MAX_GRAPHS = 128   # liteinfer/engine/cuda_graphs.py:68
 
 
+def ops_scatter(tokens, dst, src, source):
+    from liteinfer_b200 import ops      # through the module, so that a stand-in kernel is found
+    return ops.scatter_tokens(tokens, dst, src, source)
+
+
 @dataclass
 class StepEntry:
-    """One request's share of a step: its next tokens and the places among them whose logits are wanted."""
+    """One request's share of a step: its next tokens and the places among them whose logits are wanted.
+
+    `late` (an entry of one token only): the token's value is not on the host yet; it is element `late` of the
+    tensor of sampled tokens that `ModelRunner.step` is given as `late_source`, and is copied from there on the
+    device.  `tokens` then holds a stand-in that is never looked at."""
 
     request_id: str
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    late: int | None = None
+
+
+class _Views:
+    """The arrays of one staged batch (slices of one buffer, numpy or torch)."""
+
+    __slots__ = ("tok", "pos", "seq", "qsl", "ctxl", "slots", "rows", "dseq", "dtok", "pseq", "late_dst", "late_src",
+                 "tables")
+    NAMES = __slots__[:-1]
+
+    def __iter__(self):      # tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, late_dst, late_src, *tables
+        for name in self.NAMES:
+            yield getattr(self, name)
+        yield from self.tables
 
 
 class _Batch:
@@ -55,7 +78,7 @@ class _Batch:
     def __init__(self, B: int, T: int, R: int, widths: list[int], n_decode: int, n_prefill: int) -> None:
         self.B, self.T, self.R, self.widths = B, T, R, widths
         self.n_decode, self.n_prefill = n_decode, n_prefill
-        sizes = [T, T, T, B + 1, B, B, R, n_decode, n_decode, n_prefill] + [B * w for w in widths]
+        sizes = [T, T, T, B + 1, B, B, R, n_decode, n_decode, n_prefill, B, B] + [B * w for w in widths]
         # Every array starts on a 16-byte boundary.
         self.sizes = sizes
         self.offsets = []
@@ -65,19 +88,30 @@ class _Batch:
             at += -(-n // 4) * 4
         self.total = max(at, 4)
 
-    def views(self, flat):
+    def views(self, flat) -> _Views:
         """The arrays as slices of `flat` (a numpy array or a tensor)."""
-        return [flat[o:o + n] for o, n in zip(self.offsets, self.sizes)]
+        slices = [flat[o:o + n] for o, n in zip(self.offsets, self.sizes)]
+        v = _Views()
+        for name, array in zip(_Views.NAMES, slices):
+            setattr(v, name, array)
+        v.tables = slices[len(_Views.NAMES):]
+        return v
 
 
 def _fill(batch: _Batch, flat: np.ndarray, entries: list[StepEntry], cache: CacheManager,
           starts: list[int]) -> None:
-    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = batch.views(flat)
-    cursor = row_cursor = nd = npf = 0
+    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, late_dst, late_src, *tables = batch.views(flat)
+    cursor = row_cursor = nd = npf = late = 0
     qsl[0] = 0
+    late_dst[:] = -1
     for i, entry in enumerate(entries):
         n = len(entry.tokens)
-        tok[cursor:cursor + n] = entry.tokens
+        if entry.late is None:
+            tok[cursor:cursor + n] = entry.tokens
+        else:
+            tok[cursor] = 0
+            late_dst[late], late_src[late] = cursor, entry.late
+            late += 1
         pos[cursor:cursor + n] = np.arange(starts[i], starts[i] + n, dtype=np.int32)
         seq[cursor:cursor + n] = i
         for place in entry.want:
@@ -104,7 +138,7 @@ def _fill(batch: _Batch, flat: np.ndarray, entries: list[StepEntry], cache: Cach
 
 
 def _context(batch: _Batch, dev: torch.Tensor, device, counts, totals, decode_splits, decode_bound) -> StepContext:
-    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = batch.views(dev)
+    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, _, _, *tables = batch.views(dev)
     B = batch.B
     tables = [t.view(B, w) if w else torch.full((B, 1), -1, dtype=torch.int32, device=device)
               for t, w in zip(tables, batch.widths)]
@@ -144,8 +178,9 @@ class _DecodeGraph:
 
     def _write_fixed_parts(self) -> None:
         """What is the same for every batch of this width: sequence i brings token i and wants its logits."""
-        tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = self.views
+        tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, late_dst, late_src, *tables = self.views
         width = self.batch.B
+        late_dst[:] = -1
         seq[:] = np.arange(width, dtype=np.int32)
         qsl[:] = np.arange(width + 1, dtype=np.int32)
         rows[:] = seq
@@ -166,8 +201,10 @@ class _DecodeGraph:
     def stage(self, entries: list[StepEntry], cache: CacheManager, starts: list[int]) -> None:
         """Writes this step's batch (every entry one token, logits wanted) into the pinned buffer."""
         self.copied.synchronize()              # the device has read the batch before this one
-        tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = self.views
-        tok[:] = [entry.tokens[0] for entry in entries]
+        tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, late_dst, late_src, *tables = self.views
+        tok[:] = [entry.tokens[0] if entry.late is None else 0 for entry in entries]
+        late_dst[:] = [-1 if entry.late is None else i for i, entry in enumerate(entries)]     # token row i is sequence i
+        late_src[:] = [entry.late or 0 for entry in entries]
         pos[:] = starts
         np.add(pos, 1, out=ctxl)
         for i, entry in enumerate(entries):
@@ -206,10 +243,10 @@ class _DecodeGraph:
 
 
 def _write_padding(views) -> None:
-    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, *tables = views
-    for array in (tok, pos, qsl, ctxl, slots, rows, dtok):
+    tok, pos, seq, qsl, ctxl, slots, rows, dseq, dtok, pseq, late_dst, late_src, *tables = views
+    for array in (tok, pos, qsl, ctxl, slots, rows, dtok, late_src):
         array[:] = 0
-    for array in (seq, dseq, pseq, *tables):
+    for array in (seq, dseq, pseq, late_dst, *tables):
         array[:] = -1
 
 
@@ -234,7 +271,7 @@ class _PaddedGraph:
         n_decode = seqs if decode else 0
         self.batch = batch = _Batch(seqs, tokens, rows, [pages] * len(cache.groups), n_decode, prefill)
         self.device_buffer = torch.zeros(batch.total, dtype=torch.int32, device=runner.device)
-        tok, pos, seq, qsl, ctxl, slots, wanted, dseq, dtok, pseq, *tables = batch.views(self.device_buffer)
+        tok, pos, seq, qsl, ctxl, slots, wanted, dseq, dtok, pseq, _, _, *tables = batch.views(self.device_buffer)
         tables = [t.view(seqs, w) for t, w in zip(tables, batch.widths)]
         # The kernels' launch bounds are those of the padded shape; what a step really holds is in the buffers.
         plan = AttentionPlan(num_decode=n_decode, decode_seqs=dseq, decode_tokens=dtok, num_prefill=prefill,
@@ -311,13 +348,26 @@ class ModelRunner:
             n = len(entry.tokens)
             if n < 1:
                 raise ValueError(f"request {entry.request_id!r} brings no tokens")
-            if min(entry.tokens) < 0 or max(entry.tokens) >= vocab:
+            if entry.late is not None:
+                if n != 1 or entry.late < 0:
+                    raise ValueError(f"request {entry.request_id!r}: a token read on the device is one token")
+            elif min(entry.tokens) < 0 or max(entry.tokens) >= vocab:
                 raise ValueError(f"request {entry.request_id!r} has a token id outside [0, {vocab})")
             for place in entry.want:
                 if not 0 <= place < n:
                     raise ValueError(f"request {entry.request_id!r} wants logits at {place}, but brings {n} tokens")
 
-    def build_context(self, entries: list[StepEntry]) -> StepContext:
+    @staticmethod
+    def _place_late_tokens(batch: _Batch, dev: torch.Tensor, entries: list[StepEntry], late_source) -> None:
+        """Tokens that were sampled on the device and never read: from `late_source` into the batch, on the device."""
+        if not any(e.late is not None for e in entries):
+            return
+        if late_source is None:
+            raise ValueError("an entry's token is to be read on the device, but no tensor of sampled tokens was given")
+        v = batch.views(dev)
+        ops_scatter(v.tok, v.late_dst, v.late_src, late_source)
+
+    def build_context(self, entries: list[StepEntry], late_source: torch.Tensor | None = None) -> StepContext:
         """The batch as device tensors (one staging buffer, one host-to-device copy)."""
         cache = self.cache
         starts = [cache.length(e.request_id) for e in entries]
@@ -330,6 +380,7 @@ class ModelRunner:
         host = torch.empty(batch.total, dtype=torch.int32, pin_memory=self._pinned)
         _fill(batch, host.numpy(), entries, cache, starts)
         dev = host.to(self.device, non_blocking=True)
+        self._place_late_tokens(batch, dev, entries, late_source)
         decode_bound = max((t for t, c in zip(totals, counts) if c == 1), default=0)
         return _context(batch, dev, self.device, counts, totals, self.decode_splits, decode_bound)
 
@@ -382,7 +433,8 @@ class ModelRunner:
             graph = self._padded_graphs[key] = _PaddedGraph(self, *key, max_len)
         return graph
 
-    def _replay(self, graph: _DecodeGraph | _PaddedGraph, entries: list[StepEntry]) -> torch.Tensor:
+    def _replay(self, graph: _DecodeGraph | _PaddedGraph, entries: list[StepEntry],
+                late_source: torch.Tensor | None = None) -> torch.Tensor:
         if graph.graph is None:
             try:
                 graph.capture(self)
@@ -395,14 +447,16 @@ class ModelRunner:
         wanted = graph.stage(entries, self.cache, starts)
         graph.device_buffer.copy_(graph.host, non_blocking=True)
         graph.copied.record()
+        self._place_late_tokens(graph.batch, graph.device_buffer, entries, late_source)
         graph.graph.replay()
         self.graph_launches += graph.launches
         self.graph_replays += 1
         return graph.logits.clone() if wanted is None else graph.logits[:wanted].clone()
 
     # ----------------------------------------------------------------- step
-    def step(self, entries: list[StepEntry]) -> torch.Tensor:
-        """Logits [number of wanted places, vocab], in the order of `entries` and of each entry's `want`."""
+    def step(self, entries: list[StepEntry], late_source: torch.Tensor | None = None) -> torch.Tensor:
+        """Logits [number of wanted places, vocab], in the order of `entries` and of each entry's `want`.
+        `late_source` (int32, on the device): where the tokens of entries marked `late` are read from."""
         self._validate(entries)
         ids = [e.request_id for e in entries]
         totals = [self.cache.length(e.request_id) + len(e.tokens) for e in entries]
@@ -410,9 +464,9 @@ class ModelRunner:
         try:
             graph = self._graph_for(entries, totals) or self._padded_graph_for(entries, totals)
             if graph is not None:
-                logits = self._replay(graph, entries)
+                logits = self._replay(graph, entries, late_source)
             else:
-                context = self.build_context(entries)
+                context = self.build_context(entries, late_source)
                 with kernels.on_current_stream():
                     logits = self.model.forward(context, self.layer_caches)
         except BaseException:

@@ -92,6 +92,9 @@ class Sequence:
     rules: StopRules | None = None
     # Tokens the request may hold at most (prompt and output): what the cache must have room for.
     final_length: int = 0
+    # The token that ends the request by its length has been launched (its value is still to be read): the request
+    # runs no further step, though it is not finished before that token has arrived.
+    last_token_launched: bool = False
 
     def __post_init__(self) -> None:
         if self.rules is None:
@@ -102,6 +105,11 @@ class Sequence:
     @property
     def is_finished(self) -> bool:
         return self.status in _FINISHED
+
+    @property
+    def wants_step(self) -> bool:
+        """Whether the scheduler has anything to give this request."""
+        return self.status not in _FINISHED and not self.last_token_launched
 
     def __len__(self) -> int:
         return len(self.prompt_token_ids) + len(self.output_token_ids)
@@ -127,6 +135,12 @@ class Sequence:
                 break
             n += 1
         return n
+
+    @property
+    def read_token_ids(self) -> list[int]:
+        """The output tokens whose values the host has (all of them once the request is finished)."""
+        unread = self.num_unread_tokens
+        return self.output_token_ids[:len(self.output_token_ids) - unread] if unread else list(self.output_token_ids)
 
     def next_tokens(self, count: int) -> list[int]:
         """The `count` tokens after the computed ones: from the prompt or from the output, never both

@@ -32,6 +32,7 @@ _functions: dict[str, ctypes._CFuncPtr] = {}
 
 _SIGNATURES = {
     "li_embedding": ("elementwise", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "li_scatter_tokens": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "li_rmsnorm": ("elementwise", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                    c_int, c_void_p]),
     "li_add": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
@@ -212,6 +213,18 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
     _check(_fn("li_embedding")(_code(out), ids.data_ptr(), table.data_ptr(), out.data_ptr(), tokens, width,
                                table.shape[0], _ptr(error_flag), _stream()), "embedding")
     return out
+
+
+def scatter_tokens(tokens: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, source: torch.Tensor) -> torch.Tensor:
+    """tokens[dst[i]] = source[src[i]] wherever dst[i] >= 0 (all int32): sampled token ids that never left the
+    device take their places in the next step's batch."""
+    _on_gpu(tokens, dst, src, source)
+    for t, what in ((tokens, "tokens"), (dst, "dst"), (src, "src"), (source, "source")):
+        _int32(t, what)
+    assert dst.numel() == src.numel()
+    _check(_fn("li_scatter_tokens")(tokens.data_ptr(), dst.data_ptr(), src.data_ptr(), source.data_ptr(), dst.numel(),
+                                    _stream()), "scatter_tokens")
+    return tokens
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

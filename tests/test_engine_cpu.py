@@ -94,7 +94,7 @@ def test_running_out_of_pages_while_decoding_sheds_the_least_invested(cpu_kernel
     engine = EngineCore(EngineConfig(model=str(model_dirs["tiny_a"]), dtype="float32", device="cpu",
                                      block_size=page, max_num_seqs=4, max_model_len=128, num_gpu_blocks=3))
     engine.load()
-    engine.scheduler.page_gate = None                       # admit regardless, as the reference does
+    engine.scheduler.ledger = None                          # admit regardless, as the reference does
     params = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
     a = engine.add_request("a", tiny_configs.prompt(config["vocab_size"], 30, 0), params)
     b = engine.add_request("b", tiny_configs.prompt(config["vocab_size"], 14, 1), params)
@@ -250,3 +250,43 @@ def test_padded_shapes_of_the_step_graphs():
         assert padded - n < max(16, _pow2(n) // 8)
     assert len(shapes) <= 48
     assert [_pow2(n) for n in (0, 1, 2, 3, 4, 5, 33, 64)] == [1, 1, 2, 4, 4, 8, 64, 64]
+
+
+def test_steps_launched_ahead_give_the_same_outputs(cpu_kernels, model_dirs):
+    """The engine launches a step before it has read the tokens of the step before.  With every kind of ending
+    (a stop id early or late, min_tokens, max_tokens, the context limit), prompts cut by the budget and a cache
+    that makes newcomers wait, the outputs are those of the engine that reads every step before the next."""
+    from liteinfer_b200 import LLM, SamplingParams
+
+    config, _, page = tiny_configs.ALL["tiny_a"]
+    vocab = config["vocab_size"]
+    prompts = _prompts(vocab, (5, 21, 9, 30, 2, 14, 17, 40))
+    common = dict(dtype="float32", device="cpu", block_size=page, max_num_seqs=3, max_model_len=48,
+                  max_num_batched_tokens=12, num_gpu_blocks=7)
+    with LLM(str(model_dirs["tiny_a"]), async_scheduling=False, **common) as llm:
+        free = [o.token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12))]
+    params = [
+        SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[free[0][0]]),            # the very first token ends it
+        SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[free[1][4]]),
+        SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[free[2][1]], min_tokens=5),
+        SamplingParams(temperature=0.0, max_tokens=100),                                          # the context limit
+        SamplingParams(temperature=0.0, max_tokens=1),
+        SamplingParams(temperature=0.0, max_tokens=12, stop=[" " + str(free[5][3])]),            # a stop string
+        SamplingParams(temperature=0.7, top_k=5, seed=3, max_tokens=9),                           # a seeded stream
+        SamplingParams(temperature=0.0, max_tokens=7, stop_token_ids=[free[7][6]]),              # stop id and length at once
+    ]
+    runs = []
+    for ahead in (False, True):
+        with LLM(str(model_dirs["tiny_a"]), async_scheduling=ahead, **common) as llm:
+            outs = llm.generate(prompts, params)
+            runs.append([(o.token_ids, o.finish_reason, o.text) for o in outs])
+            assert llm.stats.num_requests_aborted == 0
+            llm.engine.step()
+            cache = llm.engine.runner.cache
+            cache.check_invariants()
+            assert all(g.allocator.num_held == 0 for g in cache.groups) and cache.slots.num_held == 0
+            assert not llm.engine.has_unfinished()
+    assert runs[0] == runs[1]
+    assert runs[1][0][0] == free[0][:1] and runs[1][0][1] == "stop"
+    assert runs[1][3][1] == "length" and len(prompts[3]) + len(runs[1][3][0]) == 48
+    assert all(-1 not in tokens for tokens, _, _ in runs[1])

@@ -53,10 +53,9 @@ def _plant_in_batch(monkeypatch, change):
 
     def damaged(batch, flat, entries, cache, starts):
         original(batch, flat, entries, cache, starts)
-        names = ("tok", "pos", "seq", "qsl", "ctxl", "slots", "rows", "dseq", "dtok", "pseq")
         views = batch.views(flat)
-        arrays = dict(zip(names, views))
-        arrays["tables"] = [t.reshape(batch.B, w) for t, w in zip(views[len(names):], batch.widths) if w]
+        arrays = {name: getattr(views, name) for name in ("tok", "pos", "seq", "qsl", "ctxl", "slots", "rows", "dseq", "dtok", "pseq")}
+        arrays["tables"] = [t.reshape(batch.B, w) for t, w in zip(views.tables, batch.widths) if w]
         change(batch, arrays, entries)
 
     monkeypatch.setattr(runner_module, "_fill", damaged)

@@ -86,21 +86,37 @@ def test_seats_limit_admission():
     assert [s.request_id for s in _run_step(sched).seqs] == ["r1", "r2"]
 
 
-def test_page_gate_makes_newcomers_wait_instead_of_fail():
-    free = {"pages": 3}
-    gate = lambda seq, admitted: sum(-(-len(s) // 4) for s in [seq, *admitted]) <= free["pages"]
-    sched = Scheduler(EngineConfig(model="m", max_num_seqs=4), page_gate=gate)
-    sched.add(_seq("a", 10)); sched.add(_seq("b", 10))
+class _Ledger:
+    """A cache of `pages` pages of four tokens that keeps every key: what the scheduler asks of the cache manager."""
+
+    def __init__(self, pages: int) -> None:
+        self.pages = pages
+
+    def can_hold(self, final_lengths, largest_step):
+        return sum(-(-n // 4) for n in final_lengths) <= self.pages
+
+
+def test_newcomers_wait_for_pages_instead_of_failing():
+    ledger = _Ledger(4)                                     # a to its end (10 + 2 tokens) needs three pages
+    sched = Scheduler(EngineConfig(model="m", max_num_seqs=4), ledger=ledger)
+    sched.add(_seq("a", 10, max_tokens=2)); sched.add(_seq("b", 10, max_tokens=2))
     out = _run_step(sched)
     assert [s.request_id for s in out.seqs] == ["a"] and [s.request_id for s in sched.waiting] == ["b"]
-    free["pages"] = 0
     assert [s.request_id for s in _run_step(sched).seqs] == ["a"]     # b still waits; a decodes on
-    free["pages"] = 5
+    ledger.pages = 6
     assert [s.request_id for s in _run_step(sched).seqs] == ["a", "b"]
 
 
+def test_a_cache_that_holds_exactly_n_requests_seats_n_arriving_at_once():
+    sched = Scheduler(EngineConfig(model="m", max_num_seqs=8), ledger=_Ledger(9))     # three pages a request
+    for i in range(5):
+        sched.add(_seq(f"r{i}", 10, max_tokens=2))
+    assert [s.request_id for s in _run_step(sched).seqs] == ["r0", "r1", "r2"]
+    assert len(sched.waiting) == 2
+
+
 def test_a_request_that_can_never_fit_is_let_through_to_fail_alone():
-    sched = Scheduler(EngineConfig(model="m", max_num_seqs=4), page_gate=lambda seq, admitted: False)
+    sched = Scheduler(EngineConfig(model="m", max_num_seqs=4), ledger=_Ledger(0))
     sched.add(_seq("huge", 50))
     assert [s.request_id for s in sched.schedule().seqs] == ["huge"]   # nothing runs: waiting would never end
 

@@ -30,6 +30,12 @@ def embedding(ids, table, out, error_flag=None):
     return out
 
 
+def scatter_tokens(tokens, dst, src, source):
+    live = dst >= 0
+    tokens[dst[live].long()] = source[src[live].long()]
+    return tokens
+
+
 def rmsnorm(x, weight, eps, out, delta=None, rows=None, write_residual=False):
     dtype = x.dtype
     src = x if rows is None else x[rows.long()]
@@ -264,5 +270,5 @@ def fused_decode_supports(*args) -> bool:
     return False      # the stand-ins rotate and store in `rope_kv_write`, never inside the attention
 
 
-ALL = ("fused_decode_supports", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
+ALL = ("fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
        "gated_linear", "gemm_error_flag", "error_flags", "token_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
