@@ -30,13 +30,11 @@ DEFAULT_MAX_MIXED_ISL = 2048
 
 
 def percentile(values: list[float], p: float) -> float:
-    ordered = sorted(values)
-    if len(ordered) == 1:
-        return ordered[0]
-    pos = (p / 100) * (len(ordered) - 1)
-    low = int(pos)
-    high = min(low + 1, len(ordered) - 1)
-    return ordered[low] + (ordered[high] - ordered[low]) * (pos - low)
+    """The p-th percentile with linear interpolation between neighbours (what the reference's summaries use,
+    benchmarks/stats.py:17-30)."""
+    import numpy as np
+
+    return float(np.percentile(np.asarray(values, dtype=np.float64), p))
 
 
 def make_prompts(vocab_size: int, isl: int | None, num_samples: int, max_isl: int, seed: int) -> list[list[int]]:
@@ -51,18 +49,22 @@ def make_prompts(vocab_size: int, isl: int | None, num_samples: int, max_isl: in
 
 
 def throughput_summary(output_tokens: int, num_requests: int, wall_time_s: float) -> dict:
-    return {"output_tokens_per_s": output_tokens / wall_time_s, "requests_per_s": num_requests / wall_time_s,
+    """Every request offered at once: what came out per second of wall time (benchmarks/stats.py:53-62)."""
+    per_second = 1.0 / wall_time_s
+    return {"output_tokens_per_s": output_tokens * per_second, "requests_per_s": num_requests * per_second,
             "wall_time_s": wall_time_s}
 
 
 def latency_summary(ttft_s: list[float], e2e_s: list[float], osl: int) -> dict:
+    """One request at a time: percentiles of the time to the first token, of the time per further token (derived:
+    what is left of the end-to-end time spread over the osl - 1 further tokens) and of the end-to-end time
+    (benchmarks/stats.py:65-82)."""
     if osl < 2:
         raise ValueError("latency mode needs --osl >= 2 to derive the time per further token")
-    itl_s = [(e2e - ttft) / (osl - 1) for ttft, e2e in zip(ttft_s, e2e_s, strict=True)]
-    ms = lambda values, p: percentile(values, p) * 1000
-    return {"ttft_p50_ms": ms(ttft_s, 50), "ttft_p95_ms": ms(ttft_s, 95), "ttft_p99_ms": ms(ttft_s, 99),
-            "itl_p50_ms": ms(itl_s, 50), "itl_p95_ms": ms(itl_s, 95), "itl_p99_ms": ms(itl_s, 99),
-            "e2e_p50_ms": ms(e2e_s, 50)}
+    series = {"ttft": ttft_s, "itl": [(whole - first) / (osl - 1) for first, whole in zip(ttft_s, e2e_s, strict=True)]}
+    summary = {f"{name}_p{p}_ms": percentile(values, p) * 1e3 for name, values in series.items() for p in (50, 95, 99)}
+    summary["e2e_p50_ms"] = percentile(e2e_s, 50) * 1e3
+    return summary
 
 
 def _sync(llm) -> None:

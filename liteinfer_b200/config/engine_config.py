@@ -71,37 +71,31 @@ class EngineConfig:
 
     def __post_init__(self) -> None:
         self.dtype = parse_dtype(self.dtype)
-        if self.max_num_seqs < 1:
-            raise ValueError("max_num_seqs must be >= 1")
-        if self.max_model_len < 1:
-            raise ValueError("max_model_len must be >= 1")
-        if self.block_size < 1:
-            raise ValueError("block_size must be >= 1")
+        at_least_one = ("max_num_seqs", "max_model_len", "block_size", "max_waiting_seqs")
+        optional_at_least_one = ("paged_decode_splits", "num_gpu_blocks")
+        for name in at_least_one + optional_at_least_one:
+            value = getattr(self, name)
+            if value is None and name in optional_at_least_one:
+                continue
+            if value < 1:
+                raise ValueError(f"{name}={value}: it counts something and must be at least 1")
         if self.max_num_batched_tokens is not None and self.max_num_batched_tokens < self.max_num_seqs:
-            raise ValueError(
-                f"max_num_batched_tokens={self.max_num_batched_tokens} must be >= "
-                f"max_num_seqs={self.max_num_seqs}"
-            )
-        if self.max_waiting_seqs < 1:
-            raise ValueError("max_waiting_seqs must be >= 1")
-        if self.paged_decode_splits is not None and self.paged_decode_splits < 1:
-            raise ValueError("paged_decode_splits must be >= 1")
-        if not 0 < self.gpu_memory_utilization <= 1:
-            raise ValueError("gpu_memory_utilization must be in (0, 1]")
-        if self.num_gpu_blocks is not None and self.num_gpu_blocks < 1:
-            raise ValueError("num_gpu_blocks must be >= 1")
+            # A step must have room for one token of every seated request, or decoding requests would starve a prompt.
+            raise ValueError(f"max_num_batched_tokens={self.max_num_batched_tokens} is below max_num_seqs="
+                             f"{self.max_num_seqs}: a step could not decode every seated request")
+        if not 0.0 < self.gpu_memory_utilization <= 1.0:
+            raise ValueError(f"gpu_memory_utilization={self.gpu_memory_utilization}: a share of the device's memory in (0, 1]")
         if self.attn_implementation not in (None, "paged"):
-            raise ValueError(
-                f"attn_implementation {self.attn_implementation!r} does not exist here; "
-                "this engine has one attention path, 'paged'"
-            )
+            raise ValueError(f"attn_implementation={self.attn_implementation!r}: this engine has one attention path, "
+                             "'paged' (its own kernels over the paged cache)")
 
     @property
     def token_budget(self) -> int:
-        """`max_num_batched_tokens`, with None resolved to the most a step can ever hold."""
-        if self.max_num_batched_tokens is not None:
-            return self.max_num_batched_tokens
-        return self.max_num_seqs * self.max_model_len
+        """Tokens a step may compute: `max_num_batched_tokens`, or when that is None as many as the seats could
+        ever bring (which cuts no prompt)."""
+        if self.max_num_batched_tokens is None:
+            return self.max_num_seqs * self.max_model_len
+        return self.max_num_batched_tokens
 
     def resolved_device(self) -> torch.device:
         if self.device == "auto":

@@ -12,7 +12,6 @@ sequence without decoding the whole prefix each step (tokenizer.py:50-78).
 from __future__ import annotations
 
 import json
-from dataclasses import dataclass
 from pathlib import Path
 
 _REPLACEMENT_CHAR = "�"
@@ -91,32 +90,41 @@ def load_tokenizer(model_dir: str | Path, vocab_size: int, eos_token_ids: tuple[
     return TokenIdTokenizer(vocab_size, eos_token_ids or _eos_ids_from_files(model_dir, None))
 
 
-@dataclass
 class IncrementalDetokenizer:
-    """Each step decodes a short window ending at the new token and the same window one
-    token shorter, and keeps the difference; a window that ends mid-character (U+FFFD)
-    waits for the token that completes it."""
+    """The text of a growing list of token ids without decoding all of it at every step.
 
-    text: str = ""
-    prefix_offset: int = 0
-    read_offset: int = 0
+    A tokenizer's text for a token can depend on its neighbours (spaces, bytes of one character spread over two
+    tokens), so new tokens are decoded together with a few settled tokens before them, and what those settled
+    tokens decode to alone is cut off the front.  Text that ends in the replacement character is an unfinished
+    character: it is held back until the token that completes it has come.  (The reference does the same with a
+    prefix offset and a read offset, liteinfer/tokenizer.py:50-78.)
+    """
+
+    CONTEXT = 6         # settled tokens decoded again in front of the new ones
+
+    def __init__(self) -> None:
+        self.text = ""
+        self.settled = 0            # tokens whose text is in `text`
+
+    def _fresh(self, tokenizer, token_ids: list[int]) -> str:
+        """What the tokens after the settled ones add to the text."""
+        anchor = max(0, self.settled - self.CONTEXT)
+        before = tokenizer.decode(token_ids[anchor:self.settled]) if self.settled > anchor else ""
+        whole = tokenizer.decode(token_ids[anchor:])
+        return whole[len(before):] if len(whole) > len(before) else ""
 
     def update(self, tokenizer, token_ids: list[int]) -> str:
-        prefix = tokenizer.decode(token_ids[self.prefix_offset:self.read_offset])
-        whole = tokenizer.decode(token_ids[self.prefix_offset:])
-        if len(whole) <= len(prefix) or whole.endswith(_REPLACEMENT_CHAR):
-            return self.text
-        self.text += whole[len(prefix):]
-        self.prefix_offset = self.read_offset
-        self.read_offset = len(token_ids)
+        if len(token_ids) > self.settled:
+            fresh = self._fresh(tokenizer, token_ids)
+            if fresh and not fresh.endswith(_REPLACEMENT_CHAR):
+                self.text += fresh
+                self.settled = len(token_ids)
         return self.text
 
     def catch_up(self, tokenizer, token_ids: list[int]) -> str:
-        """The text of all of `token_ids` for a detokenizer that was not called at every step: what `update`
+        """The text of all of `token_ids`, for a detokenizer that was not called at every step: what `update`
         gives, and if the ids end inside a character, everything before that character."""
         text = self.update(tokenizer, token_ids)
-        if self.read_offset == len(token_ids):
+        if self.settled == len(token_ids):
             return text
-        prefix = tokenizer.decode(token_ids[self.prefix_offset:self.read_offset])
-        whole = tokenizer.decode(token_ids[self.prefix_offset:])
-        return text + whole[len(prefix):].rstrip(_REPLACEMENT_CHAR)
+        return text + self._fresh(tokenizer, token_ids).rstrip(_REPLACEMENT_CHAR)
