@@ -24,6 +24,7 @@
 // With the rotary encoding fused in (see li_paged_attention_mma) the owner of the newest position writes the
 // rotated key and the value to their page and, for its own use, takes them from shared memory.
 #include <map>
+#include <mutex>
 #include <tuple>
 
 #include "attention_mma.cuh"
@@ -378,6 +379,8 @@ template <int D, int kRing> constexpr size_t stream_smem() { return (size_t)kWar
 // The pool [pages, kv_heads, page_size, D] as a 2-D map of rows of D with boxes of 16 rows x 64 dimensions.
 static bool make_group_map(CUtensorMap* map, const void* pool, long rows, int head_dim) {
   static std::map<std::tuple<const void*, long, int>, CUtensorMap> cache;
+  static std::mutex guard;                 // several host threads may launch (an asyncio engine beside its caller)
+  std::lock_guard<std::mutex> lock(guard);
   const auto key = std::make_tuple(pool, rows, head_dim);
   const auto found = cache.find(key);
   if (found != cache.end()) {

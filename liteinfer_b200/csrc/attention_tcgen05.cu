@@ -31,6 +31,7 @@
 // their value rows are zeroed in shared memory, so an unwritten slot of a page cannot leak.
 // Every mbarrier wait is bounded (see tcgen05.cuh); a wait that runs out sets `error_flag`.
 #include <map>
+#include <mutex>
 #include <tuple>
 
 #include "tcgen05.cuh"
@@ -416,6 +417,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 // page of one head.
 static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int page_size, int head_dim) {
   static std::map<std::tuple<const void*, long, int, int>, CUtensorMap> cache;
+  static std::mutex guard;                 // several host threads may launch (an asyncio engine beside its caller)
+  std::lock_guard<std::mutex> lock(guard);
   const auto key = std::make_tuple(pool, rows, page_size, head_dim);
   const auto found = cache.find(key);
   if (found != cache.end()) {

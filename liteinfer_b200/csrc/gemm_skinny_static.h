@@ -9,8 +9,9 @@
 //
 //   out[M, N] = x[M, K] @ w[N, K]^T (+ bias[N])        bfloat16, row-major, 1 <= M <= 64
 //
-// Same kernel and same results as li_gemm_skinny (gemm_skinny.cu); only where the partial sums of
-// the k slices are kept differs.
+// The kernel template is li_gemm_skinny's (gemm_skinny.cu), run with the plan of narrow blocks and
+// k slices (the form that needs scratch); li_gemm_skinny itself may choose wide blocks instead, so
+// the two add their products in different orders and may differ in the last bit of a result.
 //
 // Limits and rules
 //   * The scratch is LI_STATIC_SCRATCH_FLOATS floats (1 MiB) plus LI_STATIC_COUNTERS counters
@@ -29,6 +30,10 @@
 //     overlap on the GPU (different streams, or graphs replayed side by side) race on the array:
 //     order them.
 //   * K must be a multiple of 8 and x, w 16-byte aligned, as for li_gemm_skinny.
+//   * The first call on a device must come from one thread at a time (the look-up of the array's
+//     address is not locked), and the device's primary context is assumed: the address is kept per
+//     device ordinal, so a host that runs two CUDA contexts on one device must make its calls in
+//     the context that made the first.
 //
 // Returns 0, a cudaError_t, or one of the LI_ERR_* codes; li_static_error_string() names them.
 #pragma once
@@ -38,6 +43,8 @@
 
 #define LI_STATIC_SCRATCH_FLOATS (1u << 18)
 #define LI_STATIC_COUNTERS 1024
+#define LI_ERR_UNSUPPORTED 100001              /* sizes the kernel refuses: M outside 1..64, K not a multiple of 8 */
+#define LI_ERR_ALIGNMENT 100002                /* x or w not 16-byte aligned */
 #define LI_ERR_STATIC_SCRATCH_TOO_SMALL 100003
 
 #ifdef __cplusplus

@@ -330,6 +330,8 @@ static int plan_and_launch(const CUtensorMap& map, const StreamParams& p, cudaSt
   const char plan = forced ? forced[0] : (tiles <= 2 * sms ? 'b' : 'c');
   switch (plan) {
     case 'a': return launch_stream_gemm<NT, 7, 4, true>(map, p, min(sms, (tiles + 6) / 7), stream);
+    case 'e': return launch_stream_gemm<NT, 8, 5, false>(map, p, tiles <= 2 * sms ? tiles : sms, stream);
+    case 'f': return launch_stream_gemm<NT, 12, 3, false>(map, p, tiles <= 2 * sms ? tiles : sms, stream);
     case 'd': return launch_stream_gemm<NT, 6, 3, true>(map, p, min(2 * sms, (tiles + 5) / 6), stream);
     case 'c':
       // (with at most three chunks of k a warp and one tile of rows, a warp keeps its share of x in registers)

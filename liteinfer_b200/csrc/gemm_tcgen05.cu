@@ -19,6 +19,7 @@
 // `error_flag` and the block winds down (tensor memory is freed on every path), so a fault in
 // the choreography shows up as an error code, not as a hang.
 #include <map>
+#include <mutex>
 #include <tuple>
 
 #include "tcgen05.cuh"
@@ -410,6 +411,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
   // Encoding is pure host arithmetic on (pointer, sizes): the same matrix gives the same map, so maps are kept.
   static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
+  static std::mutex guard;                 // several host threads may launch (an asyncio engine beside its caller)
+  std::lock_guard<std::mutex> lock(guard);
   const auto key = std::make_tuple(ptr, rows, K, box_rows);
   const auto found = cache.find(key);
   if (found != cache.end()) {

@@ -709,3 +709,67 @@ def test_gemm_stream_epilogues(M, inter, K, act):
     assert torch.equal(stream, want)
     torch.testing.assert_close(stats.sumsq.sum(0), want.float().pow(2).sum(-1), rtol=1e-5, atol=1e-5)
     assert ops.gemm_error_flag("cuda:0") == 0
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("w,ctx", [(11, 50), (64, 129), (65, 129), (16, 81), (100, 700)])
+def test_window_edge_on_the_tensor_core_paths(d, w, ctx, monkeypatch):
+    """With a window of w the key at distance w - 1 is seen and the key at distance w is not, on every path that
+    bfloat16 heads of 64 and 128 take: single tokens with their keys unsplit and split, through the kernel with
+    TMA rings and the one with shared-memory tiles, with the rotary encoding and the cache write fused in, and a
+    portion of three tokens through the tcgen05 kernel.  The edge falls inside a tile of 64 keys, on its first key,
+    on its last, and on a page's edge."""
+    from liteinfer_b200 import ops
+
+    heads, kv_heads, page, dt = 8, 2, 16, torch.bfloat16
+    inv_freq = (1.0 / (500000.0 ** (torch.arange(0, d, 2).float() / d))).cuda()
+
+    def planted(q_len, distance, rotate):
+        case = _paged_case(dt, heads, kv_heads, d, page, [q_len], [ctx], seed=w + distance, poison=False)
+        qkv, k_pool, v_pool = case["qkv"], case["k_pool"], case["v_pool"]
+        rotated = qkv.clone()          # what the queries look like once they are rotated (or not)
+        ref.rope_kv_write(rotated, case["positions"], case["seq_of"], case["table"], k_pool.clone(), v_pool.clone(),
+                          inv_freq if rotate else None, heads, kv_heads, d, d if rotate else 0, store=False)
+        far = ctx - 1 - distance
+        pg, off = int(case["table"][0, far // page]), far % page
+        last = rotated[q_len - 1, :heads * d].view(heads, d)
+        for h in range(kv_heads):
+            k_pool[pg, h, off] = (last[h * (heads // kv_heads)].float() * 10).to(dt)
+            v_pool[pg, h, off] = 100.0
+        return case, qkv, k_pool, v_pool
+
+    def sees(out, q_len):
+        return float(out[q_len - 1].view(heads, d)[0].float().mean()) > 50
+
+    for distance, seen in ((w - 1, True), (w, False)):
+        # single tokens, keys and values already in their pages
+        for stream in ("1", "0"):
+            monkeypatch.setenv("LITEINFER_DECODE_STREAM", stream)
+            for splits in (1, 3):
+                case, qkv, k_pool, v_pool = planted(1, distance, False)
+                ops.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_pool, v_pool, None, heads,
+                                  kv_heads, d, 0)
+                out = torch.empty(1, heads * d, dtype=dt, device="cuda")
+                ops.paged_attention(qkv, qkv.shape[1], out, k_pool, v_pool, case["table"], case["qsl"], case["ctx"], 1, 1,
+                                    heads, kv_heads, d, 1.0, w, plan=_plan_for([1], [ctx]), decode_splits=splits)
+                assert sees(out, 1) == seen, (stream, splits, distance)
+        monkeypatch.setenv("LITEINFER_DECODE_STREAM", "1")
+        # the rotary encoding and the cache write inside the attention launch
+        for splits in (1, 3):
+            case, qkv, k_pool, v_pool = planted(1, distance, True)
+            q_width, kv_width = heads * d, kv_heads * d
+            newest = ops.NewestToken(inv_freq, qkv[:, q_width:], qkv[:, q_width + kv_width:])
+            out = torch.empty(1, heads * d, dtype=dt, device="cuda")
+            ops.paged_attention(qkv, qkv.shape[1], out, k_pool, v_pool, case["table"], case["qsl"], case["ctx"], 1, 1,
+                                heads, kv_heads, d, 1.0, w, plan=_plan_for([1], [ctx]), decode_splits=splits, newest=newest)
+            assert sees(out, 1) == seen, ("fused", splits, distance)
+        # a portion of three tokens: the tcgen05 kernel
+        case, qkv, k_pool, v_pool = planted(3, distance, False)
+        ops.rope_kv_write(qkv, case["positions"], case["seq_of"], case["table"], k_pool, v_pool, None, heads, kv_heads, d, 0)
+        assert ctx - 1 - distance < ctx - 3      # the planted key lies before the portion's own keys
+        out = torch.empty(3, heads * d, dtype=dt, device="cuda")
+        assert ops.tcgen05_attention_supports(dt, heads, kv_heads, d, page)
+        ops.paged_attention(qkv, qkv.shape[1], out, k_pool, v_pool, case["table"], case["qsl"], case["ctx"], 1, 3,
+                            heads, kv_heads, d, 1.0, w, plan=_plan_for([3], [ctx]))
+        assert sees(out, 3) == seen, ("portion", distance)
+    assert ops.gemm_error_flag("cuda:0") == 0
