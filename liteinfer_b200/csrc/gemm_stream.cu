@@ -173,9 +173,24 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamParams
       }
   }
 
+  // Without that, the warp's share of x for the chunk after the one it multiplies is asked for one chunk ahead, so
+  // that its way from the second-level cache overlaps the wait for the chunk's weights.
+  uint4 xn[4][NT];
+  auto ask_x = [&](int c) {
+    const int k0 = (chunk_first + c * chunk_step) * kChunkK;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int k = k0 + (q >> 1) * 64 + (2 * t + (q & 1)) * 8;
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+        xn[q][j] = (k < K && j * 8 + g < M) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
+    }
+  };
+  if (kCache == 0 && per_tile > 0) ask_x(0);
+
   int n = 0;
   bool gave_up = false;
-  // Waits for item n and multiplies it; `cached` (a compile-time index or -1) says where the warp keeps its x.
+  // Waits for item n and multiplies it; `cached` says where the warp keeps its x for this chunk, if it does.
   auto multiply = [&](int c, const uint4* cached) -> bool {
     request(n + kRing - 1);
     if (!mbar_wait(bars + 8u * (n % kRing), (unsigned)(n / kRing) & 1, p.error_flag, 31)) {
@@ -187,7 +202,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamParams
       return false;
     }
     const unsigned slot = ring + (unsigned)(n % kRing) * kStageBytes;
-    const int k0 = (chunk_first + c * chunk_step) * kChunkK;
+    uint4 xc[4][NT];
+    if (kCache == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) xc[q][j] = xn[q][j];
+      ask_x(c + 1 < per_tile ? c + 1 : 0);      // (every tile meets the same x: after a tile's last chunk comes the first)
+    }
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
 #pragma unroll
@@ -196,11 +218,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const StreamParams
         const unsigned piece = (unsigned)(2 * t + h);
         const unsigned at = slot + (unsigned)b * (kStageBytes / 2) + ((piece ^ swz) << 4);
         const uint4 wl = lds128(at + row_lo), wh = lds128(at + row_hi);
-        const int k = k0 + b * 64 + (int)piece * 8;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-          const uint4 xv = cached ? cached[b * 2 + h]
-                                  : ((k < K && j * 8 + g < M) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero);
+          const uint4 xv = kCache > 0 ? cached[b * 2 + h] : xc[b * 2 + h][j];
           mma_16816(acc[j], wl.x, wh.x, wl.y, wh.y, xv.x, xv.y);
           mma_16816(acc[j], wl.z, wh.z, wl.w, wh.w, xv.z, xv.w);
         }
