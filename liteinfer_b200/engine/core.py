@@ -32,7 +32,7 @@ import torch
 from liteinfer_b200.cache.manager import CacheManager
 from liteinfer_b200.cache.pages import CacheExhaustedError
 from liteinfer_b200.config.engine_config import EngineConfig
-from liteinfer_b200.engine.loading import resolve_model_path
+from liteinfer_b200.engine.loading import make_runner, resolve_model_path
 from liteinfer_b200.engine.metrics import EngineStats, StageTimes, StepMetrics
 from liteinfer_b200.engine.runner import ModelRunner, StepEntry
 from liteinfer_b200.engine.scheduler import Scheduler, shed_order
@@ -105,9 +105,9 @@ class EngineCore:
         eos = tuple(getattr(self.model_config, "eos_token_id", ()) or ())
         self.tokenizer = load_tokenizer(model_dir, model.spec.vocab_size, eos)
         num_pages = self._num_pages(model)
-        cache = CacheManager(model.cache_needs(), model.schedule, self.config.block_size, num_pages,
-                             self.config.max_num_seqs, self.config.dtype, self.device)
-        self.runner = ModelRunner(model, cache, self.config.paged_decode_splits)
+        self.runner = make_runner(model, self.config.dtype, self.device, self.config.block_size, num_pages,
+                                  self.config.max_num_seqs, self.config.paged_decode_splits)
+        cache = self.runner.cache
         self.scheduler.ledger = cache        # admission asks the cache what a request will cost it
         use_graphs = self.config.enable_cuda_graphs
         if use_graphs is None:
