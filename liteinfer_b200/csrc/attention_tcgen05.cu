@@ -413,6 +413,344 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   }
 }
 
+// ---- two query tiles per block ----------------------------------------------------------------------------------
+// For long runs of queries at head size 64: a block owns 256 rows (two tiles of 128: A and B) for one KV head and
+// walks the visible keys in tiles of 128.  One loader and one issuer serve both tiles, so a tile of keys and values is
+// fetched once for twice the rows and the issuer passes five waits per 256 x 128 scores where the kernel above
+// passes eight; each tile has its own group of four softmax warps (one thread per row, 128 scores in registers),
+// so that while one group works on its exponentials the tensor cores multiply for the other.  Tensor memory: S of A
+// and of B (128 columns each, single buffers: a group says when it has read its scores, and S of the next tile
+// of keys may then overwrite them), O of A and of B (64 columns each): 384 of the 512 columns, one block per SM.
+// Probabilities go through shared memory (one buffer per tile; P V of the tile of keys before has read it when the
+// new ones are stored).  Every wait is bounded.
+constexpr int kPairKeys = 128;
+constexpr int kPairStages = 3;
+constexpr int kPairThreads = 320;      // loader, issuer, two groups of four softmax warps
+
+__global__ void __launch_bounds__(kPairThreads, 1)
+attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                              const TcAttnParams p) {
+  constexpr int D = 64;
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  constexpr unsigned kQBytes = kRows * 64 * 2;                 // 16 KB: 128 rows x 64 dimensions
+  constexpr unsigned kPSubBytes = kRows * 64 * 2;              // 16 KB: 128 rows x 64 keys
+  constexpr unsigned kStageBytes = kPairKeys * D * 2;          // 16 KB: 128 keys x 64 dimensions (K or V)
+  const unsigned q_smem = base;                                // tiles A, B
+  const unsigned p_smem = q_smem + 2 * kQBytes;                // tiles A, B x two sub-tiles of 64 keys
+  const unsigned k_smem = p_smem + 4 * kPSubBytes;
+  const unsigned v_smem = k_smem + kPairStages * kStageBytes;
+  const unsigned bars = v_smem + kPairStages * kStageBytes;
+  auto kv_full = [&](int s) { return bars + 8u * s; };
+  auto kv_empty = [&](int s) { return bars + 8u * (kPairStages + s); };
+  auto s_full = [&](int x) { return bars + 8u * (2 * kPairStages + x); };
+  auto s_free = [&](int x) { return bars + 8u * (2 * kPairStages + 2 + x); };
+  auto p_full = [&](int x) { return bars + 8u * (2 * kPairStages + 4 + x); };
+  auto pv_done = [&](int x) { return bars + 8u * (2 * kPairStages + 6 + x); };
+  const unsigned tmem_slot = bars + 8u * (2 * kPairStages + 8);
+  __shared__ unsigned tmem_base_shared;
+  unsigned char* generic_base = smem_raw + (base - smem_addr(smem_raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = p.seq_index ? p.seq_index[blockIdx.y] : blockIdx.y;
+  if (seq < 0) return;        // a place of padding in the list of sequences
+  const int kvh = blockIdx.x;
+  const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
+  const int groups = p.heads / p.kv_heads;
+  const int tq = kRows / groups;                               // query tokens of one tile
+  const int q0 = (int)(gridDim.z - 1 - blockIdx.z) * 2 * tq;   // longest blocks first
+  if (q0 >= q_len) return;
+  const int ctx = p.context_lens[seq];
+  const int block_q = min(2 * tq, q_len - q0);                 // query tokens of this block
+  const int* table = p.block_table + (size_t)seq * p.table_stride;
+  const int first_qpos = ctx - q_len + q0, last_qpos = first_qpos + block_q - 1;
+  const int hi = last_qpos + 1;
+  const int lo = (p.window > 0 && first_qpos - p.window + 1 > 0) ? first_qpos - p.window + 1 : 0;
+  const int tile_lo = lo / kPairKeys, tile_hi = (hi + kPairKeys - 1) / kPairKeys;
+  const int ntiles = tile_hi - tile_lo;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(s_full(x), 1);
+      mbar_init(s_free(x), 4);
+      mbar_init(p_full(x), 4);
+      mbar_init(pv_done(x), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  grid_dependency_wait();
+  const int boxes = kPairKeys / p.page_size;
+  const unsigned box_bytes = (unsigned)p.page_size * 64 * 2;
+  auto load_tile = [&](int t, bool stage_is_new) -> bool {
+    const int stage = t % kPairStages;
+    const unsigned phase = (unsigned)(t / kPairStages) & 1;
+    const int kpos = (tile_lo + t) * kPairKeys + lane * p.page_size;
+    int row = -1;
+    if (lane < boxes && kpos < hi && kpos + p.page_size > lo) {
+      const int page = table[kpos >> p.page_shift];
+      if (page >= 0 && page < p.num_pages) row = (page * p.kv_heads + kvh) * p.page_size;
+    }
+    const int valid = __popc(__ballot_sync(0xffffffffu, row >= 0));
+    bool fine = true;
+    if (lane == 0) {
+      if (!stage_is_new) fine = mbar_wait(kv_empty(stage), phase ^ 1, p.error_flag, 41);
+      if (fine) mbar_expect_tx(kv_full(stage), 2 * valid * box_bytes);
+    }
+    fine = __shfl_sync(0xffffffffu, fine, 0);
+    if (!fine) return false;
+    if (row >= 0) {
+      tma_load_2d(k_smem + stage * kStageBytes + lane * box_bytes, &map_k, kv_full(stage), 0, row);
+      tma_load_2d(v_smem + stage * kStageBytes + lane * box_bytes, &map_v, kv_full(stage), 0, row);
+    }
+    return true;
+  };
+  const int tiles_ahead = min(kPairStages, ntiles);
+  if (warp == 0) {
+    __syncwarp();
+    for (int t = 0; t < tiles_ahead; ++t) load_tile(t, true);
+  }
+  // Q: each softmax thread copies its row of its tile (128 bytes) into the swizzled tile; rows of padding are zero.
+  const int x_of_warp = warp >= 6 ? 1 : 0;                     // which tile a softmax warp belongs to
+  const int tile_q0 = q0 + x_of_warp * tq;                     // first query token of that tile
+  const int rows_used = max(0, min(tq, q_len - tile_q0)) * groups;
+  if (warp >= 2) {
+    const int row = (warp & 3) * 32 + lane;
+    uint4 v[8];
+    if (row < rows_used) {
+      const int qi = tile_q0 + row / groups, head = kvh * groups + row % groups;
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + qi) * p.q_row_stride + (size_t)head * D);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[c] = src[c];
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[c] = make_uint4(0, 0, 0, 0);
+    }
+    unsigned char* dst = generic_base + (q_smem - base) + x_of_warp * kQBytes + row * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = v[c];
+    fence_async_shared();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  if (threadIdx.x == 0) {
+    unsigned v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(tmem_slot));
+    tmem_base_shared = v;
+  }
+  __syncthreads();
+  const unsigned tmem_base = tmem_base_shared;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ loader
+    for (int t = tiles_ahead; t < ntiles; ++t)
+      if (!load_tile(t, false)) break;
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ issuer
+    if (lane == 0) {
+      constexpr unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(kPairKeys >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
+      constexpr unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
+      const unsigned long long desc_q = umma_desc(q_smem), desc_k = umma_desc(k_smem), desc_v = umma_desc(v_smem),
+                               desc_p = umma_desc(p_smem);
+      // S of tile t for query tile x; its buffer is free once the group has read S of tile t - 1.
+      auto issue_s = [&](int t, int x) -> bool {
+        if (t > 0 && !mbar_wait(s_free(x), (unsigned)(t - 1) & 1, p.error_flag, 43)) return false;
+        tcgen05_fence_after();
+        const unsigned long long dk = desc_k + (unsigned long long)(((t % kPairStages) * kStageBytes) >> 4);
+        const unsigned long long dq = desc_q + (unsigned long long)((x * kQBytes) >> 4);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem_base + x * 128u, dq + (unsigned long long)((k * 32) >> 4), dk + (unsigned long long)((k * 32) >> 4),
+                    idesc_s, k > 0);
+        umma_commit(s_full(x));
+        return true;
+      };
+      auto issue_both = [&](int t) -> bool {
+        if (!mbar_wait(kv_full(t % kPairStages), (unsigned)(t / kPairStages) & 1, p.error_flag, 42)) return false;
+        tcgen05_fence_after();
+        return issue_s(t, 0) && issue_s(t, 1);
+      };
+      bool ok = ntiles > 0 && issue_both(0);
+      for (int t = 0; ok && t < ntiles; ++t) {
+        if (t + 1 < ntiles && !issue_both(t + 1)) { ok = false; break; }
+        const int stage = t % kPairStages;
+        const unsigned long long dv = desc_v + (unsigned long long)((stage * kStageBytes) >> 4);
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (!mbar_wait(p_full(x), (unsigned)t & 1, p.error_flag, 44)) { ok = false; break; }
+          tcgen05_fence_after();
+          const unsigned long long dp = desc_p + (unsigned long long)((x * 2 * kPSubBytes) >> 4);
+#pragma unroll
+          for (int k = 0; k < kPairKeys / 16; ++k)
+            umma_bf16(tmem_base + 256u + x * 64u, dp + (unsigned long long)(((k / 4) * kPSubBytes + (k % 4) * 32) >> 4),
+                      dv + (unsigned long long)((k * 16 * 128) >> 4), idesc_pv, t > 0 || k > 0);
+          umma_commit(pv_done(x));
+        }
+        if (ok) umma_commit(kv_empty(stage));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax of tile x
+    const int x = x_of_warp;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const unsigned lane_field = (unsigned)(quarter * 32) << 16;
+    const unsigned tmem_s = tmem_base + x * 128u, tmem_o = tmem_base + 256u + x * 64u;
+    const int tile_first_qpos = ctx - q_len + tile_q0;
+    const int tile_last_qpos = tile_first_qpos + max(rows_used / groups, 1) - 1;
+    const int qpos = row < rows_used ? tile_first_qpos + row / groups : -1;
+    const int group_thread = threadIdx.x - (x ? 192 : 64);    // 0..127 within the group
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int t = 0; ok && t < ntiles; ++t) {
+      const int stage = t % kPairStages;
+      const int key0 = (tile_lo + t) * kPairKeys;
+      if (!mbar_wait(s_full(x), (unsigned)t & 1, p.error_flag, 45)) { ok = false; break; }
+      tcgen05_fence_after();
+      unsigned sc[4][32];
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_load32(tmem_s + lane_field + c * 32, sc[c]);
+      tmem_load_wait();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free(x));      // S of the next tile of keys may overwrite these columns
+
+      const bool all_visible = rows_used > 0 && key0 + kPairKeys - 1 <= tile_first_qpos &&
+                               (p.window <= 0 || key0 > tile_last_qpos - p.window);
+      float mx = m;
+      if (all_visible && qpos >= 0) {
+        float part[4] = {m, m, m, m};
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          part[j & 3] = max3(part[j & 3], __uint_as_float(sc[0][j]), __uint_as_float(sc[1][j]));
+          part[(j + 2) & 3] = max3(part[(j + 2) & 3], __uint_as_float(sc[2][j]), __uint_as_float(sc[3][j]));
+        }
+        mx = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = key0 + c * 32 + j;
+            const bool visible = key <= qpos && (p.window <= 0 || key > qpos - p.window);
+            if (!visible) sc[c][j] = __float_as_uint(-INFINITY);
+            mx = fmaxf(mx, __uint_as_float(sc[c][j]));
+          }
+      }
+      float m_new = m, alpha = 1.f;
+      if ((mx - m) * p.scale_log2 > kLazyLog2) {
+        m_new = mx;
+        alpha = ex2((m - mx) * p.scale_log2);
+      }
+      const bool rescale = alpha != 1.f && m != -INFINITY;
+      const float neg = m_new == -INFINITY ? 0.f : -m_new * p.scale_log2;
+      // The probabilities' buffer and the accumulator belong to P V of the tile before until that product is done.
+      if (t >= 1) {
+        if (!mbar_wait(pv_done(x), (unsigned)(t - 1) & 1, p.error_flag, 46)) { ok = false; break; }
+        tcgen05_fence_after();
+      }
+      float2 sums[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg, neg);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {       // 32 keys at a time, stage by stage, so that 16 independent pairs are under way
+        unsigned char* prow = generic_base + (p_smem - base) + (x * 2 + c / 2) * kPSubBytes + row * 128;
+        float2 y[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          y[i] = fma2(make_float2(__uint_as_float(sc[c][2 * i]), __uint_as_float(sc[c][2 * i + 1])), scale2, neg2);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = make_float2(ex2(y[i].x), ex2(y[i].y));
+        unsigned w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          sums[i & 3] = add2(sums[i & 3], y[i]);
+          __nv_bfloat162 h = __floats2bfloat162_rn(y[i].x, y[i].y);
+          w[i] = *reinterpret_cast<unsigned*>(&h);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (c & 1) * 4 + q;      // the chunk of 8 keys within the sub-tile's 128-byte row
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+        }
+      }
+      const float2 total = add2(add2(sums[0], sums[1]), add2(sums[2], sums[3]));
+      const float sum = total.x + total.y;
+      if (t >= 1 && __any_sync(0xffffffffu, rescale)) {
+        unsigned o[32];
+#pragma unroll
+        for (int part = 0; part < D / 32; ++part) {
+          tmem_load32(tmem_o + lane_field + part * 32, o);
+          tmem_load_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_store32(tmem_o + lane_field + part * 32, o);
+        }
+        tmem_store_wait();
+      }
+      m = m_new;
+      l = l * alpha + sum;
+      // Value rows of keys outside [lo, hi) may hold anything (an unwritten slot): zero them before P V reads them
+      // (both groups do, so that neither product depends on the other group).
+      if (key0 < lo || key0 + kPairKeys > hi) {
+        if (!mbar_wait(kv_full(stage), (unsigned)(t / kPairStages) & 1, p.error_flag, 47)) { ok = false; break; }
+        unsigned char* vt = generic_base + (v_smem - base) + stage * kStageBytes;
+        for (int e = group_thread; e < kPairKeys * 8; e += 128) {
+          const int key = e >> 3;
+          const int kpos = key0 + key;
+          if (kpos < lo || kpos >= hi)
+            *reinterpret_cast<uint4*>(vt + key * 128 + ((e & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      fence_async_shared();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(x));
+    }
+    // Output: wait for the last P V, read the row, divide by the row's sum, store.
+    if (ok && ntiles > 0 && mbar_wait(pv_done(x), (unsigned)(ntiles - 1) & 1, p.error_flag, 48)) {
+      tcgen05_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int qi = tile_q0 + row / groups, head = kvh * groups + row % groups;
+      bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
+#pragma unroll
+      for (int half = 0; half < D / 32; ++half) {
+        unsigned o[32];
+        __syncwarp();
+        tmem_load32(tmem_o + lane_field + half * 32, o);
+        tmem_load_wait();
+        if (row < rows_used) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            unsigned w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[v * 8 + 2 * e]) * inv,
+                                                       __uint_as_float(o[v * 8 + 2 * e + 1]) * inv);
+              w[e] = *reinterpret_cast<unsigned*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + half * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
 // The pool [pages, kv_heads, page_size, head_dim] as a 2-D map of rows of head_dim; a box is 64 dimensions of one
 // page of one head.
 static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int page_size, int head_dim) {
@@ -454,6 +792,19 @@ static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, con
   return (int)launch_pdl(0, attention_tcgen05_kernel<D>, grid, dim3(kAttnThreads), smem, stream, mk, mv, p);
 }
 
+static int launch_tc_attention_pair(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
+                                    cudaStream_t stream) {
+  constexpr size_t smem = 2 * (size_t)kRows * 64 * 2 + 4 * (size_t)kRows * 64 * 2 +
+                          2 * kPairStages * (size_t)kPairKeys * 64 * 2 + 8 * (2 * kPairStages + 8) + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return (int)launch_pdl(0, attention_tcgen05_pair_kernel, grid, dim3(kPairThreads), smem, stream, mk, mv, p);
+}
+
 }  // namespace li
 
 using namespace li;
@@ -491,6 +842,16 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
                  scale * kLog2eF, window, error_flag};
   const int groups = heads / kv_heads;
   const int tq = kRows / groups;
+  // LITEINFER_TCGEN05_ATTN_PAIR=1 sends long runs of queries at head size 64 to the kernel with two query tiles per
+  // block.  Off by default: measured on B200 it reaches what the kernel with one tile reaches where there is work for
+  // every SM (one prompt of 8,192 tokens: 432 against 429 us, 636 TFLOP/s; four portions of 2,048 over 4,096 keys: 344
+  // against 342 us) and loses where there is not (one prompt of 2,048 tokens: 45.0 against 39.6 us, half as many
+  // blocks).  Its softmax groups, like the other kernel's, are bound by the latency of their own instruction stream
+  // (special-function pipe 60 % busy, 2.5 warps a scheduler), not by the issuing thread.
+  const char* pair_env = getenv("LITEINFER_TCGEN05_ATTN_PAIR");
+  const bool pair_wanted = pair_env && atoi(pair_env) == 1;
+  if (head_dim == 64 && pair_wanted && page_size <= 64 && max_q_len >= 4 * tq)
+    return launch_tc_attention_pair(mk, mv, p, dim3(kv_heads, num_seqs, (max_q_len + 2 * tq - 1) / (2 * tq)), stream);
   const dim3 grid(kv_heads, num_seqs, (max_q_len + tq - 1) / tq);
   return head_dim == 64 ? launch_tc_attention<64>(mk, mv, p, grid, stream) : launch_tc_attention<128>(mk, mv, p, grid, stream);
 }
