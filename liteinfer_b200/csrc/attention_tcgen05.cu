@@ -40,7 +40,6 @@ namespace li {
 
 constexpr int kRows = 128;       // rows (query token x head in group) per block
 constexpr int kKeys = 64;        // keys per tile
-constexpr int kKvStages = 3;
 constexpr int kAttnThreads = 192;
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kLazyLog2 = 8.f;   // how far (in powers of two) a row's maximum may outgrow the reference of its exponentials
@@ -90,7 +89,13 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
 }
 
 // Shared memory holds everything in sub-tiles of 64 columns (128 bytes, one swizzle row): Q is D/64 sub-tiles of
-// 128 rows, a K or V stage D/64 sub-tiles of 64 keys, a P buffer one sub-tile of 128 rows x 64 keys.
+// 128 rows, a K or V stage D/64 sub-tiles of 64 keys.  The probabilities do not pass through it: a softmax thread
+// writes its row of them as bfloat16 over the first 32 columns of the scores it has read, and P V takes its first
+// operand from tensor memory.  What that saves goes to the ring of keys and values: the kernel's time is how long a
+// tile takes to arrive divided by how many are on their way.
+template <int D>
+struct KvStages { static constexpr int value = D == 64 ? 5 : 6; };
+
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads, D == 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -101,10 +106,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   constexpr unsigned kKeySubBytes = kKeys * 64 * 2;                 // 8 KB: 64 keys x 64 dimensions
   constexpr unsigned kRowSubBytes = kRows * 64 * 2;                 // 16 KB: 128 rows x 64 columns
   constexpr unsigned kTileBytes = kSub * kKeySubBytes;              // one K or V tile
-  constexpr unsigned kRowTileBytes = kRowSubBytes;                  // one P buffer
+  constexpr int kKvStages = KvStages<D>::value;
   const unsigned q_smem = base;
-  const unsigned p_smem = q_smem + kSub * kRowSubBytes;             // 2 buffers
-  const unsigned k_smem = p_smem + 2 * kRowTileBytes;               // kKvStages
+  const unsigned k_smem = q_smem + kSub * kRowSubBytes;             // kKvStages
   const unsigned v_smem = k_smem + kKvStages * kTileBytes;          // kKvStages
   const unsigned bars = v_smem + kKvStages * kTileBytes;
   auto kv_full = [&](int s) { return bars + 8u * s; };                    // keys and values of a stage have landed
@@ -237,10 +241,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       constexpr unsigned idesc_pv = idesc_qk | (1u << 16);
       // A descriptor's low bits are its address in units of 16 bytes, so the descriptor of a place further on in
       // shared memory is the first one plus the distance: one addition per product instead of the whole encoding.
-      const unsigned long long desc_q = umma_desc(q_smem), desc_k = umma_desc(k_smem), desc_v = umma_desc(v_smem),
-                               desc_p = umma_desc(p_smem);
+      const unsigned long long desc_q = umma_desc(q_smem), desc_k = umma_desc(k_smem), desc_v = umma_desc(v_smem);
       // S of tile t may overwrite its buffer: the softmax threads read tile t-2 out of it before they announced its
-      // probabilities, and that announcement was waited for before P V of tile t-2 was issued.
+      // probabilities (which lie in the same columns), that announcement was waited for before P V of tile t-2 was
+      // issued, and products run in the order they were issued.
       auto issue_qk = [&](int t) -> bool {
         const int stage = t % kKvStages, buf = t & 1;
         if (!mbar_wait(kv_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 13)) return false;
@@ -260,14 +264,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         // The stage's values landed with its keys, which S = Q K^T of this tile waited for.
         if (!mbar_wait(p_full(buf), (unsigned)(t >> 1) & 1, p.error_flag, 15)) { ok = false; break; }
         tcgen05_fence_after();
-        const unsigned long long dp = desc_p + (unsigned long long)((buf * kRowTileBytes) >> 4);
         const unsigned long long dv = desc_v + (unsigned long long)((stage * kTileBytes) >> 4);
 #pragma unroll
         for (int sub = 0; sub < kSub; ++sub)
 #pragma unroll
           for (int k = 0; k < kKeys / 16; ++k)
-            umma_bf16(tmem_o + sub * 64, dp + (unsigned long long)((k * 32) >> 4),
-                      dv + (unsigned long long)((sub * kKeySubBytes + k * 16 * 128) >> 4), idesc_pv, t > 0 || k > 0);
+            umma_bf16_ts(tmem_o + sub * 64, tmem_s[buf] + k * 8u,
+                         dv + (unsigned long long)((sub * kKeySubBytes + k * 16 * 128) >> 4), idesc_pv, t > 0 || k > 0);
         umma_commit(kv_empty(stage));
         umma_commit(pv_done(buf));
       }
@@ -319,27 +322,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       }
       const bool rescale = alpha != 1.f && m != -INFINITY;   // a row that has seen no key yet holds zeros
       const float neg = m_new == -INFINITY ? 0.f : -m_new * p.scale_log2;
-      // P of this tile overwrites the buffer that P V of tile t-2 read: that product was issued before S of this
-      // tile, whose arrival (waited for above) says that every product issued before it is done.
+      // Column c of the probabilities holds keys 2c and 2c + 1 of the tile; they go where the scores were.
       float2 sums[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg, neg);
-      unsigned char* prow = generic_base + (p_smem - base) + buf * kRowTileBytes + row * 128;
+      unsigned packed[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {       // chunk of 8 keys = 16 bytes of bfloat16
-        unsigned w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = c * 8 + 2 * e;
-          const float2 x = make_float2(__uint_as_float(j < 32 ? sa[j] : sb[j - 32]),
-                                       __uint_as_float(j + 1 < 32 ? sa[j + 1] : sb[j + 1 - 32]));
-          const float2 y = fma2(x, scale2, neg2);
-          const float2 ev = make_float2(ex2(y.x), ex2(y.y));
-          sums[e] = add2(sums[e], ev);
-          __nv_bfloat162 h = __floats2bfloat162_rn(ev.x, ev.y);
-          w[e] = *reinterpret_cast<unsigned*>(&h);
-        }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int c = 0; c < 32; ++c) {
+        const int j = 2 * c;
+        const float2 x = make_float2(__uint_as_float(j < 32 ? sa[j] : sb[j - 32]),
+                                     __uint_as_float(j + 1 < 32 ? sa[j + 1] : sb[j + 1 - 32]));
+        const float2 y = fma2(x, scale2, neg2);
+        const float2 ev = make_float2(ex2(y.x), ex2(y.y));
+        sums[c & 3] = add2(sums[c & 3], ev);
+        __nv_bfloat162 h = __floats2bfloat162_rn(ev.x, ev.y);
+        packed[c] = *reinterpret_cast<unsigned*>(&h);
       }
+      tmem_store32(tmem_s[buf] + lane_field, packed);
       const float2 total = add2(add2(sums[0], sums[1]), add2(sums[2], sums[3]));
       const float sum = total.x + total.y;
       // The accumulator may be rescaled only between P V of tile t-1 and P V of this tile; the latter waits for
@@ -356,8 +354,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
           tmem_store32(tmem_o + lane_field + part * 32, o);
         }
-        tmem_store_wait();
       }
+      tmem_store_wait();
       m = m_new;
       l = l * alpha + sum;
       // Value rows of keys outside [lo, hi) may hold anything (an unwritten slot): zero them before P V reads them.
@@ -370,8 +368,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           if (kpos < lo || kpos >= hi)
             *reinterpret_cast<uint4*>(vt + sub * kKeySubBytes + key * 128 + ((e & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
+        fence_async_shared();
       }
-      fence_async_shared();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(buf));
@@ -413,25 +411,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   }
 }
 
-// ---- two query tiles per block, two softmax threads per row ------------------------------------------------------
-// For long runs of queries at head size 64.  What bounds the kernel above is neither its tensor-core work nor the
-// special-function pipe but the latency of its softmax warps' own instruction stream: with two blocks per SM there
-// are two such warps per scheduler.  Here a block owns 256 rows (two tiles of 128: A and B) for one KV head and walks
-// the visible keys in tiles of 128; every row has two softmax threads, each with one half of a tile's keys (64
-// scores in registers), its own running maximum and sum and its own accumulator in tensor memory, so that the two
-// exchange nothing until the end, where the first of them merges the two halves.  That makes sixteen softmax warps
-// per SM, four per scheduler.  One loader and one issuer serve everything: a tile of keys and values is fetched
-// once for 256 rows, and per 256 x 128 scores the issuer passes seven waits where the kernel above passes eight for
-// half the rows.  Tensor memory: S of A and of B (128 columns each, single buffers: both halves say when they have
-// read their scores, and S of the next tile of keys may then overwrite them) and four accumulators of 64 columns:
-// all 512 columns, one block per SM.  Probabilities go through shared memory, two buffers per tile and half: the
-// softmax of tile t + 1 does not wait for P V of tile t (it would leave the special-function unit idle for the
-// length of that product), only for that of tile t - 1, unless a row's maximum has moved by more than the lazy
-// threshold and the accumulator has to be scaled.  Keys and values have rings of two stages each: a stage of keys
-// is free as soon as S of its tile is done, long before the values of that tile are.  Every wait is bounded.
+// ---- two query tiles per block, probabilities in tensor memory -----------------------------------------------
+// For long runs of queries at head size 64.  Measured on B200, the kernel above is bound by neither its tensor-core
+// work nor its exponentials (with either removed a prompt of 8,192 tokens takes 414 and 416 us instead of 429) but
+// by how long a tile of keys and values takes to arrive, at the depth its shared memory leaves for the ring
+// (two stages: 544 us; three: 429), while all its blocks together ask the L2 for 2.1 GB.  Here a block owns 256
+// rows (two tiles of 128: A and B) for one KV head, so a tile of keys and values is fetched once for twice the rows,
+// and walks the visible keys in tiles of 128.  The probabilities never go through shared memory: a softmax thread
+// (one per row, all 128 scores of its row in registers) writes them as bfloat16 over the first 64 columns of the
+// scores it has just read, and P V takes its first operand from there.  That leaves 192 KB of shared memory for a
+// ring of six stages of keys and values.  Tensor memory: S / P of A, S / P of B (128 columns each), O of A, O of B
+// (64 each).  For one tile of queries the steps form a chain (softmax of tile t, P V of t, S of t + 1, softmax of
+// t + 1: S of t + 1 overwrites the probabilities that P V of t has read, and products run in the order they were
+// issued), and the two tiles of queries take turns: while the threads of one compute exponentials, the products of
+// the other run.  Every wait is bounded.
 constexpr int kPairKeys = 128;
-constexpr int kPairStages = 2;
-constexpr int kPairThreads = 576;      // loader, issuer, four groups (tile x half) of four softmax warps
+constexpr int kPairStages = 6;
+constexpr int kPairThreads = 320;      // loader, issuer, four softmax warps for each of the two query tiles
 
 __global__ void __launch_bounds__(kPairThreads, 1)
 attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -440,25 +436,16 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const _
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_addr(smem_raw) + 1023u) & ~1023u;
   constexpr unsigned kQBytes = kRows * 64 * 2;                 // 16 KB: 128 rows x 64 dimensions
-  constexpr unsigned kPSubBytes = kRows * 64 * 2;              // 16 KB: 128 rows x 64 keys
   constexpr unsigned kStageBytes = kPairKeys * D * 2;          // 16 KB: 128 keys x 64 dimensions (K or V)
   const unsigned q_smem = base;                                // tiles A, B
-  const unsigned p_smem = q_smem + 2 * kQBytes;                // (tile, half) x 128 rows x 64 keys
-  const unsigned k_smem = p_smem + 8 * kPSubBytes;             // P: (tile, half) x two buffers
+  const unsigned k_smem = q_smem + 2 * kQBytes;
   const unsigned v_smem = k_smem + kPairStages * kStageBytes;
   const unsigned bars = v_smem + kPairStages * kStageBytes;
-  auto k_full = [&](int s) { return bars + 8u * s; };
-  auto k_empty = [&](int s) { return bars + 8u * (2 + s); };
-  auto v_full = [&](int s) { return bars + 8u * (4 + s); };
-  auto v_empty = [&](int s) { return bars + 8u * (6 + s); };
-  auto s_full = [&](int x) { return bars + 8u * (8 + x); };
-  auto s_free = [&](int x) { return bars + 8u * (10 + x); };
-  // One barrier per buffer of probabilities: a group may finish tile t + 1 before the issuer has looked at its
-  // tile t (it waits for the groups in turn), and one barrier would then have gone round twice unseen.
-  auto p_full = [&](int g, int buf) { return bars + 8u * (12 + g * 2 + buf); };     // g = tile * 2 + half
-  auto pv_done = [&](int g, int buf) { return bars + 8u * (20 + g * 2 + buf); };    // P V that read buffer buf of g
-  const unsigned tmem_slot = bars + 8u * 28;
-  static_assert(kPairStages == 2, "the barriers above are laid out for rings of two stages");
+  auto kv_full = [&](int s) { return bars + 8u * s; };
+  auto kv_empty = [&](int s) { return bars + 8u * (kPairStages + s); };
+  auto s_full = [&](int x) { return bars + 8u * (2 * kPairStages + x); };       // S of tile x is there (and O, at the end)
+  auto p_full = [&](int x) { return bars + 8u * (2 * kPairStages + 2 + x); };   // P of tile x is there
+  const unsigned tmem_slot = bars + 8u * (2 * kPairStages + 4);
   __shared__ unsigned tmem_base_shared;
   unsigned char* generic_base = smem_raw + (base - smem_addr(smem_raw));
 
@@ -482,20 +469,12 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const _
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
-      mbar_init(k_full(s), 1);
-      mbar_init(k_empty(s), 1);
-      mbar_init(v_full(s), 1);
-      mbar_init(v_empty(s), 1);
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 1);
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(s_full(x), 1);
-      mbar_init(s_free(x), 8);
-    }
-    for (int g = 0; g < 4; ++g) {
-      mbar_init(p_full(g, 0), 4);
-      mbar_init(p_full(g, 1), 4);
-      mbar_init(pv_done(g, 0), 1);
-      mbar_init(pv_done(g, 1), 1);
+      mbar_init(p_full(x), 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -516,19 +495,16 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const _
       if (page >= 0 && page < p.num_pages) row = (page * p.kv_heads + kvh) * p.page_size;
     }
     const int valid = __popc(__ballot_sync(0xffffffffu, row >= 0));
-    // The keys, then the values: each ring has its own barriers.
-    for (int is_v = 0; is_v < 2; ++is_v) {
-      bool fine = true;
-      const unsigned full = is_v ? v_full(stage) : k_full(stage);
-      if (lane == 0) {
-        if (!stage_is_new) fine = mbar_wait(is_v ? v_empty(stage) : k_empty(stage), phase ^ 1, p.error_flag, 41);
-        if (fine) mbar_expect_tx(full, valid * box_bytes);
-      }
-      fine = __shfl_sync(0xffffffffu, fine, 0);
-      if (!fine) return false;
-      if (row >= 0)
-        tma_load_2d((is_v ? v_smem : k_smem) + stage * kStageBytes + lane * box_bytes, is_v ? &map_v : &map_k, full,
-                    0, row);
+    bool fine = true;
+    if (lane == 0) {
+      if (!stage_is_new) fine = mbar_wait(kv_empty(stage), phase ^ 1, p.error_flag, 41);
+      if (fine) mbar_expect_tx(kv_full(stage), 2 * valid * box_bytes);
+    }
+    fine = __shfl_sync(0xffffffffu, fine, 0);
+    if (!fine) return false;
+    if (row >= 0) {
+      tma_load_2d(k_smem + stage * kStageBytes + lane * box_bytes, &map_k, kv_full(stage), 0, row);
+      tma_load_2d(v_smem + stage * kStageBytes + lane * box_bytes, &map_v, kv_full(stage), 0, row);
     }
     return true;
   };
@@ -537,14 +513,12 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const _
     __syncwarp();
     for (int t = 0; t < tiles_ahead; ++t) load_tile(t, true);
   }
-  // The softmax warps: group g = (warp - 2) / 4 is (tile x, half h) = (g / 2, g % 2); its four warps hold the four
-  // quarters of the tile's 128 rows.
-  const int g_of_warp = warp >= 2 ? (warp - 2) >> 2 : 0;
-  const int x_of_warp = g_of_warp >> 1, h_of_warp = g_of_warp & 1;
+  // Warps 2-5 are the softmax threads of tile A, warps 6-9 those of tile B.
+  const int x_of_warp = warp >= 6 ? 1 : 0;
   const int tile_q0 = q0 + x_of_warp * tq;                     // first query token of the warp's tile
   const int rows_used = max(0, min(tq, q_len - tile_q0)) * groups;
-  // Q: the first-half thread of each row copies the row (128 bytes) into the swizzled tile; rows of padding are zero.
-  if (warp >= 2 && h_of_warp == 0) {
+  // Q: each softmax thread copies its row (128 bytes) into the swizzled tile; rows of padding are zero.
+  if (warp >= 2) {
     const int row = (warp & 3) * 32 + lane;
     uint4 v[8];
     if (row < rows_used) {
@@ -581,94 +555,92 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const _
     if (lane == 0) {
       constexpr unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(kPairKeys >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
       constexpr unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
-      const unsigned long long desc_q = umma_desc(q_smem), desc_k = umma_desc(k_smem), desc_v = umma_desc(v_smem),
-                               desc_p = umma_desc(p_smem);
-      // S of tile t for query tile x; its buffer is free once both halves have read S of tile t - 1.
-      auto issue_s = [&](int t, int x) -> bool {
-        if (t > 0 && !mbar_wait(s_free(x), (unsigned)(t - 1) & 1, p.error_flag, 43)) return false;
-        tcgen05_fence_after();
+      const unsigned long long desc_q = umma_desc(q_smem), desc_k = umma_desc(k_smem), desc_v = umma_desc(v_smem);
+      auto issue_s = [&](int t, int x) {
         const unsigned long long dk = desc_k + (unsigned long long)(((t % kPairStages) * kStageBytes) >> 4);
         const unsigned long long dq = desc_q + (unsigned long long)((x * kQBytes) >> 4);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
           umma_bf16(tmem_base + x * 128u, dq + (unsigned long long)((k * 32) >> 4), dk + (unsigned long long)((k * 32) >> 4),
                     idesc_s, k > 0);
-        umma_commit(s_full(x));
-        return true;
       };
-      auto issue_both = [&](int t) -> bool {
-        if (!mbar_wait(k_full(t % kPairStages), (unsigned)(t / kPairStages) & 1, p.error_flag, 42)) return false;
+      bool ok = ntiles > 0 && mbar_wait(kv_full(0), 0, p.error_flag, 42);
+      if (ok) {
         tcgen05_fence_after();
-        if (!issue_s(t, 0) || !issue_s(t, 1)) return false;
-        umma_commit(k_empty(t % kPairStages));
-        return true;
-      };
-      bool ok = ntiles > 0 && issue_both(0);
+        issue_s(0, 0);
+        umma_commit(s_full(0));
+        issue_s(0, 1);
+        umma_commit(s_full(1));
+      }
       for (int t = 0; ok && t < ntiles; ++t) {
-        if (t + 1 < ntiles && !issue_both(t + 1)) { ok = false; break; }
         const int stage = t % kPairStages;
         const unsigned long long dv = desc_v + (unsigned long long)((stage * kStageBytes) >> 4);
-        if (!mbar_wait(v_full(stage), (unsigned)(t / kPairStages) & 1, p.error_flag, 50)) { ok = false; break; }
-        // O of (tile, half) += P of that half (64 keys) x the stage's values of those keys.
-        for (int g = 0; g < 4 && ok; ++g) {
-          if (!mbar_wait(p_full(g, t & 1), (unsigned)(t >> 1) & 1, p.error_flag, 44)) { ok = false; break; }
-          tcgen05_fence_after();
-          const unsigned long long dp = desc_p + (unsigned long long)(((g * 2 + (t & 1)) * kPSubBytes) >> 4);
-          const int h = g & 1;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_base + 256u + g * 64u, dp + (unsigned long long)((k * 32) >> 4),
-                      dv + (unsigned long long)(((h * 4 + k) * 16 * 128) >> 4), idesc_pv, t > 0 || k > 0);
-          umma_commit(pv_done(g, t & 1));
+        if (t + 1 < ntiles &&
+            !mbar_wait(kv_full((t + 1) % kPairStages), (unsigned)((t + 1) / kPairStages) & 1, p.error_flag, 43)) {
+          ok = false;
+          break;
         }
-        if (ok) umma_commit(v_empty(stage));
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (!mbar_wait(p_full(x), (unsigned)t & 1, p.error_flag, 44)) { ok = false; break; }
+          tcgen05_fence_after();
+          // O of x += P of x (tensor memory, over the scores' first 64 columns) x the stage's values.
+#pragma unroll
+          for (int k = 0; k < kPairKeys / 16; ++k)
+            umma_bf16_ts(tmem_base + 256u + x * 64u, tmem_base + x * 128u + k * 8u,
+                         dv + (unsigned long long)((k * 16 * 128) >> 4), idesc_pv, t > 0 || k > 0);
+          // S of the next tile of keys over the scores and probabilities of this one: products run in the order
+          // they were issued.  The last arrival says that O is complete.
+          if (t + 1 < ntiles) issue_s(t + 1, x);
+          umma_commit(s_full(x));
+        }
+        if (ok) umma_commit(kv_empty(stage));
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax of (tile x, half h)
-    const int x = x_of_warp, h = h_of_warp, g = g_of_warp;
+    // ---------------------------------------------------------------- softmax of tile x
+    const int x = x_of_warp;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const unsigned lane_field = (unsigned)(quarter * 32) << 16;
-    const unsigned tmem_s = tmem_base + x * 128u + h * 64u, tmem_o = tmem_base + 256u + g * 64u;
+    const unsigned tmem_s = tmem_base + x * 128u + lane_field, tmem_o = tmem_base + 256u + x * 64u + lane_field;
     const int tile_first_qpos = ctx - q_len + tile_q0;
     const int tile_last_qpos = tile_first_qpos + max(rows_used / groups, 1) - 1;
     const int qpos = row < rows_used ? tile_first_qpos + row / groups : -1;
-    const int group_thread = threadIdx.x - 64 - g * 128;      // 0..127 within the group
+    const int group_thread = threadIdx.x - 64 - x * 128;      // 0..127 within the tile's threads
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int t = 0; ok && t < ntiles; ++t) {
       const int stage = t % kPairStages;
-      const int key0 = (tile_lo + t) * kPairKeys + h * 64;    // the first key of this half
+      const int key0 = (tile_lo + t) * kPairKeys;
       if (!mbar_wait(s_full(x), (unsigned)t & 1, p.error_flag, 45)) { ok = false; break; }
       tcgen05_fence_after();
-      unsigned sa[32], sb[32];
+      unsigned s[4][32];
       __syncwarp();
-      tmem_load32(tmem_s + lane_field, sa);
-      tmem_load32(tmem_s + lane_field + 32, sb);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) tmem_load32(tmem_s + q * 32, s[q]);
       tmem_load_wait();
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free(x));      // S of the next tile of keys may overwrite these columns
 
-      const bool all_visible = rows_used > 0 && key0 + 63 <= tile_first_qpos &&
+      const bool all_visible = rows_used > 0 && key0 + kPairKeys - 1 <= tile_first_qpos &&
                                (p.window <= 0 || key0 > tile_last_qpos - p.window);
       float mx = m;
       if (all_visible && qpos >= 0) {
         float part[4] = {m, m, m, m};
 #pragma unroll
-        for (int j = 0; j < 32; ++j) part[j & 3] = max3(part[j & 3], __uint_as_float(sa[j]), __uint_as_float(sb[j]));
+        for (int j = 0; j < 32; ++j) {
+          part[j & 3] = max3(part[j & 3], __uint_as_float(s[0][j]), __uint_as_float(s[1][j]));
+          part[(j + 2) & 3] = max3(part[(j + 2) & 3], __uint_as_float(s[2][j]), __uint_as_float(s[3][j]));
+        }
         mx = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int ka = key0 + j, kb = key0 + 32 + j;
-          const bool va = ka <= qpos && (p.window <= 0 || ka > qpos - p.window);
-          const bool vb = kb <= qpos && (p.window <= 0 || kb > qpos - p.window);
-          if (!va) sa[j] = __float_as_uint(-INFINITY);
-          if (!vb) sb[j] = __float_as_uint(-INFINITY);
-          mx = fmaxf(mx, fmaxf(__uint_as_float(sa[j]), __uint_as_float(sb[j])));
-        }
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = key0 + q * 32 + j;
+            const bool visible = key <= qpos && (p.window <= 0 || key > qpos - p.window);
+            if (!visible) s[q][j] = __float_as_uint(-INFINITY);
+            mx = fmaxf(mx, __uint_as_float(s[q][j]));
+          }
       }
       float m_new = m, alpha = 1.f;
       if ((mx - m) * p.scale_log2 > kLazyLog2) {
@@ -677,90 +649,68 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const _
       }
       const bool rescale = alpha != 1.f && m != -INFINITY;
       const float neg = m_new == -INFINITY ? 0.f : -m_new * p.scale_log2;
-      // This buffer of probabilities was read by P V of the tile two before.
-      if (t >= 2 && !mbar_wait(pv_done(g, t & 1), (unsigned)((t >> 1) - 1) & 1, p.error_flag, 46)) { ok = false; break; }
       float2 sums[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg, neg);
-      unsigned char* prow = generic_base + (p_smem - base) + (g * 2 + (t & 1)) * kPSubBytes + row * 128;
+      // Column c of the probabilities holds keys 2c and 2c + 1 of the tile as bfloat16.
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {       // chunk of 8 keys = 16 bytes of bfloat16
-        unsigned w[4];
+      for (int half = 0; half < 2; ++half) {
+        unsigned packed[32];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = c * 8 + 2 * e;
-          const float2 v = make_float2(__uint_as_float(j < 32 ? sa[j] : sb[j - 32]),
-                                       __uint_as_float(j + 1 < 32 ? sa[j + 1] : sb[j + 1 - 32]));
-          const float2 y = fma2(v, scale2, neg2);
+        for (int c = 0; c < 32; ++c) {
+          const int q = half * 2 + c / 16, j = (2 * c) % 32;
+          const float2 y = fma2(make_float2(__uint_as_float(s[q][j]), __uint_as_float(s[q][j + 1])), scale2, neg2);
           const float2 ev = make_float2(ex2(y.x), ex2(y.y));
-          sums[e] = add2(sums[e], ev);
+          sums[c & 3] = add2(sums[c & 3], ev);
           __nv_bfloat162 hh = __floats2bfloat162_rn(ev.x, ev.y);
-          w[e] = *reinterpret_cast<unsigned*>(&hh);
+          packed[c] = *reinterpret_cast<unsigned*>(&hh);
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        tmem_store32(tmem_s + half * 32, packed);
       }
       const float2 total = add2(add2(sums[0], sums[1]), add2(sums[2], sums[3]));
       const float sum = total.x + total.y;
+      // The accumulator: S of this tile arrived after P V of the tile before (the products run in order).
       if (t >= 1 && __any_sync(0xffffffffu, rescale)) {
-        // The accumulator belongs to P V of the tile before until that product is done.
-        if (!mbar_wait(pv_done(g, (t - 1) & 1), (unsigned)((t - 1) >> 1) & 1, p.error_flag, 51)) { ok = false; break; }
-        tcgen05_fence_after();
         unsigned o[32];
 #pragma unroll
         for (int part = 0; part < D / 32; ++part) {
-          tmem_load32(tmem_o + lane_field + part * 32, o);
+          tmem_load32(tmem_o + part * 32, o);
           tmem_load_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_store32(tmem_o + lane_field + part * 32, o);
+          tmem_store32(tmem_o + part * 32, o);
         }
-        tmem_store_wait();
       }
+      tmem_store_wait();
       m = m_new;
       l = l * alpha + sum;
       // Value rows of keys outside [lo, hi) may hold anything (an unwritten slot): zero them before P V reads them
-      // (every group does so for its half of the keys, so that no product depends on another group).
-      if (key0 < lo || key0 + 64 > hi) {
-        if (!mbar_wait(v_full(stage), (unsigned)(t / kPairStages) & 1, p.error_flag, 47)) { ok = false; break; }
-        unsigned char* vt = generic_base + (v_smem - base) + stage * kStageBytes + h * 64 * 128;
-        for (int e = group_thread; e < 64 * 8; e += 128) {
+      // (the threads of either tile do so, whichever comes first; both write zeros).
+      if (key0 < lo || key0 + kPairKeys > hi) {
+        if (!mbar_wait(kv_full(stage), (unsigned)(t / kPairStages) & 1, p.error_flag, 47)) { ok = false; break; }
+        unsigned char* vt = generic_base + (v_smem - base) + stage * kStageBytes;
+        for (int e = group_thread; e < kPairKeys * 8; e += 128) {
           const int key = e >> 3;
           const int kpos = key0 + key;
           if (kpos < lo || kpos >= hi)
             *reinterpret_cast<uint4*>(vt + key * 128 + ((e & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
+        fence_async_shared();
       }
-      fence_async_shared();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(g, t & 1));
+      if (lane == 0) mbar_arrive(p_full(x));
     }
-    // Output.  The second half of every row leaves its maximum and sum in shared memory; behind a barrier of the
-    // tile's eight warps the first half merges: both accumulators scaled to the common maximum, divided by the
-    // common sum.  (Every softmax thread reaches the barrier, also after a wait that gave up.)
-    // (They lie where the tile's queries lay: the last S of the tile, which this thread has waited for, was the
-    // last to read them.)
-    float2* other = reinterpret_cast<float2*>(generic_base + (q_smem - base) + x * kQBytes) + row;
-    if (h == 1) *other = make_float2(m, l);
-    asm volatile("bar.sync %0, 256;" ::"r"(1 + x) : "memory");
-    if (h == 0 && ok && ntiles > 0 &&
-        mbar_wait(pv_done(g, (ntiles - 1) & 1), (unsigned)((ntiles - 1) >> 1) & 1, p.error_flag, 48) &&
-        mbar_wait(pv_done(g + 1, (ntiles - 1) & 1), (unsigned)((ntiles - 1) >> 1) & 1, p.error_flag, 49)) {
+    // Output: the arrival after the last P V, the row out of tensor memory, divided by the row's sum.
+    if (ok && ntiles > 0 && mbar_wait(s_full(x), (unsigned)ntiles & 1, p.error_flag, 48)) {
       tcgen05_fence_after();
-      const float m1 = other->x, l1 = other->y;
-      const float mm = fmaxf(m, m1);
-      const float a0 = m == -INFINITY ? 0.f : ex2((m - mm) * p.scale_log2);
-      const float a1 = m1 == -INFINITY ? 0.f : ex2((m1 - mm) * p.scale_log2);
-      const float denom = l * a0 + l1 * a1;
-      const float inv = denom > 0.f ? 1.f / denom : 0.f;
-      const float w0 = a0 * inv, w1 = a1 * inv;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
       const int qi = tile_q0 + row / groups, head = kvh * groups + row % groups;
       bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
 #pragma unroll
       for (int half = 0; half < D / 32; ++half) {
-        unsigned o0[32], o1[32];
+        unsigned o[32];
         __syncwarp();
-        tmem_load32(tmem_o + lane_field + half * 32, o0);
-        tmem_load32(tmem_o + 64u + lane_field + half * 32, o1);
+        tmem_load32(tmem_o + half * 32, o);
         tmem_load_wait();
         if (row < rows_used) {
 #pragma unroll
@@ -769,9 +719,7 @@ attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const _
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int j = v * 8 + 2 * e;
-              __nv_bfloat162 hh = __floats2bfloat162_rn(
-                  __uint_as_float(o0[j]) * w0 + __uint_as_float(o1[j]) * w1,
-                  __uint_as_float(o0[j + 1]) * w0 + __uint_as_float(o1[j + 1]) * w1);
+              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
               w[e] = *reinterpret_cast<unsigned*>(&hh);
             }
             *reinterpret_cast<uint4*>(dst + half * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -819,8 +767,10 @@ static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int pag
 template <int D>
 static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
                                cudaStream_t stream) {
-  constexpr size_t smem = (size_t)(D / 64 + 2) * kRows * 64 * 2 + 2 * kKvStages * (size_t)kKeys * D * 2 +
+  constexpr int kKvStages = KvStages<D>::value;
+  constexpr size_t smem = (size_t)(D / 64) * kRows * 64 * 2 + 2 * kKvStages * (size_t)kKeys * D * 2 +
                           8 * (3 * kKvStages + 8) + 16 + 1024;
+  static_assert(smem <= 232448, "more shared memory than a block may have");
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -832,8 +782,8 @@ static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, con
 
 static int launch_tc_attention_pair(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
                                     cudaStream_t stream) {
-  constexpr size_t smem = 2 * (size_t)kRows * 64 * 2 + 8 * (size_t)kRows * 64 * 2 +
-                          2 * kPairStages * (size_t)kPairKeys * 64 * 2 + 8 * 28 + 16 + 1024;
+  constexpr size_t smem = 2 * (size_t)kRows * 64 * 2 + 2 * kPairStages * (size_t)kPairKeys * 64 * 2 +
+                          8 * (2 * kPairStages + 4) + 16 + 1024;
   static_assert(smem <= 232448, "more shared memory than a block may have");
   static bool configured = false;
   if (!configured) {

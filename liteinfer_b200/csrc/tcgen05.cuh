@@ -67,6 +67,17 @@ __device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a,
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
+// The same product with the first operand in tensor memory: row i of A is lane i, and a 32-bit column holds two
+// consecutive elements along k (the lower one in the low half), so a k step of 16 is eight columns.
+__device__ __forceinline__ void umma_bf16_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long b, unsigned idesc,
+                                             bool accumulate) {
+  const unsigned acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
 __device__ __forceinline__ void umma_commit(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
