@@ -6,25 +6,37 @@
 // in tiles of 64:
 //
 //   loader  (warp 0)    TMA: each page of a tile's keys and values is one box of the pool's tensor map per 64
-//                       dimensions, landing in 128-byte-swizzled shared memory, three tiles ahead at most; lane b
-//                       looks up and requests page b of a tile, and one barrier per stage counts keys and values.
+//                       dimensions, landing in 128-byte-swizzled shared memory, five tiles ahead at most (six at
+//                       head size 128); lane b requests page b of a tile, and one barrier per stage counts keys
+//                       and values.  The block table's entries are in the warp's registers, 32 at a time, the
+//                       next 32 on their way.
 //   issuer  (warp 1)    tcgen05.mma: S = Q K^T (128 x 64, K = head size) into one of two score buffers in
-//                       tensor memory, then O += P V (128 x 64 per 64 dimensions, K 64 keys) into the output
-//                       accumulator;
-//                       S of the next tile is issued before P V of this one, so the tensor cores work
-//                       while the softmax of this tile is computed.  The thread waits twice per tile (the
-//                       next stage has landed; this tile's probabilities are written): what else must hold
-//                       follows from those two and from the order in which products complete.
-//
-// The single threads of loader and issuer, not the softmax, used to set the pace of a tile: each wait that was
-// already satisfied cost them some 200 cycles, each descriptor a dozen dependent instructions.  Blocks are handed
-// out longest first (the query tile is the slowest index of the grid).
+//                       tensor memory, then O += P V (128 x 64 per 64 dimensions, K 64 keys, P from tensor
+//                       memory) into the output accumulator; S of the next tile is issued before P V of this
+//                       one, so the tensor cores work while the softmax of this tile is computed.  The thread
+//                       waits twice per tile (the next stage has landed; this tile's probabilities are
+//                       written): what else must hold follows from those two and from the order in which
+//                       products run (the one in which they were issued).
 //   softmax (warps 2-5) one thread per row: tcgen05.ld brings the row's 64 scores into registers, so
-//                       maximum and sum need no exchange between threads; the probabilities go to
-//                       shared memory as bfloat16 in the layout tcgen05.mma reads; the accumulator in
-//                       tensor memory is rescaled (ld, multiply, st) only when a row's maximum has outgrown
-//                       the reference of its exponentials by 2^8, so the softmax of one tile does not wait
-//                       for P V of the tile before it.
+//                       maximum and sum need no exchange between threads; the probabilities go back as
+//                       bfloat16 over the first 32 columns of those scores (tcgen05.st), where P V reads its
+//                       first operand; the accumulator in tensor memory is rescaled (ld, multiply, st) only
+//                       when a row's maximum has outgrown the reference of its exponentials by 2^8, so the
+//                       softmax of one tile does not wait for P V of the tile before it.
+//
+// Blocks are handed out longest first (the query tile is the slowest index of the grid); two fit an SM at head
+// size 64.  What sets the pace (cycle counters written by one block of a prompt of 8,192 tokens, B200): a tile
+// takes a block about 1,450 cycles, and both single-thread chains are that long.  The softmax warp: 220 for a wait
+// that is already satisfied, 85 for the scores to arrive, 900 for maxima, exponentials and packing (two warps of
+// two blocks share a scheduler's special-function unit), 115 for the store to tensor memory, 110 for fence and
+// arrival.  The issuer: 200 for each of its two waits, about 100 for every product and commit it issues (four for
+// S, four for P V, three commits).  With the exponentials, or three quarters of the products, or the stores of
+// the probabilities taken out, the prompt takes 416, 414 and 420 us instead of 429: no single unit is the bound.
+// Tried on this ground and not kept (all correct, none faster): 256 rows per block with 128-key tiles (432 us;
+// 597 with the probabilities in tensor memory, where softmax and products of one query tile form one chain),
+// two softmax threads per row with accumulators of their own (423 us; the issuer then issues twice as many
+// products).  Kept: the probabilities in tensor memory and the deeper ring that their shared memory pays for (413),
+// the block table in registers (405).
 //
 // Scores, maximum, sum and accumulator are 32-bit; probabilities are rounded to bfloat16 for P V
 // (liteinfer/models/paged_kernels.py:282-284).  Keys outside the visible range are masked to -inf and
@@ -162,15 +174,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   // so that the lookups and the requests of a tile's pages run side by side.  Returns false if a wait gave up.
   const int boxes = kKeys / p.page_size;
   const unsigned box_bytes = (unsigned)p.page_size * 64 * 2;
+  // The warp keeps 32 entries of the block table in registers (lane i the i-th of the chunk) and has the next 32
+  // on their way: a lookup in memory for every tile would set the pace of the whole block (its latency under load
+  // is about what a tile's softmax takes).  A tile's pages lie in one chunk: their number divides 32 and the first
+  // is a multiple of it.
+  int chunk = -1, entries = -1, entries_ahead = -1;
+  auto table_chunk = [&](int c) { return c * 32 + lane < p.table_stride ? table[c * 32 + lane] : -1; };
   auto load_tile = [&](int t, bool stage_is_new) -> bool {
     const int stage = t % kKvStages;
     const unsigned phase = (unsigned)(t / kKvStages) & 1;
     const int kpos = (tile_lo + t) * kKeys + lane * p.page_size;
-    int row = -1;
-    if (lane < boxes && kpos < hi && kpos + p.page_size > lo) {
-      const int page = table[kpos >> p.page_shift];
-      if (page >= 0 && page < p.num_pages) row = (page * p.kv_heads + kvh) * p.page_size;
+    const int first_page = ((tile_lo + t) * kKeys) >> p.page_shift;
+    if ((first_page >> 5) != chunk) {
+      entries = (first_page >> 5) == chunk + 1 && chunk >= 0 ? entries_ahead : table_chunk(first_page >> 5);
+      chunk = first_page >> 5;
+      entries_ahead = table_chunk(chunk + 1);
     }
+    const int page = __shfl_sync(0xffffffffu, entries, (first_page + lane) & 31);
+    int row = -1;
+    if (lane < boxes && kpos < hi && kpos + p.page_size > lo && page >= 0 && page < p.num_pages)
+      row = (page * p.kv_heads + kvh) * p.page_size;
     const int valid = __popc(__ballot_sync(0xffffffffu, row >= 0));
     bool fine = true;
     if (lane == 0) {
@@ -411,332 +434,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   }
 }
 
-// ---- two query tiles per block, probabilities in tensor memory -----------------------------------------------
-// For long runs of queries at head size 64.  Measured on B200, the kernel above is bound by neither its tensor-core
-// work nor its exponentials (with either removed a prompt of 8,192 tokens takes 414 and 416 us instead of 429) but
-// by how long a tile of keys and values takes to arrive, at the depth its shared memory leaves for the ring
-// (two stages: 544 us; three: 429), while all its blocks together ask the L2 for 2.1 GB.  Here a block owns 256
-// rows (two tiles of 128: A and B) for one KV head, so a tile of keys and values is fetched once for twice the rows,
-// and walks the visible keys in tiles of 128.  The probabilities never go through shared memory: a softmax thread
-// (one per row, all 128 scores of its row in registers) writes them as bfloat16 over the first 64 columns of the
-// scores it has just read, and P V takes its first operand from there.  That leaves 192 KB of shared memory for a
-// ring of six stages of keys and values.  Tensor memory: S / P of A, S / P of B (128 columns each), O of A, O of B
-// (64 each).  For one tile of queries the steps form a chain (softmax of tile t, P V of t, S of t + 1, softmax of
-// t + 1: S of t + 1 overwrites the probabilities that P V of t has read, and products run in the order they were
-// issued), and the two tiles of queries take turns: while the threads of one compute exponentials, the products of
-// the other run.  Every wait is bounded.
-constexpr int kPairKeys = 128;
-constexpr int kPairStages = 6;
-constexpr int kPairThreads = 320;      // loader, issuer, four softmax warps for each of the two query tiles
-
-__global__ void __launch_bounds__(kPairThreads, 1)
-attention_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                              const TcAttnParams p) {
-  constexpr int D = 64;
-  extern __shared__ unsigned char smem_raw[];
-  const unsigned base = (smem_addr(smem_raw) + 1023u) & ~1023u;
-  constexpr unsigned kQBytes = kRows * 64 * 2;                 // 16 KB: 128 rows x 64 dimensions
-  constexpr unsigned kStageBytes = kPairKeys * D * 2;          // 16 KB: 128 keys x 64 dimensions (K or V)
-  const unsigned q_smem = base;                                // tiles A, B
-  const unsigned k_smem = q_smem + 2 * kQBytes;
-  const unsigned v_smem = k_smem + kPairStages * kStageBytes;
-  const unsigned bars = v_smem + kPairStages * kStageBytes;
-  auto kv_full = [&](int s) { return bars + 8u * s; };
-  auto kv_empty = [&](int s) { return bars + 8u * (kPairStages + s); };
-  auto s_full = [&](int x) { return bars + 8u * (2 * kPairStages + x); };       // S of tile x is there (and O, at the end)
-  auto p_full = [&](int x) { return bars + 8u * (2 * kPairStages + 2 + x); };   // P of tile x is there
-  const unsigned tmem_slot = bars + 8u * (2 * kPairStages + 4);
-  __shared__ unsigned tmem_base_shared;
-  unsigned char* generic_base = smem_raw + (base - smem_addr(smem_raw));
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = p.seq_index ? p.seq_index[blockIdx.y] : blockIdx.y;
-  if (seq < 0) return;        // a place of padding in the list of sequences
-  const int kvh = blockIdx.x;
-  const int q_begin = p.query_start_loc[seq], q_len = p.query_start_loc[seq + 1] - q_begin;
-  const int groups = p.heads / p.kv_heads;
-  const int tq = kRows / groups;                               // query tokens of one tile
-  const int q0 = (int)(gridDim.z - 1 - blockIdx.z) * 2 * tq;   // longest blocks first
-  if (q0 >= q_len) return;
-  const int ctx = p.context_lens[seq];
-  const int block_q = min(2 * tq, q_len - q0);                 // query tokens of this block
-  const int* table = p.block_table + (size_t)seq * p.table_stride;
-  const int first_qpos = ctx - q_len + q0, last_qpos = first_qpos + block_q - 1;
-  const int hi = last_qpos + 1;
-  const int lo = (p.window > 0 && first_qpos - p.window + 1 > 0) ? first_qpos - p.window + 1 : 0;
-  const int tile_lo = lo / kPairKeys, tile_hi = (hi + kPairKeys - 1) / kPairKeys;
-  const int ntiles = tile_hi - tile_lo;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kPairStages; ++s) {
-      mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
-    }
-    for (int x = 0; x < 2; ++x) {
-      mbar_init(s_full(x), 1);
-      mbar_init(p_full(x), 4);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  grid_dependency_wait();
-  const int boxes = kPairKeys / p.page_size;
-  const unsigned box_bytes = (unsigned)p.page_size * 64 * 2;
-  auto load_tile = [&](int t, bool stage_is_new) -> bool {
-    const int stage = t % kPairStages;
-    const unsigned phase = (unsigned)(t / kPairStages) & 1;
-    const int kpos = (tile_lo + t) * kPairKeys + lane * p.page_size;
-    int row = -1;
-    if (lane < boxes && kpos < hi && kpos + p.page_size > lo) {
-      const int page = table[kpos >> p.page_shift];
-      if (page >= 0 && page < p.num_pages) row = (page * p.kv_heads + kvh) * p.page_size;
-    }
-    const int valid = __popc(__ballot_sync(0xffffffffu, row >= 0));
-    bool fine = true;
-    if (lane == 0) {
-      if (!stage_is_new) fine = mbar_wait(kv_empty(stage), phase ^ 1, p.error_flag, 41);
-      if (fine) mbar_expect_tx(kv_full(stage), 2 * valid * box_bytes);
-    }
-    fine = __shfl_sync(0xffffffffu, fine, 0);
-    if (!fine) return false;
-    if (row >= 0) {
-      tma_load_2d(k_smem + stage * kStageBytes + lane * box_bytes, &map_k, kv_full(stage), 0, row);
-      tma_load_2d(v_smem + stage * kStageBytes + lane * box_bytes, &map_v, kv_full(stage), 0, row);
-    }
-    return true;
-  };
-  const int tiles_ahead = min(kPairStages, ntiles);
-  if (warp == 0) {
-    __syncwarp();
-    for (int t = 0; t < tiles_ahead; ++t) load_tile(t, true);
-  }
-  // Warps 2-5 are the softmax threads of tile A, warps 6-9 those of tile B.
-  const int x_of_warp = warp >= 6 ? 1 : 0;
-  const int tile_q0 = q0 + x_of_warp * tq;                     // first query token of the warp's tile
-  const int rows_used = max(0, min(tq, q_len - tile_q0)) * groups;
-  // Q: each softmax thread copies its row (128 bytes) into the swizzled tile; rows of padding are zero.
-  if (warp >= 2) {
-    const int row = (warp & 3) * 32 + lane;
-    uint4 v[8];
-    if (row < rows_used) {
-      const int qi = tile_q0 + row / groups, head = kvh * groups + row % groups;
-      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + qi) * p.q_row_stride + (size_t)head * D);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) v[c] = src[c];
-    } else {
-#pragma unroll
-      for (int c = 0; c < 8; ++c) v[c] = make_uint4(0, 0, 0, 0);
-    }
-    unsigned char* dst = generic_base + (q_smem - base) + x_of_warp * kQBytes + row * 128;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = v[c];
-    fence_async_shared();
-  }
-  tcgen05_fence_before();
-  __syncthreads();
-  tcgen05_fence_after();
-  if (threadIdx.x == 0) {
-    unsigned v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(tmem_slot));
-    tmem_base_shared = v;
-  }
-  __syncthreads();
-  const unsigned tmem_base = tmem_base_shared;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------------ loader
-    for (int t = tiles_ahead; t < ntiles; ++t)
-      if (!load_tile(t, false)) break;
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ issuer
-    if (lane == 0) {
-      constexpr unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(kPairKeys >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
-      constexpr unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
-      const unsigned long long desc_q = umma_desc(q_smem), desc_k = umma_desc(k_smem), desc_v = umma_desc(v_smem);
-      auto issue_s = [&](int t, int x) {
-        const unsigned long long dk = desc_k + (unsigned long long)(((t % kPairStages) * kStageBytes) >> 4);
-        const unsigned long long dq = desc_q + (unsigned long long)((x * kQBytes) >> 4);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_bf16(tmem_base + x * 128u, dq + (unsigned long long)((k * 32) >> 4), dk + (unsigned long long)((k * 32) >> 4),
-                    idesc_s, k > 0);
-      };
-      bool ok = ntiles > 0 && mbar_wait(kv_full(0), 0, p.error_flag, 42);
-      if (ok) {
-        tcgen05_fence_after();
-        issue_s(0, 0);
-        umma_commit(s_full(0));
-        issue_s(0, 1);
-        umma_commit(s_full(1));
-      }
-      for (int t = 0; ok && t < ntiles; ++t) {
-        const int stage = t % kPairStages;
-        const unsigned long long dv = desc_v + (unsigned long long)((stage * kStageBytes) >> 4);
-        if (t + 1 < ntiles &&
-            !mbar_wait(kv_full((t + 1) % kPairStages), (unsigned)((t + 1) / kPairStages) & 1, p.error_flag, 43)) {
-          ok = false;
-          break;
-        }
-        for (int x = 0; x < 2 && ok; ++x) {
-          if (!mbar_wait(p_full(x), (unsigned)t & 1, p.error_flag, 44)) { ok = false; break; }
-          tcgen05_fence_after();
-          // O of x += P of x (tensor memory, over the scores' first 64 columns) x the stage's values.
-#pragma unroll
-          for (int k = 0; k < kPairKeys / 16; ++k)
-            umma_bf16_ts(tmem_base + 256u + x * 64u, tmem_base + x * 128u + k * 8u,
-                         dv + (unsigned long long)((k * 16 * 128) >> 4), idesc_pv, t > 0 || k > 0);
-          // S of the next tile of keys over the scores and probabilities of this one: products run in the order
-          // they were issued.  The last arrival says that O is complete.
-          if (t + 1 < ntiles) issue_s(t + 1, x);
-          umma_commit(s_full(x));
-        }
-        if (ok) umma_commit(kv_empty(stage));
-      }
-    }
-  } else {
-    // ---------------------------------------------------------------- softmax of tile x
-    const int x = x_of_warp;
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const unsigned lane_field = (unsigned)(quarter * 32) << 16;
-    const unsigned tmem_s = tmem_base + x * 128u + lane_field, tmem_o = tmem_base + 256u + x * 64u + lane_field;
-    const int tile_first_qpos = ctx - q_len + tile_q0;
-    const int tile_last_qpos = tile_first_qpos + max(rows_used / groups, 1) - 1;
-    const int qpos = row < rows_used ? tile_first_qpos + row / groups : -1;
-    const int group_thread = threadIdx.x - 64 - x * 128;      // 0..127 within the tile's threads
-    float m = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int t = 0; ok && t < ntiles; ++t) {
-      const int stage = t % kPairStages;
-      const int key0 = (tile_lo + t) * kPairKeys;
-      if (!mbar_wait(s_full(x), (unsigned)t & 1, p.error_flag, 45)) { ok = false; break; }
-      tcgen05_fence_after();
-      unsigned s[4][32];
-      __syncwarp();
-#pragma unroll
-      for (int q = 0; q < 4; ++q) tmem_load32(tmem_s + q * 32, s[q]);
-      tmem_load_wait();
-
-      const bool all_visible = rows_used > 0 && key0 + kPairKeys - 1 <= tile_first_qpos &&
-                               (p.window <= 0 || key0 > tile_last_qpos - p.window);
-      float mx = m;
-      if (all_visible && qpos >= 0) {
-        float part[4] = {m, m, m, m};
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          part[j & 3] = max3(part[j & 3], __uint_as_float(s[0][j]), __uint_as_float(s[1][j]));
-          part[(j + 2) & 3] = max3(part[(j + 2) & 3], __uint_as_float(s[2][j]), __uint_as_float(s[3][j]));
-        }
-        mx = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
-      } else {
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = key0 + q * 32 + j;
-            const bool visible = key <= qpos && (p.window <= 0 || key > qpos - p.window);
-            if (!visible) s[q][j] = __float_as_uint(-INFINITY);
-            mx = fmaxf(mx, __uint_as_float(s[q][j]));
-          }
-      }
-      float m_new = m, alpha = 1.f;
-      if ((mx - m) * p.scale_log2 > kLazyLog2) {
-        m_new = mx;
-        alpha = ex2((m - mx) * p.scale_log2);
-      }
-      const bool rescale = alpha != 1.f && m != -INFINITY;
-      const float neg = m_new == -INFINITY ? 0.f : -m_new * p.scale_log2;
-      float2 sums[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg, neg);
-      // Column c of the probabilities holds keys 2c and 2c + 1 of the tile as bfloat16.
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        unsigned packed[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int q = half * 2 + c / 16, j = (2 * c) % 32;
-          const float2 y = fma2(make_float2(__uint_as_float(s[q][j]), __uint_as_float(s[q][j + 1])), scale2, neg2);
-          const float2 ev = make_float2(ex2(y.x), ex2(y.y));
-          sums[c & 3] = add2(sums[c & 3], ev);
-          __nv_bfloat162 hh = __floats2bfloat162_rn(ev.x, ev.y);
-          packed[c] = *reinterpret_cast<unsigned*>(&hh);
-        }
-        tmem_store32(tmem_s + half * 32, packed);
-      }
-      const float2 total = add2(add2(sums[0], sums[1]), add2(sums[2], sums[3]));
-      const float sum = total.x + total.y;
-      // The accumulator: S of this tile arrived after P V of the tile before (the products run in order).
-      if (t >= 1 && __any_sync(0xffffffffu, rescale)) {
-        unsigned o[32];
-#pragma unroll
-        for (int part = 0; part < D / 32; ++part) {
-          tmem_load32(tmem_o + part * 32, o);
-          tmem_load_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_store32(tmem_o + part * 32, o);
-        }
-      }
-      tmem_store_wait();
-      m = m_new;
-      l = l * alpha + sum;
-      // Value rows of keys outside [lo, hi) may hold anything (an unwritten slot): zero them before P V reads them
-      // (the threads of either tile do so, whichever comes first; both write zeros).
-      if (key0 < lo || key0 + kPairKeys > hi) {
-        if (!mbar_wait(kv_full(stage), (unsigned)(t / kPairStages) & 1, p.error_flag, 47)) { ok = false; break; }
-        unsigned char* vt = generic_base + (v_smem - base) + stage * kStageBytes;
-        for (int e = group_thread; e < kPairKeys * 8; e += 128) {
-          const int key = e >> 3;
-          const int kpos = key0 + key;
-          if (kpos < lo || kpos >= hi)
-            *reinterpret_cast<uint4*>(vt + key * 128 + ((e & 7) << 4)) = make_uint4(0, 0, 0, 0);
-        }
-        fence_async_shared();
-      }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(x));
-    }
-    // Output: the arrival after the last P V, the row out of tensor memory, divided by the row's sum.
-    if (ok && ntiles > 0 && mbar_wait(s_full(x), (unsigned)ntiles & 1, p.error_flag, 48)) {
-      tcgen05_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int qi = tile_q0 + row / groups, head = kvh * groups + row % groups;
-      bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
-#pragma unroll
-      for (int half = 0; half < D / 32; ++half) {
-        unsigned o[32];
-        __syncwarp();
-        tmem_load32(tmem_o + half * 32, o);
-        tmem_load_wait();
-        if (row < rows_used) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            unsigned w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = v * 8 + 2 * e;
-              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
-              w[e] = *reinterpret_cast<unsigned*>(&hh);
-            }
-            *reinterpret_cast<uint4*>(dst + half * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-      }
-    }
-  }
-
-  tcgen05_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-  }
-}
-
 // The pool [pages, kv_heads, page_size, head_dim] as a 2-D map of rows of head_dim; a box is 64 dimensions of one
 // page of one head.
 static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int page_size, int head_dim) {
@@ -780,20 +477,6 @@ static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, con
   return (int)launch_pdl(0, attention_tcgen05_kernel<D>, grid, dim3(kAttnThreads), smem, stream, mk, mv, p);
 }
 
-static int launch_tc_attention_pair(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
-                                    cudaStream_t stream) {
-  constexpr size_t smem = 2 * (size_t)kRows * 64 * 2 + 2 * kPairStages * (size_t)kPairKeys * 64 * 2 +
-                          8 * (2 * kPairStages + 4) + 16 + 1024;
-  static_assert(smem <= 232448, "more shared memory than a block may have");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  return (int)launch_pdl(0, attention_tcgen05_pair_kernel, grid, dim3(kPairThreads), smem, stream, mk, mv, p);
-}
-
 }  // namespace li
 
 using namespace li;
@@ -831,16 +514,6 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
                  scale * kLog2eF, window, error_flag};
   const int groups = heads / kv_heads;
   const int tq = kRows / groups;
-  // LITEINFER_TCGEN05_ATTN_PAIR=1 sends long runs of queries at head size 64 to the kernel with two query tiles per
-  // block.  Off by default: measured on B200 it reaches what the kernel with one tile reaches where there is work for
-  // every SM (one prompt of 8,192 tokens: 432 against 429 us, 636 TFLOP/s; four portions of 2,048 over 4,096 keys: 344
-  // against 342 us) and loses where there is not (one prompt of 2,048 tokens: 45.0 against 39.6 us, half as many
-  // blocks).  Its softmax groups, like the other kernel's, are bound by the latency of their own instruction stream
-  // (special-function pipe 60 % busy, 2.5 warps a scheduler), not by the issuing thread.
-  const char* pair_env = getenv("LITEINFER_TCGEN05_ATTN_PAIR");
-  const bool pair_wanted = pair_env && atoi(pair_env) == 1;
-  if (head_dim == 64 && pair_wanted && page_size <= 64 && max_q_len >= 4 * tq)
-    return launch_tc_attention_pair(mk, mv, p, dim3(kv_heads, num_seqs, (max_q_len + 2 * tq - 1) / (2 * tq)), stream);
   const dim3 grid(kv_heads, num_seqs, (max_q_len + tq - 1) / tq);
   return head_dim == 64 ? launch_tc_attention<64>(mk, mv, p, grid, stream) : launch_tc_attention<128>(mk, mv, p, grid, stream);
 }

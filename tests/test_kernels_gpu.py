@@ -538,15 +538,12 @@ def test_gemm_tcgen05_gated_epilogue(M, inter, K, act):
 @pytest.mark.parametrize("heads,kv_heads,page_size", [(4, 1, 16), (32, 8, 16), (8, 8, 32), (16, 2, 64), (128, 1, 16),
                                                       (24, 8, 16), (5, 1, 32), (7, 7, 16)])
 @pytest.mark.parametrize("window", [0, 100])
-@pytest.mark.parametrize("d", [64, 128, "64 with two query tiles per block"])
+@pytest.mark.parametrize("d", [64, 128])
 def test_tcgen05_attention_against_the_plain_kernel(heads, kv_heads, page_size, window, d, monkeypatch):
     """The tcgen05 / TMA / tensor-memory attention kernel: portions, whole prompts and single tokens over shuffled
     pages, NaN in every slot no request owns, contexts that straddle the 64-key tiles; no wait may give up."""
     from liteinfer_b200 import ops
 
-    if isinstance(d, str):              # the variant with two query tiles of 128 rows per block (a switch)
-        monkeypatch.setenv("LITEINFER_TCGEN05_ATTN_PAIR", "1")
-        d = 64
     q_lens, ctx_lens = [1, 130, 1, 7, 64, 2, 257], [700, 190, 1, 7, 64, 129, 300]
     case = _paged_case(torch.bfloat16, heads, kv_heads, d, page_size, q_lens, ctx_lens)
     qkv, k_pool, v_pool = case["qkv"], case["k_pool"], case["v_pool"]
