@@ -37,6 +37,8 @@ struct AttnParams {
   const bf16* v_new;
   int store_new;                // 0: this layer reads pages that another layer writes
   int* error_flag;              // kernels with bounded waits record here where one gave up (may be null)
+  int cluster_merge;            // the splits of a (sequence, KV head) are one thread-block cluster and merge through
+                                // distributed shared memory (attention_stream.cu only)
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {

@@ -21,8 +21,17 @@
 //               the product then holds dimension g*D/8 + j in column g, so a thread ends up with D/4
 //               consecutive dimensions of rows g and g+8.
 //
+// The splits of one (sequence, KV head) merge without a trip to global memory where the launch can make them one
+// thread-block cluster (up to 16 splits, the partial results fitting beside the warps' states): every block leaves
+// its combined result in its own shared memory, the cluster meets at a barrier, the first block reads the others'
+// results through distributed shared memory, merges and writes the output, and a second barrier keeps the others
+// resident until it has read them.  Otherwise the last block to arrive at a counter merges partial results that
+// went through global memory (merge_splits), which costs every block a fence and an atomic and the last one three
+// more trips to L2.
+//
 // With the rotary encoding fused in (see li_paged_attention_mma) the owner of the newest position writes the
 // rotated key and the value to their page and, for its own use, takes them from shared memory.
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -55,8 +64,85 @@ __device__ __forceinline__ unsigned piece_addr(unsigned half_base, int row, int 
   return half_base + (unsigned)((piece >> 3) * 2048 + row * 128 + (((piece & 7) ^ (row & 7)) << 4));
 }
 
+// The end of a block whose (sequence, KV head) is one cluster of splits (rank = split): see the head of the file.
+// A function of its own, so that its registers are not the loop's.
+template <int D>
+__device__ __noinline__ void merge_in_cluster(const AttnParams& p, const float* os, const float* ms, float* ls, int groups,
+                                              int q_begin, int kvh, int split) {
+  // ---- the splits are one cluster (rank = split).  This block's result: mine [groups][D], normalised, and its
+  // log-sum-exp per row, behind the warps' states in this block's own shared memory.
+  float* mine = ls + kWarps * 16;                        // [16][D]
+  float* mine_lse = mine + 16 * D;                       // [16]
+  float* weights = mine_lse + 16;                        // [16][17], the first block only
+  for (int e = threadIdx.x; e < groups * D; e += kWarps * 32) {
+    const int row = e / D, d = e % D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, ms[w * 16 + row]);
+    float denom = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float mw = ms[w * 16 + row];
+      const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - mx);
+      denom += wgt * ls[w * 16 + row];
+      acc += wgt * os[((size_t)w * 16 + row) * D + d];
+    }
+    mine[row * D + d] = denom > 0.f ? acc / denom : 0.f;
+    if (d == 0) mine_lse[row] = denom > 0.f ? mx + log2f(denom) : -INFINITY;
+  }
+  cluster_sync_all();                                    // every block's result is in place (release / acquire)
+  if (split == 0) {
+    const int S = p.num_splits;
+    auto remote = [&](const float* local, int rank) {    // the same place in the shared memory of block `rank`
+      unsigned addr;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_addr(local)), "r"(rank));
+      return addr;
+    };
+    for (int e = threadIdx.x; e < groups * S; e += kWarps * 32) {
+      const int row = e / S, s = e % S;
+      float v;
+      asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote(mine_lse + row, s)));
+      weights[row * 17 + s] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < groups) {
+      float* w = weights + threadIdx.x * 17;
+      float mx = -INFINITY;
+      for (int s = 0; s < S; ++s) mx = fmaxf(mx, w[s]);
+      float denom = 0.f;
+      for (int s = 0; s < S; ++s) {
+        const float e = w[s] == -INFINITY ? 0.f : exp2f(w[s] - mx);
+        w[s] = e;
+        denom += e;
+      }
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
+      for (int s = 0; s < S; ++s) w[s] *= inv;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < groups * (D / 4); e += kWarps * 32) {
+      const int row = e / (D / 4), d4 = e % (D / 4);
+      const float* w = weights + row * 17;
+      float4 v[16];
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < S)
+          asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(v[s].x), "=f"(v[s].y), "=f"(v[s].z), "=f"(v[s].w) : "r"(remote(mine + row * D + d4 * 4, s)));
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < S) {
+          acc.x += w[s] * v[s].x; acc.y += w[s] * v[s].y; acc.z += w[s] * v[s].z; acc.w += w[s] * v[s].w;
+        }
+      bf16* dst = p.out + (size_t)q_begin * p.out_row_stride + (size_t)(kvh * groups + row) * D + d4 * 4;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    }
+  }
+  cluster_sync_all();                                    // nobody leaves while the first block reads
+}
+
 // kRing: slots per warp; up to kRing - 1 groups are on their way while one is multiplied.
-template <int D, int kRing>
+template <int D, int kRing, bool kCluster>
 __global__ void __launch_bounds__(kWarps * 32, D == 64 ? 5 : 2)   // blocks per SM that the rings leave room for
 attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const AttnParams p) {
@@ -369,12 +455,22 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
   }
   __syncthreads();
-  combine_warps<D>(p, os, ms, ls, groups, groups, q_begin, 0, kvh, split);
-  if (p.num_splits == 1) return;
-  merge_splits<D>(p, generic_base, &is_last, groups, groups, q_begin, 0, kvh, 0);
+  if (!kCluster) {
+    combine_warps<D>(p, os, ms, ls, groups, groups, q_begin, 0, kvh, split);
+    if (p.num_splits == 1) return;
+    merge_splits<D>(p, generic_base, &is_last, groups, groups, q_begin, 0, kvh, 0);
+    return;
+  }
+  merge_in_cluster<D>(p, os, ms, ls, groups, q_begin, kvh, split);
 }
 
-template <int D, int kRing> constexpr size_t stream_smem() { return (size_t)kWarps * kRing * 2 * kGroupKeys * D * 2 + 1024; }
+// The rings, which at the end hold the warps' states ([4][16][D] floats and two of [4][16]) and, with a cluster's
+// merge, the block's own result ([16][D], [16]) and the first block's weights ([16][17]).
+template <int D, int kRing> constexpr size_t stream_smem() {
+  constexpr size_t rings = (size_t)kWarps * kRing * 2 * kGroupKeys * D * 2;
+  constexpr size_t states = ((size_t)kWarps * 16 * D + 2 * kWarps * 16 + 16 * D + 16 + 16 * 17) * sizeof(float);
+  return (rings > states ? rings : states) + 1024;
+}
 
 // The pool [pages, kv_heads, page_size, D] as a 2-D map of rows of D with boxes of 16 rows x 64 dimensions.
 static bool make_group_map(CUtensorMap* map, const void* pool, long rows, int head_dim) {
@@ -406,13 +502,64 @@ template <int D, int kRing>
 int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int num_seqs, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_stream_kernel<D, kRing>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)stream_smem<D, kRing>());
+    cudaError_t e = cudaFuncSetAttribute(attention_stream_kernel<D, kRing, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stream_smem<D, kRing>());
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_stream_kernel<D, kRing, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)stream_smem<D, kRing>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const dim3 grid(p.num_splits, p.kv_heads, num_seqs);
-  return (int)launch_pdl(num_seqs, attention_stream_kernel<D, kRing>, grid, dim3(kWarps * 32), stream_smem<D, kRing>(), stream, mk, mv, p);
+  if (!p.cluster_merge)
+    return (int)launch_pdl(num_seqs, attention_stream_kernel<D, kRing, false>, grid, dim3(kWarps * 32), stream_smem<D, kRing>(), stream, mk, mv, p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(kWarps * 32);
+  config.dynamicSmemBytes = stream_smem<D, kRing>();
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = p.num_splits;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = pdl_enabled(num_seqs) ? 2 : 1;
+  return (int)cudaLaunchKernelEx(&config, attention_stream_kernel<D, kRing, true>, mk, mv, p);
+}
+
+// How many clusters of `splits` blocks of the kernel the device holds at once (0: such a cluster cannot be launched).
+template <int D, int kRing>
+int stream_cluster_capacity(int splits) {
+  static int cached[17] = {0};
+  static bool known[17] = {false};
+  if (splits < 2 || splits > 16) return 0;
+  if (known[splits]) return cached[splits];
+  int clusters = 0;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(splits, 148, 16);
+  config.blockDim = dim3(kWarps * 32);
+  config.dynamicSmemBytes = stream_smem<D, kRing>();
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = splits;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  if (cudaFuncSetAttribute(attention_stream_kernel<D, kRing, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)stream_smem<D, kRing>()) != cudaSuccess ||
+      (splits > 8 && cudaFuncSetAttribute(attention_stream_kernel<D, kRing, true>,
+                                          cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) ||
+      cudaOccupancyMaxActiveClusters(&clusters, attention_stream_kernel<D, kRing, true>, &config) != cudaSuccess) {
+    cudaGetLastError();
+    clusters = 0;
+  }
+  cached[splits] = clusters;
+  known[splits] = true;
+  return clusters;
 }
 
 // Blocks of the kernel that the current device holds at once; 0 if the query fails.
@@ -423,9 +570,9 @@ int stream_capacity() {
   int device = 0, sms = 0, per_sm = 0;
   if (cudaGetDevice(&device) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-      cudaFuncSetAttribute(attention_stream_kernel<D, kRing>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaFuncSetAttribute(attention_stream_kernel<D, kRing, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)stream_smem<D, kRing>()) != cudaSuccess ||
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_stream_kernel<D, kRing>, kWarps * 32,
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_stream_kernel<D, kRing, false>, kWarps * 32,
                                                     stream_smem<D, kRing>()) != cudaSuccess)
     return 0;
   capacity = per_sm * sms;
@@ -443,6 +590,12 @@ LI_EXPORT int li_paged_attention_stream_supports(int heads, int kv_heads, int he
   if (kv_heads < 1 || heads % kv_heads || heads / kv_heads > 16) return 0;
   if (head_dim != 64 && head_dim != 128) return 0;
   return page_size >= 16 && page_size % 16 == 0;
+}
+
+// Clusters of `splits` blocks that the device holds at once; 0 where the splits cannot be one cluster.
+LI_EXPORT int li_paged_attention_stream_cluster_capacity(int head_dim, int splits) {
+  return head_dim == 64 ? stream_cluster_capacity<64, kRing64>(splits)
+                        : (head_dim == 128 ? stream_cluster_capacity<128, kRing128>(splits) : 0);
 }
 
 LI_EXPORT int li_paged_attention_stream_capacity(int head_dim) {
@@ -476,7 +629,16 @@ LI_EXPORT int li_paged_attention_stream(const void* q, int q_row_stride, void* o
   AttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                block_table, table_stride, query_start_loc, context_lens, seq_index, heads, kv_heads, page_size,
                num_pages, -1, scale * kLog2e, window, num_splits, partial_out, partial_lse, counters,
-               rope_inv_freq, (const bf16*)k_new, (const bf16*)v_new, store_new, error_flag};
+               rope_inv_freq, (const bf16*)k_new, (const bf16*)v_new, store_new, error_flag, 0};
+  // LITEINFER_ATTN_CLUSTER_MERGE=1 (read at every call) merges the splits as clusters where all the launch's
+  // clusters are resident at once.  Off by default: measured on B200 the launch alone gains (batch 8 at 4,096
+  // tokens: 17.5 against 18.6 us; batch 1: 8.6 against 10.7), but inside the decode step, where every kernel starts
+  // while the one before it drains (programmatic dependent launch), a launch of clusters starts later than a
+  // launch of single blocks does, and the step loses more than the merge gains (1.065 against 0.948 ms).
+  const char* cluster_env = getenv("LITEINFER_ATTN_CLUSTER_MERGE");
+  if (cluster_env && atoi(cluster_env) == 1 && num_splits >= 2 && num_splits <= 16 &&
+      li_paged_attention_stream_cluster_capacity(head_dim, num_splits) >= kv_heads * num_seqs)
+    p.cluster_merge = 1;
   if ((page_size & (page_size - 1)) == 0)
     for (int s = 0; s < 31; ++s)
       if ((1 << s) == page_size) p.page_shift = s;

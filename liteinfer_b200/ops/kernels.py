@@ -54,6 +54,7 @@ _SIGNATURES = {
         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "li_paged_attention_stream_supports": ("attention_stream", [c_int, c_int, c_int, c_int]),
     "li_paged_attention_stream_capacity": ("attention_stream", [c_int]),
+    "li_paged_attention_stream_cluster_capacity": ("attention_stream", [c_int, c_int]),
     "li_paged_attention_mma_counters": ("attention_mma", [c_int, c_int, c_int, c_int]),
     "li_paged_attention_mma_decode_capacity": ("attention_mma", [c_int]),
     "li_paged_attention_tcgen05": ("attention_tcgen05", [
@@ -615,7 +616,35 @@ def decode_splits_for(num_decode: int, kv_heads: int, max_context_len: int, head
     tiles = -(-max_context_len // 64)
     if tiles < 4:
         return 1
-    return max(1, min(decode_capacity(head_dim, streaming) // max(1, num_decode * kv_heads), tiles // 2, 32))
+    pairs = max(1, num_decode * kv_heads)
+    splits = max(1, min(decode_capacity(head_dim, streaming) // pairs, tiles // 2, 32))
+    if streaming and cluster_merge_wanted() and splits > 1:
+        # The streaming kernel can merge the splits of a sequence through distributed shared memory when they are
+        # one thread-block cluster (16 blocks at most) and every cluster of the launch is resident at once: then a
+        # count that allows it is worth more than the last few splits (see attention_stream.cu for the figures).
+        for fewer in range(min(splits, 16), max(1, splits // 2) - 1, -1):
+            if fewer > 1 and cluster_capacity(head_dim, fewer) >= pairs:
+                return fewer
+    return splits
+
+
+def cluster_merge_wanted() -> bool:
+    """The switch LITEINFER_ATTN_CLUSTER_MERGE=1 (off by default; the kernel's entry point reads the same variable)."""
+    return os.environ.get("LITEINFER_ATTN_CLUSTER_MERGE", "0") == "1"
+
+
+_cluster_capacity: dict[tuple[int, int], int] = {}
+
+
+def cluster_capacity(head_dim: int, splits: int) -> int:
+    """Clusters of `splits` blocks of the streaming decode kernel that the device holds at once (0: none)."""
+    key = (head_dim, splits)
+    if key not in _cluster_capacity:
+        clusters = 0
+        if torch.cuda.is_available():
+            clusters = int(_fn("li_paged_attention_stream_cluster_capacity")(head_dim, splits))
+        _cluster_capacity[key] = clusters
+    return _cluster_capacity[key]
 
 
 def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,

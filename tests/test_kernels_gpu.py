@@ -344,15 +344,25 @@ def _plan_for(q_lens, ctx_lens):
                          max_decode_context_len=max([ctx_lens[i] for i in dec], default=0))
 
 
+def _splits(splits, monkeypatch):
+    """`"11 as a cluster"`: 11 splits with the streaming kernel's merge through a cluster switched on."""
+    if isinstance(splits, str):
+        monkeypatch.setenv("LITEINFER_ATTN_CLUSTER_MERGE", "1")
+        return int(splits.split()[0])
+    return splits
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [(4, 2, 64, 16), (8, 8, 64, 8), (32, 8, 128, 16),
                                                                (6, 2, 128, 5), (64, 1, 64, 32), (5, 1, 64, 16)])
 @pytest.mark.parametrize("window", [0, 100])
-@pytest.mark.parametrize("splits", [None, 1, 3, 32])
-def test_tensor_core_attention_against_the_plain_kernel(heads, kv_heads, head_dim, page_size, window, splits):
+@pytest.mark.parametrize("splits", [None, 1, 3, 32, "2 as a cluster", "11 as a cluster", "16 as a cluster"])
+def test_tensor_core_attention_against_the_plain_kernel(heads, kv_heads, head_dim, page_size, window, splits,
+                                                        monkeypatch):
     """Portions and single tokens, planned (split decode rows beside unsplit portions) or not, over
     contexts that straddle the 64-key tiles, with NaN in every slot no request owns."""
     from liteinfer_b200 import ops
 
+    splits = _splits(splits, monkeypatch)
     q_lens = [1, 130, 1, 7, 64, 1, 1, 2]
     ctx_lens = [700, 190, 1, 7, 64, 63, 65, 129]
     case = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page_size, q_lens, ctx_lens)
@@ -373,13 +383,15 @@ def test_tensor_core_attention_against_the_plain_kernel(heads, kv_heads, head_di
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [(32, 8, 64, 16), (8, 8, 64, 8), (16, 1, 128, 16),
                                                                (6, 2, 128, 5), (5, 1, 64, 32)])
 @pytest.mark.parametrize("window", [0, 100])
-@pytest.mark.parametrize("splits", [1, 3, 32])
-def test_decode_attention_with_rotary_and_cache_write_fused(heads, kv_heads, head_dim, page_size, window, splits):
+@pytest.mark.parametrize("splits", [1, 3, 32, "11 as a cluster", "16 as a cluster"])
+def test_decode_attention_with_rotary_and_cache_write_fused(heads, kv_heads, head_dim, page_size, window, splits,
+                                                            monkeypatch):
     """One launch that rotates q and the newest key, stores key and value and attends, against the two
     launches it replaces: the same output and the same pages, to the bit; contexts end at, just before and
     just after the edges of pages and of 64-key tiles."""
     from liteinfer_b200 import ops
 
+    splits = _splits(splits, monkeypatch)
     ctx_lens = [700, 1, 64, 65, 63, 129, 320, 16, 17]
     q_lens = [1] * len(ctx_lens)
     case = _paged_case(torch.bfloat16, heads, kv_heads, head_dim, page_size, q_lens, ctx_lens, seed=3)
@@ -441,6 +453,17 @@ def test_split_policy():
     assert decode_splits_for(1, 8, 4096) == 32
     assert 2 <= decode_splits_for(8, 8, 4096) <= 16
     assert decode_splits_for(64, 8, 4096) == 1
+
+
+def test_split_policy_with_the_cluster_merge(monkeypatch):
+    """With the switch on, the streaming kernel gets a count whose splits can be one cluster each, all of them
+    resident at once."""
+    from liteinfer_b200.ops import decode_splits_for, kernels
+
+    monkeypatch.setenv("LITEINFER_ATTN_CLUSTER_MERGE", "1")
+    for batch in (1, 4, 8, 16):
+        chosen = decode_splits_for(batch, 8, 4096, 64, True)
+        assert 2 <= chosen <= 16 and kernels.cluster_capacity(64, chosen) >= batch * 8, (batch, chosen)
 
 
 def _interleave(gate, up):
