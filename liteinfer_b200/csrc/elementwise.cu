@@ -281,9 +281,39 @@ __global__ void scatter_tokens_kernel(int* __restrict__ tokens, const int* __res
   if (d >= 0) tokens[d] = source[src[i]];
 }
 
+// A step's batch from pinned host memory (read by the kernel itself, over the bus) into its place on the device, and
+// then the late tokens into theirs: one launch of one block instead of a copy and a launch.
+__global__ void __launch_bounds__(1024) stage_batch_kernel(int* __restrict__ device, const int* __restrict__ host, int words,
+                                                           int* __restrict__ tokens, const int* __restrict__ dst,
+                                                           const int* __restrict__ src, const int* __restrict__ source,
+                                                           int n_late) {
+  for (int i = threadIdx.x; i < words; i += blockDim.x) device[i] = host[i];
+  if (n_late <= 0 || source == nullptr) return;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_late; i += blockDim.x) {
+    const int d = dst[i];
+    if (d >= 0) tokens[d] = source[src[i]];
+  }
+}
+
 }  // namespace li
 
 using namespace li;
+
+// device[0 .. words) = host[0 .. words), then tokens[dst[i]] = source[src[i]] wherever dst[i] >= 0 (tokens, dst and
+// src lie inside `device`; source may be null: nothing is placed then).  `host` must be page-locked memory that the
+// device can read in place; where it cannot, LI_ERR_UNSUPPORTED is returned and nothing is launched.
+LI_EXPORT int li_stage_batch(int* device, const int* host, int words, int* tokens, const int* dst, const int* src,
+                             const int* source, int n_late, cudaStream_t stream) {
+  if (words <= 0) return 0;
+  void* mapped = nullptr;
+  if (cudaHostGetDevicePointer(&mapped, const_cast<int*>(host), 0) != cudaSuccess || mapped == nullptr) {
+    cudaGetLastError();
+    return LI_ERR_UNSUPPORTED;
+  }
+  stage_batch_kernel<<<1, 1024, 0, stream>>>(device, static_cast<const int*>(mapped), words, tokens, dst, src, source, n_late);
+  LI_LAUNCH_CHECK();
+}
 
 LI_EXPORT int li_scatter_tokens(int* tokens, const int* dst, const int* src, const int* source, int n,
                                 cudaStream_t stream) {

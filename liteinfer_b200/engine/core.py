@@ -97,6 +97,8 @@ class EngineCore:
         self._in_flight: _Launched | None = None
         self._event_sets: list[list] = []   # CUDA events that mark the forward and the sampler of a step on the stream
         self._host_buffers: list[tuple[torch.Tensor, object]] = []   # pinned buffers for the sampled tokens, with their events
+        self._copy_stream = None            # the stream those copies run on (made at the first one)
+        self._sampled_ready = None
 
     # ----------------------------------------------------------------- load
     def load(self) -> None:
@@ -222,7 +224,8 @@ class EngineCore:
         try:
             if events:
                 events[0].record()
-            logits = self.runner.step(entries, before.sampled if before is not None else None)
+            # The logits are sampled from on this stream before the next step is launched: no copy of them.
+            logits = self.runner.step(entries, before.sampled if before is not None else None, borrow=True)
             if events:
                 events[1].record()
         except CacheExhaustedError as error:
@@ -243,12 +246,20 @@ class EngineCore:
             if events:
                 events[2].record()
             if self.device.type == "cuda":
-                # The tokens start for the host now, behind this step on the stream: a copy asked for later would
-                # queue behind the step launched meanwhile.
+                # The tokens start for the host now, behind this step's sampling: a copy asked for later would queue
+                # behind the step launched meanwhile.  They travel on a stream of their own, so that the next step
+                # (which reads them on the device) does not wait for the copy either.
                 host_copy, copied = self._host_buffers.pop() if self._host_buffers else (
                     torch.empty(self.config.max_num_seqs, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
-                host_copy[:len(sampling)].copy_(sampled, non_blocking=True)
-                copied.record()
+                if self._copy_stream is None:
+                    self._copy_stream = torch.cuda.Stream(self.device)
+                    self._sampled_ready = torch.cuda.Event()
+                self._sampled_ready.record()
+                self._copy_stream.wait_event(self._sampled_ready)
+                with torch.cuda.stream(self._copy_stream):
+                    host_copy[:len(sampling)].copy_(sampled, non_blocking=True)
+                    copied.record()
+                sampled.record_stream(self._copy_stream)
             for seq in sampling:
                 places.append(len(seq.output_token_ids))
                 seq.output_token_ids.append(PENDING)

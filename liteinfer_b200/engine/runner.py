@@ -45,6 +45,11 @@ def ops_scatter(tokens, dst, src, source):
     return ops.scatter_tokens(tokens, dst, src, source)
 
 
+def ops_stage(device, host, tokens, dst, src, source) -> bool:
+    from liteinfer_b200 import ops
+    return ops.stage_batch(device, host, tokens, dst, src, source)
+
+
 @dataclass
 class StepEntry:
     """One request's share of a step: its next tokens and the places among them whose logits are wanted.
@@ -357,6 +362,19 @@ class ModelRunner:
                 if not 0 <= place < n:
                     raise ValueError(f"request {entry.request_id!r} wants logits at {place}, but brings {n} tokens")
 
+    def _stage(self, batch: _Batch, dev: torch.Tensor, host: torch.Tensor, entries: list[StepEntry], late_source) -> None:
+        """The staged batch from its pinned buffer to the device and the late tokens into it: one kernel that reads
+        the pinned buffer in place where the batch is small, else a copy and the scatter."""
+        late = any(e.late is not None for e in entries)
+        if late and late_source is None:
+            raise ValueError("an entry's token is to be read on the device, but no tensor of sampled tokens was given")
+        if dev.is_cuda:
+            v = batch.views(dev)
+            if ops_stage(dev, host, v.tok, v.late_dst, v.late_src, late_source if late else None):
+                return
+        dev.copy_(host, non_blocking=True)
+        self._place_late_tokens(batch, dev, entries, late_source)
+
     @staticmethod
     def _place_late_tokens(batch: _Batch, dev: torch.Tensor, entries: list[StepEntry], late_source) -> None:
         """Tokens that were sampled on the device and never read: from `late_source` into the batch, on the device."""
@@ -434,7 +452,7 @@ class ModelRunner:
         return graph
 
     def _replay(self, graph: _DecodeGraph | _PaddedGraph, entries: list[StepEntry],
-                late_source: torch.Tensor | None = None) -> torch.Tensor:
+                late_source: torch.Tensor | None = None, borrow: bool = False) -> torch.Tensor:
         if graph.graph is None:
             try:
                 graph.capture(self)
@@ -445,18 +463,21 @@ class ModelRunner:
                 raise
         starts = [self.cache.length(e.request_id) for e in entries]
         wanted = graph.stage(entries, self.cache, starts)
-        graph.device_buffer.copy_(graph.host, non_blocking=True)
+        self._stage(graph.batch, graph.device_buffer, graph.host, entries, late_source)
         graph.copied.record()
-        self._place_late_tokens(graph.batch, graph.device_buffer, entries, late_source)
         graph.graph.replay()
         self.graph_launches += graph.launches
         self.graph_replays += 1
-        return graph.logits.clone() if wanted is None else graph.logits[:wanted].clone()
+        logits = graph.logits if wanted is None else graph.logits[:wanted]
+        return logits if borrow else logits.clone()
 
     # ----------------------------------------------------------------- step
-    def step(self, entries: list[StepEntry], late_source: torch.Tensor | None = None) -> torch.Tensor:
+    def step(self, entries: list[StepEntry], late_source: torch.Tensor | None = None,
+             borrow: bool = False) -> torch.Tensor:
         """Logits [number of wanted places, vocab], in the order of `entries` and of each entry's `want`.
-        `late_source` (int32, on the device): where the tokens of entries marked `late` are read from."""
+        `late_source` (int32, on the device): where the tokens of entries marked `late` are read from.
+        `borrow`: the caller is done with the logits (on this stream) before it calls `step` again, so a step that a
+        graph replays may return the graph's own buffer instead of a copy of it."""
         self._validate(entries)
         ids = [e.request_id for e in entries]
         totals = [self.cache.length(e.request_id) + len(e.tokens) for e in entries]
@@ -464,7 +485,7 @@ class ModelRunner:
         try:
             graph = self._graph_for(entries, totals) or self._padded_graph_for(entries, totals)
             if graph is not None:
-                logits = self._replay(graph, entries, late_source)
+                logits = self._replay(graph, entries, late_source, borrow)
             else:
                 context = self.build_context(entries, late_source)
                 with kernels.on_current_stream():

@@ -33,6 +33,7 @@ _functions: dict[str, ctypes._CFuncPtr] = {}
 _SIGNATURES = {
     "li_embedding": ("elementwise", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "li_scatter_tokens": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "li_stage_batch": ("elementwise", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "li_rmsnorm": ("elementwise", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                    c_int, c_void_p]),
     "li_add": ("elementwise", [c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
@@ -226,6 +227,30 @@ def scatter_tokens(tokens: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, s
     _check(_fn("li_scatter_tokens")(tokens.data_ptr(), dst.data_ptr(), src.data_ptr(), source.data_ptr(), dst.numel(),
                                     _stream()), "scatter_tokens")
     return tokens
+
+
+# Batches up to this many 32-bit words are brought to the device by a kernel that reads the pinned buffer in place
+# (one block; a copy engine's latency is longer than that for a few kilobytes, shorter for many).
+STAGE_KERNEL_MAX_WORDS = 16384
+
+
+def stage_batch(device: torch.Tensor, host: torch.Tensor, tokens: torch.Tensor, dst: torch.Tensor, src: torch.Tensor,
+                source: torch.Tensor | None) -> bool:
+    """device[:] = host[:] (int32; `host` pinned), then tokens[dst[i]] = source[src[i]] wherever dst[i] >= 0, in one
+    launch.  False (and nothing done) where the buffer is too large for that or the device cannot read `host` in
+    place: the caller then copies and scatters."""
+    _on_gpu(device, tokens, dst, src, source)
+    for t, what in ((device, "device"), (host, "host"), (tokens, "tokens"), (dst, "dst"), (src, "src")):
+        _int32(t, what)
+    words = device.numel()
+    if words > STAGE_KERNEL_MAX_WORDS or host.numel() != words or not host.is_pinned():
+        return False
+    code = _fn("li_stage_batch")(device.data_ptr(), host.data_ptr(), words, tokens.data_ptr(), dst.data_ptr(),
+                                 src.data_ptr(), _ptr(source), dst.numel() if source is not None else 0, _stream())
+    if code == 100001:        # LI_ERR_UNSUPPORTED: the device cannot read this host memory in place
+        return False
+    _check(code, "stage_batch")
+    return True
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

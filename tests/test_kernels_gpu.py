@@ -446,6 +446,35 @@ def test_tensor_core_attention_finds_one_far_key_under_splits():
                                        rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("words,n_late", [(40, 0), (2105, 8), (16384, 64), (16385, 3)])
+def test_stage_batch_equals_copy_and_scatter(words, n_late):
+    """The kernel that reads a pinned batch in place and places the late tokens gives what the copy followed by the
+    scatter gives; a batch beyond its limit is refused (the caller copies)."""
+    from liteinfer_b200 import ops
+
+    g = torch.Generator().manual_seed(words)
+    tok_len, n = 16, max(n_late, 1)                      # layout: tokens [0, 16), dst [20, 20 + n), src after it
+    host = torch.randint(0, 1000, (words,), generator=g, dtype=torch.int32)
+    dst = torch.full((n,), -1, dtype=torch.int32)
+    places = torch.randperm(tok_len, generator=g).to(torch.int32)
+    for i in range(0, min(n_late, 2 * tok_len), 2):      # every second entry names a place, each place once
+        dst[i] = places[i // 2]
+    host[20:20 + n] = dst
+    host[20 + n:20 + 2 * n] = torch.randint(0, 32, (n,), generator=g, dtype=torch.int32)
+    host = host.pin_memory()
+    source = torch.randint(0, 50000, (32,), generator=g, dtype=torch.int32).cuda()
+    views = lambda t: (t[:tok_len], t[20:20 + n], t[20 + n:20 + 2 * n])
+    want = host.cuda()
+    if n_late:
+        ops.scatter_tokens(*views(want), source)
+    device = torch.full((words,), -7, dtype=torch.int32, device="cuda")
+    done = ops.stage_batch(device, host, *views(device), source if n_late else None)
+    assert done == (words <= ops.kernels.STAGE_KERNEL_MAX_WORDS)
+    if done:
+        torch.cuda.synchronize()
+        assert torch.equal(device, want)
+
+
 def test_split_policy():
     from liteinfer_b200.ops import decode_splits_for
 
