@@ -230,6 +230,10 @@ CASES = {
     "tcgen05_gate_up_b64": lambda: tcgen05_gemm(64, 16384, 2048),
     "tcgen05_down_b64": lambda: tcgen05_gemm(64, 2048, 8192),
     "library_down_b64": lambda: library_gemm(64, 2048, 8192),
+    "library_qkv_b64": lambda: library_gemm(64, 3072, 2048),
+    "library_o_b64": lambda: library_gemm(64, 2048, 2048),
+    "library_head_b64": lambda: library_gemm(64, 128256, 2048),
+    "library_gate_up_b24": lambda: library_gemm(24, 16384, 2048),
     "library_qkv_2048": lambda: library_gemm(2048, 3072, 2048),
     "library_gate_up_2048": lambda: library_gemm(2048, 16384, 2048),
     "library_down_2048": lambda: library_gemm(2048, 2048, 8192),
