@@ -112,8 +112,8 @@ __device__ __forceinline__ void combine_warps(const AttnParams& p, const float* 
 }
 
 // The block that arrives last at the counter of its (sequence, KV head, query tile) merges the splits' partial
-// results (in split order) into the output and leaves the counter at zero.  Called by all threads of every block
-// of a split launch, after the block's partial result is written; `smem` needs 64 x 33 floats.
+// results (in split order, eight at a time) into the output and leaves the counter at zero.  Called by all threads
+// of every block of a split launch, after the block's partial result is written (`smem_raw` is not used any more).
 template <int D>
 __device__ __forceinline__ void merge_splits(const AttnParams& p, unsigned char* smem_raw, bool* is_last_flag,
                                              int rows_used, int groups, int q_begin, int q0, int kvh, int qtile) {
@@ -128,64 +128,47 @@ __device__ __forceinline__ void merge_splits(const AttnParams& p, unsigned char*
   __syncthreads();
   if (!*is_last_flag) return;
   __threadfence();
-  // All loads of a phase are issued before any is used: the merge costs a few trips to L2, not one per split.
-  constexpr int kMaxSplits = 32;
-  float* wsm = reinterpret_cast<float*>(smem_raw);              // [64 rows][kMaxSplits + 1] weights
+  // Every thread merges four dimensions of one row by itself, eight splits at a time: the eight log-sum-exps and the
+  // eight partial rows are asked for together (one trip to L2 per eight splits), and the running result is rescaled
+  // to the largest log-sum-exp seen so far, as a softmax over blocks of keys would be.  No thread waits for another.
   const int S = p.num_splits;
-  __syncthreads();
-  for (int e0 = 0; e0 < rows_used * S; e0 += kWarps * 32 * 4) {
-    float v[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int e = e0 + j * kWarps * 32 + threadIdx.x;
-      if (e < rows_used * S) {
-        const int row = e / S, sidx = e - row * S;
-        const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-        v[j] = __ldcg(p.partial_lse + ((size_t)(q_begin + qi) * p.heads + head) * S + sidx);
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int e = e0 + j * kWarps * 32 + threadIdx.x;
-      if (e < rows_used * S) wsm[(e / S) * (kMaxSplits + 1) + (e % S)] = v[j];
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x < rows_used) {
-    float* w = wsm + threadIdx.x * (kMaxSplits + 1);
-    float mx = -INFINITY;
-    for (int sidx = 0; sidx < S; ++sidx) mx = fmaxf(mx, w[sidx]);
-    float denom = 0.f;
-    for (int sidx = 0; sidx < S; ++sidx) {
-      const float e = w[sidx] == -INFINITY ? 0.f : exp2f(w[sidx] - mx);
-      w[sidx] = e;
-      denom += e;
-    }
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    for (int sidx = 0; sidx < S; ++sidx) w[sidx] *= inv;
-  }
-  __syncthreads();
   for (int e = threadIdx.x; e < rows_used * (D / 4); e += kWarps * 32) {
     const int row = e / (D / 4), d4 = e % (D / 4);
     const int qi = q0 + row / groups, head = kvh * groups + row % groups;
-    const float4* src = reinterpret_cast<const float4*>(
-        p.partial_out + ((size_t)(q_begin + qi) * p.heads + head) * S * D) + d4;
-    const float* w = wsm + row * (kMaxSplits + 1);
+    const size_t first = ((size_t)(q_begin + qi) * p.heads + head) * S;
+    const float* lse = p.partial_lse + first;
+    const float4* src = reinterpret_cast<const float4*>(p.partial_out + first * D) + d4;
+    float mx = -INFINITY, denom = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < S; s0 += 8) {
+      float w[8];
       float4 v[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (s0 + j < S) v[j] = __ldcg(src + (size_t)(s0 + j) * (D / 4));
+        if (s0 + j < S) {
+          w[j] = __ldcg(lse + s0 + j);
+          v[j] = __ldcg(src + (size_t)(s0 + j) * (D / 4));
+        }
+      float top = mx;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < S) top = fmaxf(top, w[j]);
+      if (top == -INFINITY) continue;            // nothing seen yet in any of these splits
+      const float keep = mx == -INFINITY ? 0.f : exp2f(mx - top);
+      denom *= keep;
+      acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+      mx = top;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (s0 + j < S) {
-          const float wj = w[s0 + j];
+          const float wj = w[j] == -INFINITY ? 0.f : exp2f(w[j] - top);
+          denom += wj;
           acc.x += wj * v[j].x; acc.y += wj * v[j].y; acc.z += wj * v[j].z; acc.w += wj * v[j].w;
         }
     }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
     bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d4 * 4;
-    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
   }
   if (threadIdx.x == 0) p.counters[counter_index] = 0;   // ready for the next launch
 }
