@@ -6,8 +6,9 @@ Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 with ever
 sequence near the benchmark context (4,096), timed on the device over K decode
 steps of the engine's own step function and sampler.  `e2e` is the same measured
 through the Python entry point (`LLM.generate`: host token ids in, host token
-ids out, one host-to-device copy of the step's inputs and one device-to-host read
-of the sampled tokens every step).  `prefill` times one 2,048-token prompt,
+ids out; every step its inputs travel from pinned host memory to the device, read
+in place by the kernel that stages the batch, and the sampled tokens travel back
+to the host).  `prefill` times one 2,048-token prompt,
 `roofline` relates the decode step to the bytes it must read, `points` holds
 decode at batch 1 and 64.  Weights are random (seeded) and token ids synthetic.
 """
