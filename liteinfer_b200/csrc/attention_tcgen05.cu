@@ -1,14 +1,14 @@
 // Paged attention for prompts and portions of prompts on the fifth-generation tensor cores
 // (bfloat16, head sizes 64 and 128, pages of 16, 32 or 64 tokens).
 //
-// Rule as in attention_generic.cu (liteinfer/models/attention.py:24-27,69-84).  A block owns 128
-// rows for one KV head, a row being (query token, head of the group), and walks the visible keys
-// in tiles of 64:
+// Rule as in attention_generic.cu (liteinfer/models/attention.py:24-27,69-84).  A block owns one tile of 128
+// rows for one KV head (two tiles at head size 128, see KvStages below), a row being (query token, head of the
+// group), and walks the visible keys in tiles of 64.  Per tile of rows:
 //
 //   loader  (warp 0)    TMA: each page of a tile's keys and values is one box of the pool's tensor map per 64
-//                       dimensions, landing in 128-byte-swizzled shared memory, five tiles ahead at most (six at
-//                       head size 128); lane b requests page b of a tile, and one barrier per stage counts keys
-//                       and values.  The block table's entries are in the warp's registers, 32 at a time, the
+//                       dimensions, landing in 128-byte-swizzled shared memory, five tiles ahead at most;
+//                       lane b requests page b of a tile, and one barrier per stage counts keys and values
+//                       (one loader for the block, whatever its number of query tiles).  The block table's entries are in the warp's registers, 32 at a time, the
 //                       next 32 on their way.
 //   issuer  (warp 1)    tcgen05.mma: S = Q K^T (128 x 64, K = head size) into one of two score buffers in
 //                       tensor memory, then O += P V (128 x 64 per 64 dimensions, K 64 keys, P from tensor
@@ -36,12 +36,16 @@
 // 597 with the probabilities in tensor memory, where softmax and products of one query tile form one chain),
 // two softmax threads per row with accumulators of their own (423 us; the issuer then issues twice as many
 // products).  Kept: the probabilities in tensor memory and the deeper ring that their shared memory pays for (413),
-// the block table in registers (405).
+// the block table in registers (405).  Head size 128 has twice the products per tile and had one block of four
+// softmax warps per SM (its shared memory): there two query tiles per block, each with an issuing thread of its own,
+// took a prompt of 8,192 tokens from 898 to 554 us (612 to 992 TFLOP/s, 0.61 of the burst peak) and one of 2,048 from
+// 82 to 52 us; the same at head size 64, where two blocks per SM already give every SM two issuers: 472 against 407.
 //
 // Scores, maximum, sum and accumulator are 32-bit; probabilities are rounded to bfloat16 for P V
 // (liteinfer/models/paged_kernels.py:282-284).  Keys outside the visible range are masked to -inf and
 // their value rows are zeroed in shared memory, so an unwritten slot of a page cannot leak.
 // Every mbarrier wait is bounded (see tcgen05.cuh); a wait that runs out sets `error_flag`.
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -52,7 +56,6 @@ namespace li {
 
 constexpr int kRows = 128;       // rows (query token x head in group) per block
 constexpr int kKeys = 64;        // keys per tile
-constexpr int kAttnThreads = 192;
 constexpr float kLog2eF = 1.4426950408889634f;
 constexpr float kLazyLog2 = 8.f;   // how far (in powers of two) a row's maximum may outgrow the reference of its exponentials
 
@@ -105,11 +108,19 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
 // writes its row of them as bfloat16 over the first 32 columns of the scores it has read, and P V takes its first
 // operand from tensor memory.  What that saves goes to the ring of keys and values: the kernel's time is how long a
 // tile takes to arrive divided by how many are on their way.
-template <int D>
-struct KvStages { static constexpr int value = D == 64 ? 5 : 6; };
+//
+// X query tiles of 128 rows per block (X = 2 at head size 128, where one tile's block would be alone on its SM with
+// four softmax warps and an issuing thread that sets the pace: 612 TFLOP/s for a prompt of 8,192 tokens).  Every tile
+// has an issuing thread, four softmax warps, score buffers, accumulator and barriers of its own and runs as if it
+// were alone; the tiles share the loader and the ring, so a tile of keys and values is fetched once for all of them,
+// and a stage is free when every tile's P V has read it.
+template <int D, int X>
+struct KvStages { static constexpr int value = D == 64 ? 5 : (X == 1 ? 6 : 5); };
 
-template <int D>
-__global__ void __launch_bounds__(kAttnThreads, D == 64 ? 2 : 1)
+template <int X> constexpr int attn_threads() { return 32 + 32 * X + 128 * X; }   // loader, X issuers, X x 4 softmax warps
+
+template <int D, int X>
+__global__ void __launch_bounds__(attn_threads<X>(), (D == 64 && X == 1) ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          const TcAttnParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -118,17 +129,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   constexpr unsigned kKeySubBytes = kKeys * 64 * 2;                 // 8 KB: 64 keys x 64 dimensions
   constexpr unsigned kRowSubBytes = kRows * 64 * 2;                 // 16 KB: 128 rows x 64 columns
   constexpr unsigned kTileBytes = kSub * kKeySubBytes;              // one K or V tile
-  constexpr int kKvStages = KvStages<D>::value;
-  const unsigned q_smem = base;
-  const unsigned k_smem = q_smem + kSub * kRowSubBytes;             // kKvStages
+  constexpr int kKvStages = KvStages<D, X>::value;
+  const unsigned q_smem = base;                                     // X tiles
+  const unsigned k_smem = q_smem + X * kSub * kRowSubBytes;         // kKvStages
   const unsigned v_smem = k_smem + kKvStages * kTileBytes;          // kKvStages
   const unsigned bars = v_smem + kKvStages * kTileBytes;
   auto kv_full = [&](int s) { return bars + 8u * s; };                    // keys and values of a stage have landed
   auto kv_empty = [&](int s) { return bars + 8u * (2 * kKvStages + s); };
-  auto s_full = [&](int b) { return bars + 8u * (3 * kKvStages + b); };
-  auto p_full = [&](int b) { return bars + 8u * (3 * kKvStages + 4 + b); };
-  auto pv_done = [&](int b) { return bars + 8u * (3 * kKvStages + 6 + b); };
-  const unsigned tmem_slot = bars + 8u * (3 * kKvStages + 8);
+  // (tile x's own barriers: x is the warp's tile, fixed below)
+  auto tile_bar = [&](int x, int which, int b) { return bars + 8u * (3 * kKvStages + x * 6 + which * 2 + b); };
+  const unsigned tmem_slot = bars + 8u * (3 * kKvStages + 6 * X);
   __shared__ unsigned tmem_base_shared;
   unsigned char* generic_base = smem_raw + (base - smem_addr(smem_raw));   // the same place as a generic pointer
 
@@ -141,32 +151,42 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   const int tq = kRows / groups;
   // The last query tiles see the most keys: they are handed out first, across all heads and sequences (the query
   // tile is the slowest index of the grid), so that the long blocks do not end up alone at the end of the launch.
-  const int q0 = (int)(gridDim.z - 1 - blockIdx.z) * tq;
-  if (q0 >= q_len) return;
+  const int block_q0 = (int)(gridDim.z - 1 - blockIdx.z) * X * tq;
+  if (block_q0 >= q_len) return;
   const int ctx = p.context_lens[seq];
-  const int tile_q = min(tq, q_len - q0);
-  const int rows_used = tile_q * groups;
+  const int block_q = min(X * tq, q_len - block_q0);         // query tokens of the block: its tiles walk the same keys
   const int* table = p.block_table + (size_t)seq * p.table_stride;
-  const int first_qpos = ctx - q_len + q0, last_qpos = first_qpos + tile_q - 1;
-  const int hi = last_qpos + 1;
-  const int lo = (p.window > 0 && first_qpos - p.window + 1 > 0) ? first_qpos - p.window + 1 : 0;
+  const int hi = ctx - q_len + block_q0 + block_q;
+  const int lo = (p.window > 0 && ctx - q_len + block_q0 - p.window + 1 > 0) ? ctx - q_len + block_q0 - p.window + 1 : 0;
+  // The warp's own tile (issuer x is warp 1 + x, its softmax warps are 1 + X + 4 x ...): its queries and positions.
+  const int x = X == 1 ? 0 : (warp <= X ? max(warp - 1, 0) : (warp - 1 - X) >> 2);
+  const int q0 = block_q0 + x * tq;
+  const int tile_q = max(0, min(tq, q_len - q0));
+  const int rows_used = tile_q * groups;
+  const int first_qpos = ctx - q_len + q0, last_qpos = first_qpos + max(tile_q, 1) - 1;
+  auto s_full = [&](int b) { return tile_bar(x, 0, b); };
+  auto p_full = [&](int b) { return tile_bar(x, 1, b); };
+  auto pv_done = [&](int b) { return tile_bar(x, 2, b); };
   const int tile_lo = lo / kKeys, tile_hi = (hi + kKeys - 1) / kKeys;
   const int ntiles = tile_hi - tile_lo;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kKvStages; ++s) {
       mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
+      mbar_init(kv_empty(s), X);          // every tile's issuer says when its P V has read the stage
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full(b), 1);
-      mbar_init(p_full(b), 4);
-      mbar_init(pv_done(b), 1);
-    }
+    for (int t = 0; t < X; ++t)
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(tile_bar(t, 0, b), 1);
+        mbar_init(tile_bar(t, 1, b), 4);
+        mbar_init(tile_bar(t, 2, b), 1);
+      }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {   // scores 2 x 64 columns, output D columns: 256 columns asked for (a power of two)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256u) : "memory");
+  // Per tile two score buffers of 64 columns and an accumulator of D: a power of two of columns is asked for.
+  constexpr unsigned kTmemCols = X * (128 + D) <= 256 ? 256u : 512u;
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   grid_dependency_wait();   // q and the newest keys and values come from the kernel before; what is above waits for nobody
@@ -219,7 +239,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     for (int t = 0; t < tiles_ahead; ++t) load_tile(t, true);
   }
   // Q: each softmax thread copies its row (128 bytes) into the swizzled tile; rows of padding are zero.
-  if (warp >= 2) {
+  if (warp > X) {
     const int row = (warp & 3) * 32 + lane;
 #pragma unroll
     for (int sub = 0; sub < kSub; ++sub) {
@@ -233,7 +253,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 #pragma unroll
         for (int c = 0; c < 8; ++c) v[c] = make_uint4(0, 0, 0, 0);
       }
-      unsigned char* dst = generic_base + (q_smem - base) + sub * kRowSubBytes + row * 128;
+      unsigned char* dst = generic_base + (q_smem - base) + (x * kSub + sub) * kRowSubBytes + row * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(dst + ((c ^ (row & 7)) << 4)) = v[c];
     }
@@ -249,14 +269,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   }
   __syncthreads();
   const unsigned tmem_base = tmem_base_shared;
-  const unsigned tmem_s[2] = {tmem_base, tmem_base + 64u};
-  const unsigned tmem_o = tmem_base + 128u;
+  const unsigned tmem_s[2] = {tmem_base + x * 128u, tmem_base + x * 128u + 64u};
+  const unsigned tmem_o = tmem_base + X * 128u + x * D;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ loader
     for (int t = tiles_ahead; t < ntiles; ++t)
       if (!load_tile(t, false)) break;
-  } else if (warp == 1) {
+  } else if (warp <= X) {
     // ------------------------------------------------------------------ issuer
     if (lane == 0) {
       // f32 accumulate, bf16 x bf16, M 128, N 64; for P V the second operand (values) is N-major.
@@ -264,7 +284,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       constexpr unsigned idesc_pv = idesc_qk | (1u << 16);
       // A descriptor's low bits are its address in units of 16 bytes, so the descriptor of a place further on in
       // shared memory is the first one plus the distance: one addition per product instead of the whole encoding.
-      const unsigned long long desc_q = umma_desc(q_smem), desc_k = umma_desc(k_smem), desc_v = umma_desc(v_smem);
+      const unsigned long long desc_q = umma_desc(q_smem + x * kSub * kRowSubBytes), desc_k = umma_desc(k_smem),
+                               desc_v = umma_desc(v_smem);
       // S of tile t may overwrite its buffer: the softmax threads read tile t-2 out of it before they announced its
       // probabilities (which lie in the same columns), that announcement was waited for before P V of tile t-2 was
       // issued, and products run in the order they were issued.
@@ -385,7 +406,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       if (key0 < lo || key0 + kKeys > hi) {
         if (!mbar_wait(kv_full(stage), (unsigned)(t / kKvStages) & 1, p.error_flag, 18)) { ok = false; break; }
         unsigned char* vt = generic_base + (v_smem - base) + stage * kTileBytes;
-        for (int e = threadIdx.x - 64; e < kSub * kKeys * 8; e += 128) {
+        for (int e = threadIdx.x - 32 * (1 + X) - 128 * x; e < kSub * kKeys * 8; e += 128) {
           const int sub = e / (kKeys * 8), key = (e >> 3) % kKeys;
           const int kpos = key0 + key;
           if (kpos < lo || kpos >= hi)
@@ -430,7 +451,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -461,20 +482,20 @@ static bool make_pool_map(CUtensorMap* map, const void* pool, long rows, int pag
   return true;
 }
 
-template <int D>
+template <int D, int X>
 static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
                                cudaStream_t stream) {
-  constexpr int kKvStages = KvStages<D>::value;
-  constexpr size_t smem = (size_t)(D / 64) * kRows * 64 * 2 + 2 * kKvStages * (size_t)kKeys * D * 2 +
-                          8 * (3 * kKvStages + 8) + 16 + 1024;
+  constexpr int kKvStages = KvStages<D, X>::value;
+  constexpr size_t smem = (size_t)X * (D / 64) * kRows * 64 * 2 + 2 * kKvStages * (size_t)kKeys * D * 2 +
+                          8 * (3 * kKvStages + 6 * X + 2) + 16 + 1024;
   static_assert(smem <= 232448, "more shared memory than a block may have");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)launch_pdl(0, attention_tcgen05_kernel<D>, grid, dim3(kAttnThreads), smem, stream, mk, mv, p);
+  return (int)launch_pdl(0, attention_tcgen05_kernel<D, X>, grid, dim3(attn_threads<X>()), smem, stream, mk, mv, p);
 }
 
 }  // namespace li
@@ -514,6 +535,12 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
                  scale * kLog2eF, window, error_flag};
   const int groups = heads / kv_heads;
   const int tq = kRows / groups;
+  // Two query tiles per block at head size 128 where some sequence brings enough queries for two
+  // (LITEINFER_TCGEN05_ATTN_TILES=1 keeps one).
+  static const bool one_tile = [] { const char* e = getenv("LITEINFER_TCGEN05_ATTN_TILES"); return e && atoi(e) == 1; }();
+  if (head_dim == 128 && max_q_len > tq && !one_tile)
+    return launch_tc_attention<128, 2>(mk, mv, p, dim3(kv_heads, num_seqs, (max_q_len + 2 * tq - 1) / (2 * tq)), stream);
   const dim3 grid(kv_heads, num_seqs, (max_q_len + tq - 1) / tq);
-  return head_dim == 64 ? launch_tc_attention<64>(mk, mv, p, grid, stream) : launch_tc_attention<128>(mk, mv, p, grid, stream);
+  return head_dim == 64 ? launch_tc_attention<64, 1>(mk, mv, p, grid, stream)
+                        : launch_tc_attention<128, 1>(mk, mv, p, grid, stream);
 }
