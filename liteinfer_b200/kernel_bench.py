@@ -184,6 +184,8 @@ CASES = {
     "prefill_attention_512": lambda: attention(1, 512, 512),
     "prefill_attention_8192": lambda: attention(1, 8192, 8192),
     "prefill_attention_8192_page64": lambda: attention(1, 8192, 8192, page=64),
+    "prefill_attention_8192_head128": lambda: attention(1, 8192, 8192, head_dim=128),
+    "prefill_attention_4x2048_ctx4096_head128": lambda: attention(4, 2048, 4096, head_dim=128),
     "prefill_attention_16384": lambda: attention(1, 16384, 16384),
     "prefill_attention_32x1024": lambda: attention(32, 1024, 1024),
     "decode_attention_b8_ctx1024": lambda: attention(8, 1, 1024),
