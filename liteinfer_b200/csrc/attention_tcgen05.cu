@@ -40,6 +40,8 @@
 // softmax warps per SM (its shared memory): there two query tiles per block, each with an issuing thread of its own,
 // took a prompt of 8,192 tokens from 898 to 554 us (612 to 992 TFLOP/s, 0.61 of the burst peak) and one of 2,048 from
 // 82 to 52 us; the same at head size 64, where two blocks per SM already give every SM two issuers: 472 against 407.
+// A second issuing thread per tile (one for S, one for P V, ordered by a barrier where the order of issue used to
+// do) changed nothing for the better: 579 against 554 us at head size 128, 425 against 407 at 64.
 //
 // Scores, maximum, sum and accumulator are 32-bit; probabilities are rounded to bfloat16 for P V
 // (liteinfer/models/paged_kernels.py:282-284).  Keys outside the visible range are masked to -inf and
