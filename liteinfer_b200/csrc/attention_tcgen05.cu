@@ -311,12 +311,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         if (!mbar_wait(p_full(buf), (unsigned)(t >> 1) & 1, p.error_flag, 15)) { ok = false; break; }
         tcgen05_fence_after();
         const unsigned long long dv = desc_v + (unsigned long long)((stage * kTileBytes) >> 4);
+        // One product per 16 keys covers all D dimensions: the values' sub-tiles of 64 dimensions lie kKeySubBytes
+        // apart, which the descriptor's leading offset says (it is unused where D is 64).
+        constexpr unsigned idesc_pv_all = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) |
+                                          ((unsigned)(kRows >> 4) << 24);
+        const unsigned long long dv_all = (dv & ~(0x3fffULL << 16)) | ((unsigned long long)((kKeySubBytes >> 4) & 0x3fff) << 16);
 #pragma unroll
-        for (int sub = 0; sub < kSub; ++sub)
-#pragma unroll
-          for (int k = 0; k < kKeys / 16; ++k)
-            umma_bf16_ts(tmem_o + sub * 64, tmem_s[buf] + k * 8u,
-                         dv + (unsigned long long)((sub * kKeySubBytes + k * 16 * 128) >> 4), idesc_pv, t > 0 || k > 0);
+        for (int k = 0; k < kKeys / 16; ++k)
+          umma_bf16_ts(tmem_o, tmem_s[buf] + k * 8u, (kSub == 1 ? dv : dv_all) + (unsigned long long)((k * 16 * 128) >> 4),
+                       kSub == 1 ? idesc_pv : idesc_pv_all, t > 0 || k > 0);
         umma_commit(kv_empty(stage));
         umma_commit(pv_done(buf));
       }
