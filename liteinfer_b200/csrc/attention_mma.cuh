@@ -128,31 +128,38 @@ __device__ __forceinline__ void merge_splits(const AttnParams& p, unsigned char*
   __syncthreads();
   if (!*is_last_flag) return;
   __threadfence();
-  // Every thread merges four dimensions of one row by itself, eight splits at a time: the eight log-sum-exps and the
-  // eight partial rows are asked for together (one trip to L2 per eight splits), and the running result is rescaled
-  // to the largest log-sum-exp seen so far, as a softmax over blocks of keys would be.  No thread waits for another.
+  // A thread merges four dimensions of one row, eight splits at a time: the eight log-sum-exps and the eight partial
+  // rows are asked for together (one trip to L2 per eight splits), and the running result is rescaled to the largest
+  // log-sum-exp seen so far, as a softmax over blocks of keys would be.  Where the block has more threads than such
+  // items, P neighbouring lanes share an item (lane j takes the splits j, j + P, ...) and merge their running
+  // results by shuffles at the end.  No shared memory, no barrier.
   const int S = p.num_splits;
-  for (int e = threadIdx.x; e < rows_used * (D / 4); e += kWarps * 32) {
-    const int row = e / (D / 4), d4 = e % (D / 4);
+  const int items = rows_used * (D / 4);
+  const int P = items * 4 <= kWarps * 32 ? 4 : (items * 2 <= kWarps * 32 ? 2 : 1);
+  for (int e0 = 0; e0 < items * P; e0 += kWarps * 32) {
+    const int e = e0 + threadIdx.x;
+    const bool live = e < items * P;             // (whole warps are live or not where P > 1: items * P is a multiple of 32 then, or the loop runs once)
+    const int item = live ? e / P : 0, part = e % P;
+    const int row = item / (D / 4), d4 = item % (D / 4);
     const int qi = q0 + row / groups, head = kvh * groups + row % groups;
     const size_t first = ((size_t)(q_begin + qi) * p.heads + head) * S;
     const float* lse = p.partial_lse + first;
     const float4* src = reinterpret_cast<const float4*>(p.partial_out + first * D) + d4;
     float mx = -INFINITY, denom = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < S; s0 += 8) {
+    for (int s0 = part; live && s0 < S; s0 += 8 * P) {
       float w[8];
       float4 v[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (s0 + j < S) {
-          w[j] = __ldcg(lse + s0 + j);
-          v[j] = __ldcg(src + (size_t)(s0 + j) * (D / 4));
+        if (s0 + j * P < S) {
+          w[j] = __ldcg(lse + s0 + j * P);
+          v[j] = __ldcg(src + (size_t)(s0 + j * P) * (D / 4));
         }
       float top = mx;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (s0 + j < S) top = fmaxf(top, w[j]);
+        if (s0 + j * P < S) top = fmaxf(top, w[j]);
       if (top == -INFINITY) continue;            // nothing seen yet in any of these splits
       const float keep = mx == -INFINITY ? 0.f : exp2f(mx - top);
       denom *= keep;
@@ -160,15 +167,29 @@ __device__ __forceinline__ void merge_splits(const AttnParams& p, unsigned char*
       mx = top;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (s0 + j < S) {
+        if (s0 + j * P < S) {
           const float wj = w[j] == -INFINITY ? 0.f : exp2f(w[j] - top);
           denom += wj;
           acc.x += wj * v[j].x; acc.y += wj * v[j].y; acc.z += wj * v[j].z; acc.w += wj * v[j].w;
         }
     }
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d4 * 4;
-    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+    // The lanes of an item meet: each pair's results are scaled to the larger maximum and added.
+    for (int o = 1; o < P; o <<= 1) {
+      const float mo = __shfl_xor_sync(0xffffffffu, mx, o), dn = __shfl_xor_sync(0xffffffffu, denom, o);
+      const float ax = __shfl_xor_sync(0xffffffffu, acc.x, o), ay = __shfl_xor_sync(0xffffffffu, acc.y, o);
+      const float az = __shfl_xor_sync(0xffffffffu, acc.z, o), aw = __shfl_xor_sync(0xffffffffu, acc.w, o);
+      const float top = fmaxf(mx, mo);
+      const float mine = mx == -INFINITY ? 0.f : exp2f(mx - top), theirs = mo == -INFINITY ? 0.f : exp2f(mo - top);
+      denom = denom * mine + dn * theirs;
+      acc.x = acc.x * mine + ax * theirs; acc.y = acc.y * mine + ay * theirs;
+      acc.z = acc.z * mine + az * theirs; acc.w = acc.w * mine + aw * theirs;
+      mx = top;
+    }
+    if (live && part == 0) {
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
+      bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d4 * 4;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+    }
   }
   if (threadIdx.x == 0) p.counters[counter_index] = 0;   // ready for the next launch
 }
